@@ -1,0 +1,332 @@
+// extern "C" entry points of libflashdmla.so: argument checks, problem
+// set-up and dispatch to the tcgen05 or the portable kernels.  Nothing here
+// allocates or synchronises; every scratch buffer comes from the caller.
+#include "common.cuh"
+
+#include <atomic>
+
+namespace fdmla {
+
+static std::atomic<int> g_backend{FDMLA_BACKEND_AUTO};
+static thread_local const char *t_last_kernel = "none";
+
+static inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+static inline size_t elem_size(int dtype) { return dtype == FDMLA_F32 ? 4 : 2; }
+static inline bool dtype_ok(int dtype) { return dtype == FDMLA_F32 || dtype == FDMLA_BF16; }
+
+static int run_forward(const FwdProblem &p, int dtype, cudaStream_t stream) {
+    const int backend = g_backend.load();
+    const bool tc_ok = fwd_tensor_supported(p, dtype);
+    if (backend == FDMLA_BACKEND_TENSOR && !tc_ok) return FDMLA_ERR_UNSUPPORTED;
+    if (tc_ok && backend != FDMLA_BACKEND_PORTABLE) {
+        t_last_kernel = "tcgen05";
+        return launch_fwd_tensor(p, dtype, stream);
+    }
+    t_last_kernel = "portable";
+    return launch_fwd_portable(p, dtype, stream);
+}
+
+// --- paged cache writer / gather -------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+cache_append_kernel(const T *__restrict__ rows, T *__restrict__ pool,
+                    const int32_t *__restrict__ page_table, const int32_t *__restrict__ start_pos,
+                    int n_tokens, int d, int page_size, int max_pages, int num_pages) {
+    const int b = blockIdx.y, t = blockIdx.x;
+    const int pos = start_pos[b] + t;
+    const int lp = pos / page_size;
+    if (pos < 0 || lp >= max_pages) return;
+    const int pg = page_table[(size_t)b * max_pages + lp];
+    if (pg < 0 || pg >= num_pages) return;
+    const T *src = rows + ((size_t)b * n_tokens + t) * d;
+    T *dst = pool + ((size_t)pg * page_size + (pos - lp * page_size)) * d;
+    for (int k = threadIdx.x; k < d; k += blockDim.x) dst[k] = src[k];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+cache_gather_kernel(const T *__restrict__ pool, const int32_t *__restrict__ page_table,
+                    const int32_t *__restrict__ seqlens, T *__restrict__ out, int n_tokens, int d,
+                    int page_size, int max_pages, int num_pages) {
+    const int b = blockIdx.y, t = blockIdx.x;
+    T *dst = out + ((size_t)b * n_tokens + t) * d;
+    const int lp = t / page_size;
+    int pg = -1;
+    if (t < seqlens[b] && lp < max_pages) pg = page_table[(size_t)b * max_pages + lp];
+    if (pg < 0 || pg >= num_pages) {
+        for (int k = threadIdx.x; k < d; k += blockDim.x) dst[k] = from_f32<T>(0.f);
+        return;
+    }
+    const T *src = pool + ((size_t)pg * page_size + (t - lp * page_size)) * d;
+    for (int k = threadIdx.x; k < d; k += blockDim.x) dst[k] = src[k];
+}
+
+}  // namespace fdmla
+
+using namespace fdmla;
+
+extern "C" {
+
+int fdmla_version(void) { return 100; }
+
+const char *fdmla_status_string(int status) {
+    switch (status) {
+        case FDMLA_OK: return "ok";
+        case FDMLA_ERR_INVALID: return "invalid argument";
+        case FDMLA_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+        case FDMLA_ERR_CUDA: return "CUDA error";
+        case FDMLA_ERR_WORKSPACE: return "workspace missing or too small";
+        default: return "unknown status";
+    }
+}
+
+int fdmla_set_backend(int backend) {
+    if (backend < FDMLA_BACKEND_AUTO || backend > FDMLA_BACKEND_TENSOR) return FDMLA_ERR_INVALID;
+    g_backend.store(backend);
+    return FDMLA_OK;
+}
+int fdmla_get_backend(void) { return g_backend.load(); }
+const char *fdmla_last_kernel(void) { return t_last_kernel; }
+
+int fdmla_fwd_cache_latent(const void *Q, const void *K_lat, void *O, float *m, float *l, int B,
+                           int H, int Sq, int Skv, int d_qk, int d_v, float scale, int causal,
+                           int dtype, void *stream) {
+    if (!dtype_ok(dtype)) return FDMLA_ERR_INVALID;
+    if (B < 0 || H < 0 || Sq < 0 || Skv < 0 || d_qk <= 0 || d_v <= 0 || d_v > d_qk) return FDMLA_ERR_INVALID;
+    if (B == 0 || H == 0 || Sq == 0) return FDMLA_OK;
+    if (!Q || !O || !m || !l || (!K_lat && Skv > 0)) return FDMLA_ERR_INVALID;
+    if ((long long)H * Sq > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
+    FwdProblem p{};
+    p.Q = Q; p.K = K_lat; p.V = nullptr; p.page_table = nullptr; p.seqlens = nullptr;
+    p.O = O; p.m = m; p.l = l;
+    p.G = B; p.R = H * Sq; p.Sq = Sq; p.Skv = Skv; p.d_qk = d_qk; p.d_v = d_v;
+    p.page_size = 0; p.max_pages = 0; p.num_pages = 0; p.num_splits = 1;
+    p.kv_begin = 0; p.kv_end = -1; p.causal = causal ? 1 : 0; p.scale = scale;
+    return run_forward(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+size_t fdmla_fwd_on_the_fly_workspace_bytes(int B, int H, int Skv, int d_lat, int dtype) {
+    if (B <= 0 || H <= 0 || Skv <= 0 || d_lat <= 0 || !dtype_ok(dtype)) return 0;
+    return 2 * align256((size_t)B * H * Skv * d_lat * elem_size(dtype));
+}
+
+int fdmla_fwd_on_the_fly(const void *Q, const void *K, const void *V, const void *WK,
+                         const void *WV, void *O, float *m, float *l, void *workspace,
+                         size_t workspace_bytes, int B, int H, int Sq, int Skv, int d_model,
+                         int d_lat, float scale, int causal, int dtype, void *stream) {
+    if (!dtype_ok(dtype)) return FDMLA_ERR_INVALID;
+    if (B < 0 || H < 0 || Sq < 0 || Skv < 0 || d_model <= 0 || d_lat <= 0) return FDMLA_ERR_INVALID;
+    if (B == 0 || H == 0 || Sq == 0) return FDMLA_OK;
+    if (!Q || !O || !m || !l || !WK || !WV) return FDMLA_ERR_INVALID;
+    if (Skv > 0 && (!K || !V)) return FDMLA_ERR_INVALID;
+    const size_t need = fdmla_fwd_on_the_fly_workspace_bytes(B, H, Skv, d_lat, dtype);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return FDMLA_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return FDMLA_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+    void *K_lat = ws;
+    void *V_lat = ws + need / 2;
+    const long long nkv = (long long)B * H * Skv;
+    int rc = launch_project(K, WK, K_lat, nkv, d_model, d_lat, 0, 0, dtype, st);
+    if (rc) return rc;
+    rc = launch_project(V, WV, V_lat, nkv, d_model, d_lat, 0, 0, dtype, st);
+    if (rc) return rc;
+    FwdProblem p{};
+    p.Q = Q; p.K = K_lat; p.V = V_lat; p.O = O; p.m = m; p.l = l;
+    p.G = B * H; p.R = Sq; p.Sq = Sq; p.Skv = Skv; p.d_qk = d_lat; p.d_v = d_lat;
+    p.num_splits = 1; p.kv_begin = 0; p.kv_end = -1; p.causal = causal ? 1 : 0; p.scale = scale;
+    if (p.G > 65535) return FDMLA_ERR_UNSUPPORTED;
+    return run_forward(p, dtype, st);
+}
+
+int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v, int page_size,
+                                int dtype) {
+    (void)d_qk; (void)dtype;
+    if (B <= 0 || H <= 0 || max_seqlen <= 0 || page_size <= 0) return 1;
+    const int pages = (max_seqlen + page_size - 1) / page_size;
+    // thread blocks per split: tcgen05 path uses 128-row tiles x d_v halves
+    long long per_split = (long long)B * ((H + 127) / 128) * (d_v > 256 ? 2 : 1);
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= 32 && s <= pages; ++s) {
+        long long blocks = per_split * s;
+        long long waves = (blocks + kNumSMs - 1) / kNumSMs;
+        double eff = (double)blocks / (double)(waves * kNumSMs);
+        // each split adds a partial write + merge read; prefer fewer splits on ties
+        eff -= 0.004 * s;
+        if ((pages / s) < 4) break;
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+    }
+    return best;
+}
+
+int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_table,
+                       const int32_t *seqlens, void *O, float *m, float *l, float *O_part,
+                       float *m_part, float *l_part, int B, int H, int d_qk, int d_v,
+                       int page_size, int max_pages, int num_pages, int num_splits, int kv_begin,
+                       int kv_end, float scale, int dtype, void *stream) {
+    if (!dtype_ok(dtype)) return FDMLA_ERR_INVALID;
+    if (B < 0 || H < 0 || d_qk <= 0 || d_v <= 0 || d_v > d_qk || page_size <= 0 || max_pages < 0 ||
+        num_pages < 0 || num_splits < 1)
+        return FDMLA_ERR_INVALID;
+    if (B == 0 || H == 0) return FDMLA_OK;
+    if (!Q || !kv_pool || !page_table || !seqlens) return FDMLA_ERR_INVALID;
+    const bool partial_only = (O == nullptr);
+    if (!partial_only && (!m || !l)) return FDMLA_ERR_INVALID;
+    if ((num_splits > 1 || partial_only) && (!O_part || !m_part || !l_part)) return FDMLA_ERR_WORKSPACE;
+    if (B > 65535) return FDMLA_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    FwdProblem p{};
+    p.Q = Q; p.K = kv_pool; p.V = nullptr; p.page_table = page_table; p.seqlens = seqlens;
+    p.O = (num_splits == 1) ? O : nullptr; p.m = m; p.l = l;
+    p.O_part = O_part; p.m_part = m_part; p.l_part = l_part;
+    p.G = B; p.R = H; p.Sq = 1; p.Skv = max_pages * page_size; p.d_qk = d_qk; p.d_v = d_v;
+    p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages;
+    p.num_splits = num_splits; p.kv_begin = kv_begin; p.kv_end = kv_end; p.causal = 0; p.scale = scale;
+    int rc = run_forward(p, dtype, st);
+    if (rc) return rc;
+    if (num_splits > 1 && !partial_only)
+        rc = launch_merge(O_part, m_part, l_part, O, m, l, (long long)B * H, d_v, num_splits, dtype, st);
+    return rc;
+}
+
+int fdmla_merge_lse(const float *O_part, const float *m_part, const float *l_part, void *O,
+                    float *m, float *l, long long rows, int d_v, int num_parts, int out_dtype,
+                    void *stream) {
+    if (!dtype_ok(out_dtype) || rows < 0 || d_v <= 0 || num_parts < 1) return FDMLA_ERR_INVALID;
+    if (rows == 0) return FDMLA_OK;
+    if (!O_part || !m_part || !l_part || !O || !m || !l) return FDMLA_ERR_INVALID;
+    return launch_merge(O_part, m_part, l_part, O, m, l, rows, d_v, num_parts, out_dtype,
+                        static_cast<cudaStream_t>(stream));
+}
+
+// workspace of the on-the-fly backward:
+//   K_lat, V_lat (dtype) | dK_lat, dV_lat (fp32) | D (fp32) | wgrad partial slabs (fp32)
+struct BwdOtfLayout { size_t klat, vlat, dklat, dvlat, D, part, total; };
+static BwdOtfLayout bwd_otf_layout(int B, int H, int Sq, int Skv, int d_model, int d_lat, int dtype) {
+    BwdOtfLayout L{};
+    const size_t nkv = (size_t)B * H * Skv, nq = (size_t)B * H * Sq;
+    size_t off = 0;
+    L.klat = off; off += align256(nkv * d_lat * elem_size(dtype));
+    L.vlat = off; off += align256(nkv * d_lat * elem_size(dtype));
+    L.dklat = off; off += align256(nkv * d_lat * 4);
+    L.dvlat = off; off += align256(nkv * d_lat * 4);
+    L.D = off; off += align256(nq * 4);
+    L.part = off; off += align256((size_t)wgrad_num_partials((long long)nkv) * d_model * d_lat * 4);
+    L.total = off;
+    return L;
+}
+
+size_t fdmla_bwd_on_the_fly_workspace_bytes(int B, int H, int Sq, int Skv, int d_model, int d_lat,
+                                            int dtype) {
+    if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || d_model <= 0 || d_lat <= 0 || !dtype_ok(dtype)) return 0;
+    return bwd_otf_layout(B, H, Sq, Skv, d_model, d_lat, dtype).total;
+}
+
+int fdmla_bwd_on_the_fly(const void *Q, const void *K, const void *V, const void *WK,
+                         const void *WV, const void *O, const float *m, const float *l,
+                         const void *dO, void *dQ, void *dK, void *dV, void *dWK, void *dWV,
+                         void *workspace, size_t workspace_bytes, int B, int H, int Sq, int Skv,
+                         int d_model, int d_lat, float scale, int causal, int dtype, void *stream) {
+    if (!dtype_ok(dtype)) return FDMLA_ERR_INVALID;
+    if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || d_model <= 0 || d_lat <= 0) return FDMLA_ERR_INVALID;
+    if (!Q || !K || !V || !WK || !WV || !O || !m || !l || !dO || !dQ || !dK || !dV || !dWK || !dWV)
+        return FDMLA_ERR_INVALID;
+    const BwdOtfLayout L = bwd_otf_layout(B, H, Sq, Skv, d_model, d_lat, dtype);
+    if (!workspace || workspace_bytes < L.total) return FDMLA_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return FDMLA_ERR_INVALID;
+    if ((long long)B * H > 65535) return FDMLA_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *ws = static_cast<char *>(workspace);
+    void *K_lat = ws + L.klat, *V_lat = ws + L.vlat;
+    float *dK_lat = reinterpret_cast<float *>(ws + L.dklat);
+    float *dV_lat = reinterpret_cast<float *>(ws + L.dvlat);
+    const long long nkv = (long long)B * H * Skv;
+    int rc = launch_project(K, WK, K_lat, nkv, d_model, d_lat, 0, 0, dtype, st);
+    if (rc) return rc;
+    rc = launch_project(V, WV, V_lat, nkv, d_model, d_lat, 0, 0, dtype, st);
+    if (rc) return rc;
+    BwdProblem p{};
+    p.Q = Q; p.K = K_lat; p.V = V_lat; p.O = O; p.dO = dO; p.m = m; p.l = l;
+    p.D = reinterpret_cast<float *>(ws + L.D);
+    p.dQ = dQ; p.dK = dK_lat; p.dV = dV_lat;
+    p.G = B * H; p.R = Sq; p.Sq = Sq; p.Skv = Skv; p.d_qk = d_lat; p.d_v = d_lat;
+    p.causal = causal ? 1 : 0; p.scale = scale;
+    rc = launch_bwd_portable(p, dtype, /*grads_f32=*/1, st);
+    if (rc) return rc;
+    // dK = dK_lat WK^T, dV = dV_lat WV^T
+    rc = launch_project(dK_lat, WK, dK, nkv, d_lat, d_model, 1, 1, dtype, st);
+    if (rc) return rc;
+    rc = launch_project(dV_lat, WV, dV, nkv, d_lat, d_model, 1, 1, dtype, st);
+    if (rc) return rc;
+    // dWK = sum K^T dK_lat, dWV = sum V^T dV_lat
+    float *part = reinterpret_cast<float *>(ws + L.part);
+    rc = launch_wgrad(K, dK_lat, part, dWK, nkv, d_model, d_lat, dtype, st);
+    if (rc) return rc;
+    return launch_wgrad(V, dV_lat, part, dWV, nkv, d_model, d_lat, dtype, st);
+}
+
+size_t fdmla_bwd_cache_latent_workspace_bytes(int B, int H, int Sq, int Skv, int d_qk, int d_v,
+                                              int dtype) {
+    (void)Skv; (void)d_qk; (void)d_v;
+    if (B <= 0 || H <= 0 || Sq <= 0 || !dtype_ok(dtype)) return 0;
+    return align256((size_t)B * H * Sq * 4);
+}
+
+int fdmla_bwd_cache_latent(const void *Q, const void *K_lat, const void *O, const float *m,
+                           const float *l, const void *dO, void *dQ, void *dK_lat,
+                           void *workspace, size_t workspace_bytes, int B, int H, int Sq, int Skv,
+                           int d_qk, int d_v, float scale, int causal, int dtype, void *stream) {
+    if (!dtype_ok(dtype)) return FDMLA_ERR_INVALID;
+    if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || d_qk <= 0 || d_v <= 0 || d_v > d_qk) return FDMLA_ERR_INVALID;
+    if (!Q || !K_lat || !O || !m || !l || !dO || !dQ || !dK_lat) return FDMLA_ERR_INVALID;
+    const size_t need = fdmla_bwd_cache_latent_workspace_bytes(B, H, Sq, Skv, d_qk, d_v, dtype);
+    if (!workspace || workspace_bytes < need) return FDMLA_ERR_WORKSPACE;
+    BwdProblem p{};
+    p.Q = Q; p.K = K_lat; p.V = nullptr; p.O = O; p.dO = dO; p.m = m; p.l = l;
+    p.D = static_cast<float *>(workspace);
+    p.dQ = dQ; p.dK = dK_lat; p.dV = nullptr;
+    p.G = B; p.R = H * Sq; p.Sq = Sq; p.Skv = Skv; p.d_qk = d_qk; p.d_v = d_v;
+    p.causal = causal ? 1 : 0; p.scale = scale;
+    return launch_bwd_portable(p, dtype, /*grads_f32=*/0, static_cast<cudaStream_t>(stream));
+}
+
+int fdmla_cache_append(const void *new_rows, void *kv_pool, const int32_t *page_table,
+                       const int32_t *start_pos, int B, int n_tokens, int d_qk, int page_size,
+                       int max_pages, int num_pages, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || B < 0 || n_tokens < 0 || d_qk <= 0 || page_size <= 0 || max_pages < 0 || num_pages < 0)
+        return FDMLA_ERR_INVALID;
+    if (B == 0 || n_tokens == 0) return FDMLA_OK;
+    if (!new_rows || !kv_pool || !page_table || !start_pos) return FDMLA_ERR_INVALID;
+    if (B > 65535) return FDMLA_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid(n_tokens, B);
+    if (dtype == FDMLA_F32)
+        cache_append_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float *>(new_rows),
+            static_cast<float *>(kv_pool), page_table, start_pos, n_tokens, d_qk, page_size, max_pages, num_pages);
+    else
+        cache_append_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(new_rows),
+            static_cast<__nv_bfloat16 *>(kv_pool), page_table, start_pos, n_tokens, d_qk, page_size, max_pages, num_pages);
+    return check_launch();
+}
+
+int fdmla_cache_gather(const void *kv_pool, const int32_t *page_table, const int32_t *seqlens,
+                       void *out, int B, int n_tokens, int d_qk, int page_size, int max_pages,
+                       int num_pages, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || B < 0 || n_tokens < 0 || d_qk <= 0 || page_size <= 0 || max_pages < 0 || num_pages < 0)
+        return FDMLA_ERR_INVALID;
+    if (B == 0 || n_tokens == 0) return FDMLA_OK;
+    if (!kv_pool || !page_table || !seqlens || !out) return FDMLA_ERR_INVALID;
+    if (B > 65535) return FDMLA_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid(n_tokens, B);
+    if (dtype == FDMLA_F32)
+        cache_gather_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float *>(kv_pool), page_table, seqlens,
+            static_cast<float *>(out), n_tokens, d_qk, page_size, max_pages, num_pages);
+    else
+        cache_gather_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(kv_pool),
+            page_table, seqlens, static_cast<__nv_bfloat16 *>(out), n_tokens, d_qk, page_size, max_pages, num_pages);
+    return check_launch();
+}
+
+}  // extern "C"

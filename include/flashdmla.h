@@ -1,0 +1,203 @@
+/*
+ * flashdmla.h - C ABI of libflashdmla.so, the B200 (sm_100a) Flash-DMLA
+ * attention backend.
+ *
+ * Conventions shared by every entry point (they keep the style of the
+ * reference's host launchers, csrc/attention/fa2_fwd.cu:139-147: raw device
+ * pointers, dense row-major tensors, an explicit softmax scale, a trailing
+ * stream argument):
+ *   - every pointer is a DEVICE pointer owned by the caller; nothing is
+ *     allocated, freed or synchronised inside the library;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*) and the
+ *     call returns immediately;
+ *   - unlike the reference (void launchers, silent return on bad arguments:
+ *     fa2_fwd.cu:149, vanallia_attn.cu:95) every call returns a status:
+ *     0 on success, a negative FDMLA_ERR_* otherwise;
+ *   - `dtype` selects the element type of Q/K/V/W/O/dO and gradient tensors
+ *     (FDMLA_F32 or FDMLA_BF16); row statistics m, l and partial results are
+ *     always fp32; accumulation is always fp32;
+ *   - m[i] = max_j s_ij and l[i] = sum_j exp(s_ij - m[i]) over the visible
+ *     keys of row i with s = scale * q.k (natural exp), the row_max/row_sum of
+ *     vanallia_attn.cu:50,69; a row with no visible key has m=-inf, l=0, O=0;
+ *   - the causal mask is bottom-right aligned: key j is visible to query i
+ *     iff j <= i + (Skv - Sq).
+ */
+#ifndef FLASHDMLA_H_
+#define FLASHDMLA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FDMLA_F32  0
+#define FDMLA_BF16 1
+
+#define FDMLA_OK               0
+#define FDMLA_ERR_INVALID     -1   /* null pointer, non-positive size, bad enum      */
+#define FDMLA_ERR_UNSUPPORTED -2   /* shape outside what the kernels implement        */
+#define FDMLA_ERR_CUDA        -3   /* a CUDA runtime/driver call or a launch failed   */
+#define FDMLA_ERR_WORKSPACE   -4   /* workspace missing or smaller than required      */
+
+/* Kernel families, for fdmla_set_backend(): AUTO picks the tcgen05/TMA kernels
+ * whenever the shape qualifies and the portable CUDA-core kernels otherwise. */
+#define FDMLA_BACKEND_AUTO     0
+#define FDMLA_BACKEND_PORTABLE 1   /* CUDA-core kernels only (any shape)              */
+#define FDMLA_BACKEND_TENSOR   2   /* tcgen05 kernels only; unsupported shapes fail   */
+
+/* Library version (major*10000 + minor*100 + patch).  No reference counterpart. */
+int fdmla_version(void);
+
+/* Human-readable text for a status code.  No reference counterpart (the
+ * reference reports no errors at all). */
+const char *fdmla_status_string(int status);
+
+/* Process-wide kernel-family override used by tests and profiling.  Replaces
+ * the reference's per-call `warps_per_block` tuning knob (fa2_fwd.cu:146,150). */
+int fdmla_set_backend(int backend);
+int fdmla_get_backend(void);
+
+/* Name of the kernel family the last call on this thread dispatched to
+ * ("tcgen05" or "portable").  No reference counterpart. */
+const char *fdmla_last_kernel(void);
+
+/*
+ * Cache-latent DMLA forward.
+ *   Q     [B, H, Sq, d_qk]
+ *   K_lat [B, Skv, d_qk]      latent rows shared by all heads; V = K_lat[..., :d_v]
+ *   O     [B, H, Sq, d_v]     m, l [B, H, Sq] fp32
+ * Replaces the role of fa2_forward (csrc/attention/fa2_fwd.cu:139-156) for the
+ * cache-latent mode the reference's README describes (README.md:15); per
+ * (b, h) it solves the same problem as that launcher with K = K_lat[b],
+ * V = K_lat[b][:, :d_v], plus the causal mask and the m/l outputs.
+ */
+int fdmla_fwd_cache_latent(const void *Q, const void *K_lat, void *O, float *m,
+                           float *l, int B, int H, int Sq, int Skv, int d_qk,
+                           int d_v, float scale, int causal, int dtype,
+                           void *stream);
+
+/*
+ * On-the-fly DMLA forward: K_lat = K*WK and V_lat = V*WV are projected inside
+ * the call, then attention runs on the latents.
+ *   Q [B, H, Sq, d_lat]   K, V [B, H, Skv, d_model]   WK, WV [d_model, d_lat]
+ *   O [B, H, Sq, d_lat]   m, l [B, H, Sq] fp32
+ *   workspace: fdmla_fwd_on_the_fly_workspace_bytes() bytes of device scratch
+ *   (holds the projected latents; they are left there for the backward).
+ * Replaces fa2_forward (fa2_fwd.cu:139-156) for the on-the-fly mode of
+ * README.md:14.
+ */
+size_t fdmla_fwd_on_the_fly_workspace_bytes(int B, int H, int Skv, int d_lat, int dtype);
+int fdmla_fwd_on_the_fly(const void *Q, const void *K, const void *V,
+                         const void *WK, const void *WV, void *O, float *m,
+                         float *l, void *workspace, size_t workspace_bytes,
+                         int B, int H, int Sq, int Skv, int d_model, int d_lat,
+                         float scale, int causal, int dtype, void *stream);
+
+/*
+ * Paged cache-latent decode (one query token per sequence), split-KV.
+ *   Q          [B, H, d_qk]
+ *   kv_pool    [num_pages, page_size, d_qk]   latent rows, V = first d_v columns
+ *   page_table [B, max_pages] int32           logical page -> physical page
+ *   seqlens    [B] int32                      tokens held by each sequence
+ *   Only tokens t with kv_begin <= t < min(kv_end, seqlens[b]) are attended
+ *   (kv_end < 0: no upper limit), so a rank can compute the partial result of
+ *   its slice of a long sequence.
+ *   num_splits >= 1 splits the attended range of every sequence into that many
+ *   page-aligned pieces computed by different thread blocks.  Their partial
+ *   results go to O_part [num_splits, B, H, d_v], m_part, l_part
+ *   [num_splits, B, H] (fp32, caller-provided scratch; may be NULL when
+ *   num_splits == 1) and are merged into O [B, H, d_v] (dtype), m, l [B, H].
+ *   If O is NULL only the partials are produced.
+ *   Every page id read from page_table must be in [0, num_pages).
+ * The paged cache is the "KV-cache" of README.md:15; per (b, h) the math is
+ * that of vanilla_attn_forward (vanallia_attn.cu:85-99) on the gathered rows.
+ */
+int fdmla_decode_paged(const void *Q, const void *kv_pool,
+                       const int32_t *page_table, const int32_t *seqlens,
+                       void *O, float *m, float *l, float *O_part,
+                       float *m_part, float *l_part, int B, int H, int d_qk,
+                       int d_v, int page_size, int max_pages, int num_pages,
+                       int num_splits, int kv_begin, int kv_end, float scale,
+                       int dtype, void *stream);
+
+/* Split count the library would choose for a decode problem (fills the GPU
+ * with whole waves).  No reference counterpart. */
+int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,
+                                int page_size, int dtype);
+
+/*
+ * Log-sum-exp merge of partial attention results over disjoint key sets.
+ *   O_part [num_parts, rows, d_v] fp32 (each normalised by its own l_part)
+ *   m_part, l_part [num_parts, rows] fp32
+ *   O [rows, d_v] (out_dtype), m, l [rows] fp32
+ * m = max_p m_p; w_p = l_p exp(m_p - m); l = sum w_p; O = sum w_p O_p / l:
+ * the running update of fa2_fwd.cu:93-111 applied across partials.
+ */
+int fdmla_merge_lse(const float *O_part, const float *m_part,
+                    const float *l_part, void *O, float *m, float *l,
+                    long long rows, int d_v, int num_parts, int out_dtype,
+                    void *stream);
+
+/*
+ * On-the-fly DMLA backward.  Inputs of the forward plus its outputs O, m, l
+ * and the incoming gradient dO [B, H, Sq, d_lat].  P is recomputed from the
+ * saved m, l.  Outputs (overwritten, no pre-zeroing needed, no atomics):
+ *   dQ [B, H, Sq, d_lat]   dK, dV [B, H, Skv, d_model]   dWK, dWV [d_model, d_lat]
+ *   workspace: fdmla_bwd_on_the_fly_workspace_bytes() bytes of device scratch.
+ * Replaces fa2_backward (csrc/attention/fa2_bwd.cu:332-356), whose formulas
+ * (:198-216, :234, :252-254, :259-272, :293-309) it follows with the softmax
+ * scale applied to dQ and dK_lat.
+ */
+size_t fdmla_bwd_on_the_fly_workspace_bytes(int B, int H, int Sq, int Skv,
+                                            int d_model, int d_lat, int dtype);
+int fdmla_bwd_on_the_fly(const void *Q, const void *K, const void *V,
+                         const void *WK, const void *WV, const void *O,
+                         const float *m, const float *l, const void *dO,
+                         void *dQ, void *dK, void *dV, void *dWK, void *dWV,
+                         void *workspace, size_t workspace_bytes, int B, int H,
+                         int Sq, int Skv, int d_model, int d_lat, float scale,
+                         int causal, int dtype, void *stream);
+
+/*
+ * Cache-latent backward: dQ [B, H, Sq, d_qk] and dK_lat [B, Skv, d_qk]; the
+ * value gradient is folded into the first d_v columns of dK_lat because
+ * V = K_lat[..., :d_v].  Same formulas as above (fa2_bwd.cu:198-309).
+ *   workspace: fdmla_bwd_cache_latent_workspace_bytes() bytes.
+ */
+size_t fdmla_bwd_cache_latent_workspace_bytes(int B, int H, int Sq, int Skv,
+                                              int d_qk, int d_v, int dtype);
+int fdmla_bwd_cache_latent(const void *Q, const void *K_lat, const void *O,
+                           const float *m, const float *l, const void *dO,
+                           void *dQ, void *dK_lat, void *workspace,
+                           size_t workspace_bytes, int B, int H, int Sq,
+                           int Skv, int d_qk, int d_v, float scale, int causal,
+                           int dtype, void *stream);
+
+/*
+ * Copy `n_tokens` new latent rows per sequence into the paged pool.
+ *   new_rows [B, n_tokens, d_qk]; token t of sequence b is written at logical
+ *   position start_pos[b] + t through page_table.
+ * The writer side of the cache the decode consumes (README.md:15); no source
+ * for it exists in the reference.
+ */
+int fdmla_cache_append(const void *new_rows, void *kv_pool,
+                       const int32_t *page_table, const int32_t *start_pos,
+                       int B, int n_tokens, int d_qk, int page_size,
+                       int max_pages, int num_pages, int dtype, void *stream);
+
+/*
+ * Gather the first n_tokens logical rows of every sequence into a dense
+ * [B, n_tokens, d_qk] tensor (rows past seqlens[b] are zero).  Used to check
+ * page-table indexing bit-exactly.  No reference counterpart.
+ */
+int fdmla_cache_gather(const void *kv_pool, const int32_t *page_table,
+                       const int32_t *seqlens, void *out, int B, int n_tokens,
+                       int d_qk, int page_size, int max_pages, int num_pages,
+                       int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHDMLA_H_ */
