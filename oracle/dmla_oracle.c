@@ -131,6 +131,18 @@ void oracle_fwd_cache_latent(const float *Q, const float *K_lat, float *O,
     }
 }
 
+/* Round to the nearest bfloat16 (ties to even), returned as fp32. */
+static float bf16_round(float x)
+{
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return x;   /* NaN */
+    u += 0x7fffu + ((u >> 16) & 1u);
+    u &= 0xffff0000u;
+    memcpy(&x, &u, 4);
+    return x;
+}
+
 /* C[M,N] = A[M,K] * B[K,N], fp32, ascending-k fused multiply-add. */
 static void matmul(const float *A, const float *Bm, float *C, long M, int K, int N)
 {
@@ -151,18 +163,23 @@ static void matmul(const float *A, const float *Bm, float *C, long M, int K, int
  * WK,WV[d_model,d_lat] shared by every (b,h).  K_lat = K*WK, V_lat = V*WV,
  * then attn_row per query row with per-head latents, d_qk = d_v = d_lat.
  * K_lat_out / V_lat_out (may be NULL) receive the projected latents.
+ * latents_bf16 != 0 rounds the projected latents to bfloat16 before the
+ * attention, which is how a bf16 kernel has to store them to feed them to the
+ * tensor cores.
  */
 void oracle_fwd_on_the_fly(const float *Q, const float *K, const float *V,
                            const float *WK, const float *WV, float *O, float *m,
                            float *l, float *K_lat_out, float *V_lat_out, int B,
                            int H, int Sq, int Skv, int d_model, int d_lat,
-                           float scale, int causal)
+                           float scale, int causal, int latents_bf16)
 {
     long nkv = (long)B * H * Skv;
     float *Kl = K_lat_out ? K_lat_out : (float *)malloc(sizeof(float) * nkv * d_lat);
     float *Vl = V_lat_out ? V_lat_out : (float *)malloc(sizeof(float) * nkv * d_lat);
     matmul(K, WK, Kl, nkv, d_model, d_lat);
     matmul(V, WV, Vl, nkv, d_model, d_lat);
+    if (latents_bf16)
+        for (long t = 0; t < nkv * d_lat; ++t) { Kl[t] = bf16_round(Kl[t]); Vl[t] = bf16_round(Vl[t]); }
     long rows = (long)B * H * Sq;
 #pragma omp parallel
     {

@@ -115,7 +115,7 @@ def fwd_cache_latent(Q, K_lat, d_v, scale, causal=True):
     return O, m, l
 
 
-def fwd_on_the_fly(Q, K, V, WK, WV, scale, causal=True, return_latents=False):
+def fwd_on_the_fly(Q, K, V, WK, WV, scale, causal=True, return_latents=False, latents_bf16=False):
     Q, K, V, WK, WV = map(_f32, (Q, K, V, WK, WV))
     B, H, Sq, d_lat = Q.shape
     Skv, d_model = K.shape[2], K.shape[3]
@@ -126,7 +126,8 @@ def fwd_on_the_fly(Q, K, V, WK, WV, scale, causal=True, return_latents=False):
     Vl = np.empty((B, H, Skv, d_lat), np.float32) if return_latents else None
     lib().oracle_fwd_on_the_fly(_p(Q), _p(K), _p(V), _p(WK), _p(WV), _p(O), _p(m),
                                 _p(l), _p(Kl), _p(Vl), B, H, Sq, Skv, d_model,
-                                d_lat, ctypes.c_float(scale), int(bool(causal)))
+                                d_lat, ctypes.c_float(scale), int(bool(causal)),
+                                int(bool(latents_bf16)))
     if return_latents:
         return O, m, l, Kl, Vl
     return O, m, l
