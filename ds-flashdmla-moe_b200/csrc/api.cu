@@ -87,6 +87,7 @@ int fdmla_set_backend(int backend) {
 }
 int fdmla_get_backend(void) { return g_backend.load(); }
 const char *fdmla_last_kernel(void) { return t_last_kernel; }
+int fdmla_device_error_flag(int reset) { return tensor_error_flag(reset); }
 
 int fdmla_fwd_cache_latent(const void *Q, const void *K_lat, void *O, float *m, float *l, int B,
                            int H, int Sq, int Skv, int d_qk, int d_v, float scale, int causal,

@@ -56,7 +56,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: gives up after `kSpinLimit` polls (each poll may itself suspend
 // for a hardware-defined time) so that a lost arrival can never hang the GPU.
 // Returns false on time-out.
-constexpr uint32_t kSpinLimit = 8u << 20;
+constexpr uint32_t kSpinLimit = 2u << 20;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t it = 0; it < kSpinLimit; ++it)
         if (mbar_try_wait(bar, parity)) return true;

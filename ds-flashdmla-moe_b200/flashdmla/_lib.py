@@ -24,6 +24,7 @@ SIGNATURES = {
     "fdmla_set_backend": (_i, [_i]),
     "fdmla_get_backend": (_i, []),
     "fdmla_last_kernel": (ctypes.c_char_p, []),
+    "fdmla_device_error_flag": (_i, [_i]),
     "fdmla_fwd_cache_latent": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
     "fdmla_fwd_on_the_fly_workspace_bytes": (_sz, [_i] * 5),
     "fdmla_fwd_on_the_fly": (_i, [_vp] * 9 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),
@@ -73,3 +74,8 @@ def set_backend(backend: int) -> None:
 
 def last_kernel() -> str:
     return lib().fdmla_last_kernel().decode()
+
+
+def device_error_flag(reset: bool = False) -> int:
+    """0 if no tensor-core kernel reported a timed-out wait or a bad page id (synchronises)."""
+    return int(lib().fdmla_device_error_flag(int(reset)))

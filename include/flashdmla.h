@@ -63,6 +63,13 @@ int fdmla_get_backend(void);
  * ("tcgen05" or "portable").  No reference counterpart. */
 const char *fdmla_last_kernel(void);
 
+/* Device-side error flag of the tensor-core kernels on the current device:
+ * 0 = none, 1..3 = a bounded wait inside a kernel gave up (producer, MMA,
+ * softmax role), 4 = a page id outside [0, num_pages) was read from a page
+ * table.  Synchronises the device; reset != 0 clears the flag.  Returns -1 if
+ * the flag cannot be read.  No reference counterpart. */
+int fdmla_device_error_flag(int reset);
+
 /*
  * Cache-latent DMLA forward.
  *   Q     [B, H, Sq, d_qk]

@@ -253,6 +253,29 @@ def test_cache_latent_backward(dtype, backend, cuda):
     assert rel_fro(Qd.grad, dQ) <= tol and rel_fro(Kd.grad, dK) <= tol
 
 
+def test_production_shapes_run_on_tensor_cores(cuda):
+    """bf16 MLA / d=64 shapes dispatch to the tcgen05 kernels, and no kernel reported a
+    timed-out wait or a bad page id."""
+    import flashdmla
+    flashdmla.set_backend(flashdmla.BACKEND_AUTO)
+    Q = _rand((1, 4, 128, 576), 0.1, 1, torch.bfloat16).to(cuda)
+    K = _rand((1, 128, 576), 0.1, 2, torch.bfloat16).to(cuda)
+    flashdmla.flash_dmla_cache_latent(Q, K, 512, 0.07, True)
+    assert flashdmla.last_kernel() == "tcgen05"
+    Q, pool, table, sl = _paged(2, 128, [130, 64], 576, 64, torch.bfloat16)
+    flashdmla.flash_dmla_paged_decode(Q.to(cuda), pool.to(cuda), table.to(cuda), sl.to(cuda), 512, 0.07)
+    assert flashdmla.last_kernel() == "tcgen05"
+    Qo = _rand((1, 2, 128, 64), 1.0, 3, torch.bfloat16).to(cuda)
+    Ko = _rand((1, 2, 128, 128), 1.0, 4, torch.bfloat16).to(cuda)
+    W = _rand((128, 64), 0.1, 5, torch.bfloat16).to(cuda)
+    flashdmla.flash_dmla_on_the_fly(Qo, Ko, Ko, W, W, 0.125, True)
+    assert flashdmla.last_kernel() == "tcgen05"
+    flashdmla.flash_dmla_cache_latent(Q.to(cuda).float()[:, :, None, :64].contiguous(),
+                                      K.float()[:, :, :64].contiguous(), 32, 0.1, True)
+    assert flashdmla.last_kernel() == "portable"      # fp32 stays on the CUDA-core kernels
+    assert flashdmla.device_error_flag() == 0
+
+
 # ----------------------------------------------------------------------------- properties
 def test_runs_are_deterministic(backend, cuda):
     import flashdmla
