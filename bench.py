@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the Flash-DMLA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload (one "step"): DeepSeek-V3-shape paged MLA decode, bf16,
+B=128 sequences per GPU, H=128, Skv=4096, 576-wide latent rows (V = first 512),
+page size 64, page table = seeded random permutation of the pool, scale
+1/sqrt(192), entries 0.1*N(0,1).  Sequences are sharded over GPUs with no
+collective (weak scaling: every GPU decodes its own 128 sequences).  The line
+also carries the causal-prefill figure (B=4, H=128, S=8192, heads sharded).
+
+`--impl reference` times the CPU oracle (the restatement of the reference's
+naive attention; the reference ships no CPU code and no DMLA kernels) on the
+host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "ds-flashdmla-moe_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+# ---- workload constants (BASELINE configs 2 and 3) -------------------------------------------
+B, H, SKV, D_QK, D_V, PAGE = 128, 128, 4096, 576, 512, 64
+SCALE = 1.0 / math.sqrt(192.0)
+DECODE_BYTES = (B * SKV * D_QK * 2          # latent rows read once
+                + B * H * D_QK * 2          # Q
+                + B * H * D_V * 2           # O
+                + 2 * B * H * 4             # m, l
+                + B * (SKV // PAGE) * 4)    # page table            = 639 795 200
+DECODE_FLOP = 2 * B * H * SKV * (D_QK + D_V)
+PF_B, PF_H, PF_S = 4, 128, 8192
+PREFILL_FLOP_CAUSAL = 2 * PF_B * PF_H * (PF_S * (PF_S + 1) // 2) * (D_QK + D_V)
+
+
+def set_batch(b: int) -> None:
+    """Reduced decode case (fewer sequences, same per-sequence shape) for profiler captures."""
+    global B, DECODE_BYTES, DECODE_FLOP
+    B = int(b)
+    DECODE_BYTES = B * SKV * D_QK * 2 + B * H * D_QK * 2 + B * H * D_V * 2 + 2 * B * H * 4 + B * (SKV // PAGE) * 4
+    DECODE_FLOP = 2 * B * H * SKV * (D_QK + D_V)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle sampling while the timed region runs (rank 0)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc, self.idx = None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_decode_inputs(dev, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    n_pages = B * SKV // PAGE
+    pool = (torch.randn(n_pages, PAGE, D_QK, generator=g, device=dev, dtype=torch.float32) * 0.1).to(torch.bfloat16)
+    Q = (torch.randn(B, H, D_QK, generator=g, device=dev, dtype=torch.float32) * 0.1).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).to(torch.int32)
+    table = perm.view(B, SKV // PAGE).contiguous().to(dev)
+    seqlens = torch.full((B,), SKV, dtype=torch.int32, device=dev)
+    return Q, pool, table, seqlens
+
+
+def time_steps(fn, steps, warmup, world):
+    """W untimed + exactly K timed steps between barrier+synchronize; device time, ms total."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def cpu_baseline_sample(target_s=12.0):
+    """Oracle (port of the reference's naive attention) on the host cores, bounded sample."""
+    from flashdmla import synthetic
+    from oracle import dmla_oracle as orc
+    def run(nseq):
+        Q, pool, table, sl = synthetic.paged_decode_inputs(nseq, H, [SKV] * nseq, D_QK, PAGE, seed=3, std=0.1,
+                                                          dtype=torch.float32)
+        t = time.perf_counter()
+        orc.decode_paged(Q, pool, table, sl, D_V, SCALE)
+        return time.perf_counter() - t
+    t1 = run(2) / 2.0
+    nseq = int(max(2, min(B, target_s / max(t1, 1e-3))))
+    dt = run(nseq)
+    return {"value": nseq / dt, "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
+            "sample": f"{nseq} of {B} sequences x {H} heads x {SKV} keys, fp32 oracle (oracle/dmla_oracle.c), "
+                      f"{dt:.2f} s, all host threads"}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU oracle on the host cores, same metric and config."""
+    if rank != 0:
+        return
+    from flashdmla import synthetic
+    from oracle import dmla_oracle as orc
+    probe = 2
+    Q, pool, table, sl = synthetic.paged_decode_inputs(probe, H, [SKV] * probe, D_QK, PAGE, seed=3, std=0.1,
+                                                      dtype=torch.float32)
+    t = time.perf_counter()
+    orc.decode_paged(Q, pool, table, sl, D_V, SCALE)
+    t1 = (time.perf_counter() - t) / probe
+    budget = 150.0 / max(1, args.steps + args.warmup)           # whole run within a few minutes
+    nseq = int(max(1, min(B, min(2.0, budget) / max(t1, 1e-3))))
+    Q, pool, table, sl = synthetic.paged_decode_inputs(nseq, H, [SKV] * nseq, D_QK, PAGE, seed=3, std=0.1,
+                                                      dtype=torch.float32)
+    for _ in range(args.warmup):
+        orc.decode_paged(Q, pool, table, sl, D_V, SCALE)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        orc.decode_paged(Q, pool, table, sl, D_V, SCALE)
+    dt = time.perf_counter() - t
+    value = nseq * args.steps / dt
+    sample = (f"{nseq} of {B} sequences x {H} heads x {SKV} keys per step, fp32 oracle "
+              f"(oracle/dmla_oracle.c, restating the reference's csrc/attention/vanallia_attn.cu), all host threads")
+    print(json.dumps({
+        "impl": "reference", "metric": "paged_mla_decode_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "paged_mla_decode B=128 H=128 Skv=4096 d=576/512 page=64 (bounded sample per step)"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-prefill", action="store_true", help="skip the secondary causal-prefill measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--splits", type=int, default=0, help="override the decode split count (0 = library choice)")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="decode sequences per GPU (default 128); smaller values give the reduced case used for ncu captures")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.batch:
+        set_batch(args.batch)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import flashdmla
+    from flashdmla import _lib
+
+    hbm_peak, tf_burst, tf_sust, peak_src = peaks()
+    Q, pool, table, seqlens = make_decode_inputs(dev, seed=1000 + rank)
+    splits = args.splits or flashdmla.suggest_splits(B, H, SKV, D_QK, D_V, PAGE)
+    ws = flashdmla.DecodeWorkspace()
+    launches_per_step = 2 if splits > 1 else 1
+
+    def step():
+        return flashdmla.flash_dmla_paged_decode(Q, pool, table, seqlens, D_V, SCALE, num_splits=splits,
+                                                 workspace=ws, max_seqlen=SKV)
+
+    O, m, l = step()
+    torch.cuda.synchronize()
+    kernel_family = flashdmla.last_kernel()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    total_ms = time_steps(step, args.steps, args.warmup, world)
+    ms_per_step = total_ms / args.steps
+    value = world * B / (ms_per_step * 1e-3)
+
+    # dominant kernel alone (split-KV attention without the merge), CUDA events on its stream
+    Op, mp, lp = ws.get(splits, B, H, D_V, dev)
+    L = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def kernel_only():
+        _lib.check(L.fdmla_decode_paged(Q.data_ptr(), pool.data_ptr(), table.data_ptr(), seqlens.data_ptr(),
+                                        None, None, None, Op.data_ptr(), mp.data_ptr(), lp.data_ptr(), B, H, D_QK,
+                                        D_V, PAGE, SKV // PAGE, pool.shape[0], splits, 0, -1, SCALE, _lib.BF16,
+                                        stream), "fdmla_decode_paged")
+    k_ms = time_steps(kernel_only, args.steps, 3, world) / args.steps
+    achieved = DECODE_BYTES / (k_ms * 1e-3) / 1e9
+
+    # end to end: host buffers in, host buffers out, through the public operator
+    hQ, htab, hlen = Q.cpu().pin_memory(), table.cpu().pin_memory(), seqlens.cpu().pin_memory()
+    dQ, dtab, dlen = torch.empty_like(Q), torch.empty_like(table), torch.empty_like(seqlens)
+    hO = torch.empty(B, H, D_V, dtype=torch.bfloat16).pin_memory()
+    hm, hl = torch.empty(B, H).pin_memory(), torch.empty(B, H).pin_memory()
+
+    def e2e_step():
+        dQ.copy_(hQ, non_blocking=True); dtab.copy_(htab, non_blocking=True); dlen.copy_(hlen, non_blocking=True)
+        o, mm, ll = flashdmla.flash_dmla_paged_decode(dQ, pool, dtab, dlen, D_V, SCALE, num_splits=splits,
+                                                      workspace=ws, max_seqlen=SKV)
+        hO.copy_(o, non_blocking=True); hm.copy_(mm, non_blocking=True); hl.copy_(ll, non_blocking=True)
+    e2e_ms = time_steps(e2e_step, args.steps, 3, world) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    h2d = hQ.numel() * 2 + htab.numel() * 4 + hlen.numel() * 4
+    d2h = hO.numel() * 2 + hm.numel() * 4 + hl.numel() * 4
+
+    prefill = None
+    if not args.no_prefill:
+        prefill = bench_prefill(dev, rank, world, tf_burst)
+
+    err = flashdmla.device_error_flag()
+    if rank == 0:
+        cpu = None if (args.no_cpu or world > 1) else cpu_baseline_sample()
+        line = {
+            "metric": "paged_mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "paged_mla_decode", "B_per_gpu": B, "H": H, "Skv": SKV, "d_qk": D_QK, "d_v": D_V,
+                       "page_size": PAGE, "num_splits": splits, "parallelism": f"batch-sharded x{world}, no collective",
+                       "l2": "working set 604 MB per step exceeds the 126 MB L2 (no flush needed)",
+                       "kernel_family": kernel_family},
+            "clocks": clocks,
+            "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "note": "paged KV pool stays resident in HBM (it is the cache); Q, page table, seqlens in, O, m, l out"},
+            "gpu_launches": launches_per_step * args.steps * world,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "fwd_tc_kernel (split-KV decode)", "kernel_ms": k_ms,
+                         "algorithmic_bytes": DECODE_BYTES, "tensor_tflops": DECODE_FLOP / (k_ms * 1e-3) / 1e12,
+                         "frac_of_8TBs_spec": achieved / 8000.0},
+            "decode_hbm_gbs_per_gpu": DECODE_BYTES / (ms_per_step * 1e-3) / 1e9,
+            "prefill": prefill,
+            "device_error_flag": err,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_prefill(dev, rank, world, tf_peak, iters=3):
+    """Causal prefill, B=4,H=128,S=8192, d=576/512, heads sharded over ranks (K_lat replicated)."""
+    import flashdmla
+    Hl = PF_H // world
+    g = torch.Generator(device=dev).manual_seed(77)
+    K = (torch.randn(PF_B, PF_S, D_QK, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    Q = torch.empty(PF_B, Hl, PF_S, D_QK, dtype=torch.bfloat16, device=dev)
+    for b in range(PF_B):       # generated per batch entry to bound the fp32 temporary
+        Q[b] = (torch.randn(Hl, PF_S, D_QK, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+
+    def step():
+        return flashdmla.flash_dmla_cache_latent(Q, K, D_V, SCALE, True)
+    ms = time_steps(step, iters, 1, world) / iters
+    tflops = PREFILL_FLOP_CAUSAL / (ms * 1e-3) / 1e12
+    return {"workload": "causal prefill B=4 H=128 S=8192 d=576/512, heads sharded", "ms": ms, "tflops_total": tflops,
+            "tflops_per_gpu": tflops / world, "frac_of_measured_bf16_peak": tflops / world / tf_peak,
+            "frac_of_2250_spec": tflops / world / 2250.0, "kernel_family": flashdmla.last_kernel(),
+            "tokens_per_s": PF_B * PF_S / (ms * 1e-3)}
+
+
+if __name__ == "__main__":
+    main()

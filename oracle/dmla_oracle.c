@@ -219,22 +219,26 @@ void oracle_decode_paged(const float *Q, const float *kv_pool,
         long cap = (long)max_pages * page_size;
         long *idx = (long *)malloc(sizeof(long) * (size_t)(cap > 0 ? cap : 1));
         float *sbuf = (float *)malloc(sizeof(float) * (size_t)(cap > 0 ? cap : 1));
-#pragma omp for schedule(dynamic, 1)
-        for (int b = 0; b < B; ++b) {
-            int hi = seqlens[b];
-            if (kv_end >= 0 && kv_end < hi) hi = kv_end;
-            int lo = kv_begin > 0 ? kv_begin : 0;
-            int n = hi > lo ? hi - lo : 0;
-            for (int t = 0; t < n; ++t) {
-                int tok = lo + t;
-                idx[t] = (long)page_table[(size_t)b * max_pages + tok / page_size] *
-                             page_size + tok % page_size;
+        long last_b = -1;
+        int n = 0;
+#pragma omp for schedule(dynamic, 4)
+        for (long bh = 0; bh < (long)B * H; ++bh) {
+            int b = (int)(bh / H);
+            if (b != last_b) {              /* gather list of this sequence's pool rows */
+                int hi = seqlens[b];
+                if (kv_end >= 0 && kv_end < hi) hi = kv_end;
+                int lo = kv_begin > 0 ? kv_begin : 0;
+                n = hi > lo ? hi - lo : 0;
+                for (int t = 0; t < n; ++t) {
+                    int tok = lo + t;
+                    idx[t] = (long)page_table[(size_t)b * max_pages + tok / page_size] *
+                                 page_size + tok % page_size;
+                }
+                last_b = b;
             }
-            for (int h = 0; h < H; ++h) {
-                size_t r = (size_t)b * H + h;
-                attn_row(Q + r * d_qk, kv_pool, d_qk, kv_pool, d_qk, idx, n,
-                         d_qk, d_v, scale, sbuf, O + r * d_v, m + r, l + r);
-            }
+            size_t r = (size_t)bh;
+            attn_row(Q + r * d_qk, kv_pool, d_qk, kv_pool, d_qk, idx, n, d_qk,
+                     d_v, scale, sbuf, O + r * d_v, m + r, l + r);
         }
         free(idx);
         free(sbuf);

@@ -28,9 +28,20 @@ def max_abs(a, b):
 
 
 def assert_O(got, want, bf16=True, what="O"):
-    ma, rf = max_abs(got, want), rel_fro(got, want)
-    lim_a, lim_r = (O_MAX_ABS, O_REL_FRO) if bf16 else (F32_MAX_ABS, F32_REL_FRO)
-    assert ma <= lim_a and rf <= lim_r, f"{what}: max-abs {ma:.3e} (<= {lim_a}), rel-Fro {rf:.3e} (<= {lim_r})"
+    """Target tolerance: max-abs <= 1e-2 and relative Frobenius <= 5e-3.  A bf16 OUTPUT
+    cannot meet an absolute 1e-2 where |O| >= 4 (its spacing there is 2^-5), so each element
+    is allowed 1e-2 plus one bf16 rounding step (2^-8 |O|) of the value it has to represent."""
+    g, w = to_np(got).astype(np.float64), to_np(want).astype(np.float64)
+    rf = rel_fro(got, want)
+    if bf16:
+        excess = np.abs(g - w) - (O_MAX_ABS + np.abs(w) * 2.0 ** -8)
+        worst = float(excess.max()) if excess.size else -1.0
+        assert worst <= 0 and rf <= O_REL_FRO, \
+            f"{what}: max-abs {max_abs(got, want):.3e} exceeds 1e-2 + 2^-8|O| by {worst:.3e}; rel-Fro {rf:.3e} (<= {O_REL_FRO})"
+    else:
+        ma = max_abs(got, want)
+        assert ma <= F32_MAX_ABS and rf <= F32_REL_FRO, \
+            f"{what}: max-abs {ma:.3e} (<= {F32_MAX_ABS}), rel-Fro {rf:.3e} (<= {F32_REL_FRO})"
 
 
 def assert_stats(m, l, m_ref, l_ref, what="m/l"):
