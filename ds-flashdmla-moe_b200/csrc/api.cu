@@ -86,6 +86,7 @@ int fdmla_set_backend(int backend) {
     return FDMLA_OK;
 }
 int fdmla_get_backend(void) { return g_backend.load(); }
+int fdmla_set_single_cta(int on) { tensor_prefer_single_cta(on != 0); return FDMLA_OK; }
 const char *fdmla_last_kernel(void) { return t_last_kernel; }
 int fdmla_device_error_flag(int reset) { return tensor_error_flag(reset); }
 

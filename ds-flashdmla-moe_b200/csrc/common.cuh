@@ -83,7 +83,8 @@ __host__ __device__ __forceinline__ void split_window(int w_lo, int w_hi, int gr
 int launch_fwd_portable(const FwdProblem &p, int dtype, cudaStream_t stream);
 int launch_fwd_tensor(const FwdProblem &p, int dtype, cudaStream_t stream);   // tcgen05
 bool fwd_tensor_supported(const FwdProblem &p, int dtype);
-int tensor_error_flag(int reset);   // device-side time-out / bad-page flag of the tcgen05 kernels
+int tensor_error_flag(int reset);
+void tensor_prefer_single_cta(int on);   // keep MLA shapes on the 1-CTA kernel (A/B tests)   // device-side time-out / bad-page flag of the tcgen05 kernels
 int launch_merge(const float *O_part, const float *m_part, const float *l_part, void *O,
                  float *m, float *l, long long rows, int d_v, int num_parts, int out_dtype,
                  cudaStream_t stream);

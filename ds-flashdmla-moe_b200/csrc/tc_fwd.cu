@@ -431,6 +431,19 @@ static bool make_map(CUtensorMap *m, const void *base, long long rows, int cols,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_tensor_map_bf16(CUtensorMap *m, const void *base, long long rows, int cols, int box_rows) {
+    return make_map(m, base, rows, cols, box_rows);
+}
+
+}  // namespace fdmla
+
+#include "tc_fwd2.cuh"   // 2-CTA kernel for the MLA dimensions
+
+namespace fdmla {
+
+static int g_prefer_single_cta = 0;                            // debugging / A-B switch
+void tensor_prefer_single_cta(int on) { g_prefer_single_cta = on; }
+
 template <class C>
 static bool cfg_matches(const FwdProblem &p) {
     if (p.d_qk != C::D_QK || p.d_v != C::D_V) return false;
@@ -471,6 +484,7 @@ static int launch_cfg(const FwdProblem &p, cudaStream_t stream) {
 
 int launch_fwd_tensor(const FwdProblem &p, int dtype, cudaStream_t stream) {
     if (!fwd_tensor_supported(p, dtype)) return FDMLA_ERR_UNSUPPORTED;
+    if (!g_prefer_single_cta && fwd_tensor2_supported(p, dtype)) return launch_fwd_tensor2(p, stream);
     if (cfg_matches<MlaCfg>(p)) return launch_cfg<MlaCfg>(p, stream);
     if (cfg_matches<OtfCfg>(p)) return launch_cfg<OtfCfg>(p, stream);
     return launch_cfg<Cl64Cfg>(p, stream);

@@ -23,6 +23,7 @@ SIGNATURES = {
     "fdmla_status_string": (ctypes.c_char_p, [_i]),
     "fdmla_set_backend": (_i, [_i]),
     "fdmla_get_backend": (_i, []),
+    "fdmla_set_single_cta": (_i, [_i]),
     "fdmla_last_kernel": (ctypes.c_char_p, []),
     "fdmla_device_error_flag": (_i, [_i]),
     "fdmla_fwd_cache_latent": (_i, [_vp] * 5 + [_i] * 6 + [_f, _i, _i, _vp]),
@@ -70,6 +71,11 @@ def check(status: int, what: str) -> None:
 
 def set_backend(backend: int) -> None:
     check(lib().fdmla_set_backend(int(backend)), "fdmla_set_backend")
+
+
+def set_single_cta(on: bool) -> None:
+    """Keep 576/512 shapes on the single-CTA tcgen05 kernel (A/B measurements, tests)."""
+    check(lib().fdmla_set_single_cta(int(bool(on))), "fdmla_set_single_cta")
 
 
 def last_kernel() -> str:

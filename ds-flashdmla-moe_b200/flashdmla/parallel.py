@@ -51,11 +51,27 @@ def unpack_partials(buf: torch.Tensor):
     return buf[..., :-2].contiguous(), buf[..., -2].contiguous(), buf[..., -1].contiguous()
 
 
+class PartialCheckError(RuntimeError):
+    """A gathered partial (O, m, l) is not a possible softmax partial."""
+
+
+def check_partials(O_p: torch.Tensor, m_p: torch.Tensor, l_p: torch.Tensor) -> None:
+    """Host-side failure detection for the exchange step: every rank's partial must
+    have finite O, l >= 0, and m finite or -inf exactly where l == 0.  Names the
+    first offending rank."""
+    bad_O = ~torch.isfinite(O_p).flatten(1).all(dim=1)
+    bad_l = (~torch.isfinite(l_p) | (l_p < 0)).flatten(1).any(dim=1)
+    bad_m = (torch.isnan(m_p) | (torch.isinf(m_p) & ((m_p > 0) | (l_p != 0)))).flatten(1).any(dim=1)
+    bad = (bad_O | bad_l | bad_m).nonzero().flatten().tolist()
+    if bad:
+        raise PartialCheckError(f"invalid partial attention result received from rank(s) {bad}")
+
+
 def sequence_parallel_decode(Q, local_pool, local_page_table, local_seqlens, d_v, scale=None,
                              group: Optional[dist.ProcessGroup] = None, out_dtype=None,
                              num_splits: Optional[int] = None,
                              decode_fn: Optional[Callable] = None,
-                             merge_fn: Optional[Callable] = None):
+                             merge_fn: Optional[Callable] = None, validate: bool = False):
     """Decode when every rank holds one slice of each sequence's paged cache.
 
     Q [B,H,d_qk] is replicated; local_* describe this rank's slice only.
@@ -77,7 +93,10 @@ def sequence_parallel_decode(Q, local_pool, local_page_table, local_seqlens, d_v
     O_loc, m_loc, l_loc = decode_fn(Q, local_pool, local_page_table, local_seqlens, d_v, scale)
     msg = pack_partial(O_loc, m_loc, l_loc)
     world = dist.get_world_size(group)
-    gathered = torch.empty((world,) + tuple(msg.shape), dtype=msg.dtype, device=msg.device)
-    dist.all_gather_into_tensor(gathered, msg, group=group)
+    flat = torch.empty((world * msg.shape[0],) + tuple(msg.shape[1:]), dtype=msg.dtype, device=msg.device)
+    dist.all_gather_into_tensor(flat, msg, group=group)      # concatenated along dim 0, rank-major
+    gathered = flat.view((world,) + tuple(msg.shape))
     O_p, m_p, l_p = unpack_partials(gathered)
+    if validate:          # synchronises; meant for debugging and for the failure-detection tests
+        check_partials(O_p, m_p, l_p)
     return merge_fn(O_p, m_p, l_p, out_dtype or Q.dtype)

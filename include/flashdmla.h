@@ -59,6 +59,11 @@ const char *fdmla_status_string(int status);
 int fdmla_set_backend(int backend);
 int fdmla_get_backend(void);
 
+/* on != 0 keeps the MLA-dimension shapes (576/512) on the single-CTA tcgen05
+ * kernel instead of the 2-CTA cluster kernel; used for A/B measurements and to
+ * keep both kernels under test.  No reference counterpart. */
+int fdmla_set_single_cta(int on);
+
 /* Name of the kernel family the last call on this thread dispatched to
  * ("tcgen05" or "portable").  No reference counterpart. */
 const char *fdmla_last_kernel(void);

@@ -13,15 +13,20 @@ from oracle import dmla_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-BACKENDS = ["portable", "auto"]
+# portable: CUDA-core kernels; auto: tcgen05 kernels wherever the shape qualifies (2-CTA kernel
+# for the MLA dimensions); auto1: the same but MLA shapes stay on the single-CTA tcgen05 kernel
+BACKENDS = ["portable", "auto", "auto1"]
 
 
 @pytest.fixture(params=BACKENDS)
 def backend(request, cuda):
     import flashdmla
-    flashdmla.set_backend({"portable": flashdmla.BACKEND_PORTABLE, "auto": flashdmla.BACKEND_AUTO}[request.param])
+    flashdmla.set_backend(flashdmla.BACKEND_PORTABLE if request.param == "portable" else flashdmla.BACKEND_AUTO)
+    flashdmla.set_single_cta(request.param == "auto1")
     yield request.param
+    flashdmla.set_single_cta(False)
     flashdmla.set_backend(flashdmla.BACKEND_AUTO)
+    assert flashdmla.device_error_flag() == 0
 
 
 def _rand(shape, std, seed, dtype):
@@ -270,8 +275,7 @@ def test_production_shapes_run_on_tensor_cores(cuda):
     W = _rand((128, 64), 0.1, 5, torch.bfloat16).to(cuda)
     flashdmla.flash_dmla_on_the_fly(Qo, Ko, Ko, W, W, 0.125, True)
     assert flashdmla.last_kernel() == "tcgen05"
-    flashdmla.flash_dmla_cache_latent(Q.to(cuda).float()[:, :, None, :64].contiguous(),
-                                      K.float()[:, :, :64].contiguous(), 32, 0.1, True)
+    flashdmla.flash_dmla_cache_latent(Qo.float(), Ko[:, 0, :, :64].float().contiguous(), 32, 0.1, True)
     assert flashdmla.last_kernel() == "portable"      # fp32 stays on the CUDA-core kernels
     assert flashdmla.device_error_flag() == 0
 
