@@ -5,21 +5,29 @@
 // a prefill) is owned by a CLUSTER of two CTAs running tcgen05.mma with
 // cta_group::2, M = 128: each CTA holds 64 of the rows.  That is what makes the
 // 512-wide output fit: 64 rows x 512 fp32 columns occupy 128 TMEM lanes x 256
-// columns per CTA, leaving room for a double-buffered S, and each CTA keeps only
-// its 64 rows of Q (72 KB) in shared memory, leaving room for a KV ring.
+// columns per CTA, next to a double-buffered S of 2 x 128 columns, and each CTA
+// keeps only its 64 rows of Q (72 KB) in shared memory.
 //
-// Per 64-key tile and per CTA (rank r of the pair):
-//   S = Q K^T   A: own 64 rows of Q        B: own 32 keys x 576 (K-major)
-//               D: 64 rows x 64 keys -> TMEM lanes 0-63 hold keys 0-31,
-//                  lanes 64-127 hold keys 32-63
-//   O += P V    A: own 64 rows of P        B: all 64 keys x own 256 columns of
-//               d_v (MN-major), as two N = 256 MMAs whose halves come from the
-//               two CTAs; D: lanes 0-63 hold d_v [0,256), lanes 64-127 [256,512)
-// so each CTA loads (32 x 576 + 64 x 256) elements per tile with TMA (no
-// multicast anywhere).  Only the leader CTA (rank 0) issues MMAs; completion is
+// Keys are processed in tiles of 256.  A tcgen05.mma costs at least ~55 cycles
+// to issue whatever its shape, so every MMA here is N = 256 wide (64 cycles of
+// work per SM):
+//   S = Q K^T   36 MMAs per tile: for each of the 9 64-column chunks of d_qk,
+//               4 K=16 steps.  A: own 64 rows of Q.  B: own 128 keys of the tile
+//               x that chunk (K-major, 16 KB per CTA and chunk).
+//               D: 64 rows x 256 keys -> TMEM lanes 0-63 hold keys 0-127,
+//                  lanes 64-127 hold keys 128-255
+//   O += P V    32 MMAs per tile: for each 64-key quarter and each half j of this
+//               CTA's d_v columns, 4 K=16 steps.  A: own 64 rows of P (quarter).
+//               B: the quarter's 64 keys x 128 own columns of d_v (MN-major,
+//               16 KB per CTA).  D: lanes 0-63 hold d_v [0,256), lanes 64-127
+//               hold d_v [256,512)
+// All operand traffic goes through ONE ring of seven 16 KB slots per CTA, filled
+// by TMA (no multicast anywhere) in exactly the order the MMAs consume it; Q*K^T
+// of tile t+1 is interleaved with P*V of tile t so both the tensor pipe and the
+// ring stay busy.  Only the leader CTA (rank 0) issues MMAs; completion is
 // broadcast to both CTAs' mbarriers with tcgen05.commit.  CTA 1 forwards "my
-// loads have landed" and "my P is written" to the leader with remote mbarrier
-// arrivals.
+// slot has landed" and both CTAs forward "my P quarter is written" to the leader
+// with remote mbarrier arrivals.
 //
 // Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (leader) / load relay
 // (peer) and TMEM owner, warps 2-5 softmax (thread L owns TMEM lane L: row
@@ -36,25 +44,25 @@ namespace fdmla {
 
 namespace tc2 {
 
-constexpr int T = 64;                 // keys per tile (pair-wide)
-constexpr int STAGES = 2;
+constexpr int T = 256;                // keys per tile (pair-wide)
+constexpr int SUB = 64;               // keys per sub-block (one TMA box, one P quarter)
 constexpr int NQC = 9;                // 64-column chunks of d_qk
 constexpr int Q_CHUNK = 64 * 128;     // 64 rows x 128 B
 constexpr int Q_BYTES = NQC * Q_CHUNK;            // 73 728
-constexpr int KA_CHUNK = 32 * 128;    // own 32 keys x 128 B
-constexpr int KA_BYTES = NQC * KA_CHUNK;          // 36 864
-constexpr int VB_CHUNK = 64 * 128;    // 64 keys x 128 B
-constexpr int VB_BYTES = 4 * VB_CHUNK;            // 32 768
-constexpr int STAGE_BYTES = KA_BYTES + VB_BYTES;  // 69 632
-constexpr int P_BYTES = 64 * T * 2;               // 8 192
-constexpr int P_SBO = (T / 8) * 128;              // 1 024
+constexpr int SLOT = 16384;           // ring slot: 2 boxes of [64 keys x 128 B]
+constexpr int BOX = 8192;
+constexpr int NSLOT = 7;
+constexpr int P_Q = 64 * SUB * 2;     // one P quarter: 64 rows x 64 keys bf16 = 8 192
+constexpr int P_BYTES = 4 * P_Q;
+constexpr int P_SBO = (SUB / 8) * 128;            // 1 024
 constexpr int RED_BYTES = 2 * 128 * 4;
-constexpr int O_COLS = 256, S_COL0 = 256, S_COLS = 32, TMEM_COLS = 512;
-// barriers
-constexpr int B_QFULL = 0, B_PEER_QFULL = 1, B_KVFULL = 2, B_PEER_FULL = B_KVFULL + STAGES,
-              B_KVEMPTY = B_PEER_FULL + STAGES, B_KVFIX = B_KVEMPTY + STAGES, B_SFULL = B_KVFIX + 1,
-              B_PFULL = B_SFULL + 2, B_OREADY = B_PFULL + 1, NBARS = B_OREADY + 1;
-constexpr int SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + RED_BYTES + NBARS * 8 + 16;
+constexpr int ROWS_CACHE = 1920;      // sub-block rows resolved through the page table up front
+constexpr int O_COLS = 256, S_COL0 = 256, S_COLS = 128, TMEM_COLS = 512;
+// barriers (same offsets in both CTAs)
+constexpr int B_QFULL = 0, B_PEER_QFULL = 1, B_FULL = 2, B_PEER = B_FULL + NSLOT, B_EMPTY = B_PEER + NSLOT,
+              B_FIX = B_EMPTY + NSLOT, B_SFULL = B_FIX + 2, B_SEMPTY = B_SFULL + 2, B_PFULL = B_SEMPTY + 2,
+              B_OREADY = B_PFULL + 4, NBARS = B_OREADY + 2;
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + NSLOT * SLOT + P_BYTES + RED_BYTES + ROWS_CACHE * 4 + NBARS * 8 + 16;
 static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
 constexpr int THREADS = 192;
 enum { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_PAGE = 4, ERR_RELAY = 14 };
@@ -65,17 +73,55 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Optional event trace of the first cluster (development builds only, -DFDMLA_TRACE):
+// g_trace[rank][stream][index] = SM clock at the event.
+#ifdef FDMLA_TRACE
+constexpr int TR_N = 256;
+__device__ long long g_trace[2][6][TR_N];
+#define TRACE(stream, idx)                                                                        \
+    do {                                                                                           \
+        if (trace_on && (idx) < TR_N) g_trace[rank][stream][idx] = clock64();                      \
+    } while (0)
+#else
+#define TRACE(stream, idx) do { } while (0)
+#endif
+
+// The one order in which ring slots are filled and consumed.  `f(is_v, t, a, b)` is
+// called for a K slot as (false, tile, chunk, 0) and for a V slot as (true, tile, quarter,
+// half j); it returns false to stop.  n_sub = number of 64-key sub-blocks to attend.
+template <class F>
+__device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
+    for (int c = 0; c < NQC; ++c)
+        if (!f(false, 0, c, 0)) return false;
+    for (int t = 0; t < n_tiles; ++t) {
+        const bool next = t + 1 < n_tiles;
+        const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;     // quarters of tile t that exist
+        int c = 0;
+        for (int q = 0; q < 4; ++q) {
+            const int c_end = (q == 0) ? 3 : (q == 1 ? 5 : (q == 2 ? 7 : 9));
+            if (next)
+                for (; c < c_end; ++c)
+                    if (!f(false, t + 1, c, 0)) return false;
+            if (q < nq) {
+                if (!f(true, t, q, 0)) return false;
+                if (!f(true, t, q, 1)) return false;
+            }
+        }
+    }
+    return true;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
-               const __grid_constant__ CUtensorMap tmK32, const __grid_constant__ CUtensorMap tmK64) {
+fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK) {
     using namespace ptx;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *sQ = smem;
-    uint8_t *sKV = sQ + Q_BYTES;
-    uint8_t *sP = sKV + STAGES * STAGE_BYTES;
+    uint8_t *sRing = sQ + Q_BYTES;                     // [NSLOT][2 boxes][64 keys][128 B]
+    uint8_t *sP = sRing + NSLOT * SLOT;                // [4 quarters][64 rows x 64 keys bf16]
     float *red = reinterpret_cast<float *>(sP + P_BYTES);       // [2][128]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(red) + RED_BYTES);
+    int *s_rows = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(red) + RED_BYTES);   // [ROWS_CACHE]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_rows + ROWS_CACHE);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * i; };
@@ -83,6 +129,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const bool leader = rank == 0;
+#ifdef FDMLA_TRACE
+    const bool trace_on = blockIdx.x < 2 && blockIdx.y == 0 && blockIdx.z == 0;
+#endif
 
     // ---- work item (identical in both CTAs of the pair) ---------------------------
     const int n_row_tiles = (p.R + 127) / 128;
@@ -107,22 +156,26 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
     const int t_begin = (lo / T) * T;
     const int err_now = *reinterpret_cast<volatile int *>(&g_tc_error);
     const bool poisoned = err_now != 0 && err_now != ERR_PAGE;
-    const int n_tiles = (blk_hi > lo && !poisoned) ? (blk_hi - t_begin + T - 1) / T : 0;
+    const int n_sub = (blk_hi > lo && !poisoned) ? (blk_hi - t_begin + SUB - 1) / SUB : 0;   // sub-blocks to attend
+    const int n_tiles = (n_sub + 3) / 4;
 
     // ---- set-up ------------------------------------------------------------------------
     if (threadIdx.x == 0) {
         mbar_init(BAR(B_QFULL), 1);
         mbar_init(BAR(B_PEER_QFULL), 1);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(BAR(B_KVFULL + s), 1);
-            mbar_init(BAR(B_PEER_FULL + s), 1);
-            mbar_init(BAR(B_KVEMPTY + s), 1);
+        for (int s = 0; s < NSLOT; ++s) {
+            mbar_init(BAR(B_FULL + s), 1);
+            mbar_init(BAR(B_PEER + s), 1);
+            mbar_init(BAR(B_EMPTY + s), 1);
         }
-        mbar_init(BAR(B_KVFIX), 1);
-        mbar_init(BAR(B_SFULL + 0), 1);
-        mbar_init(BAR(B_SFULL + 1), 1);
-        mbar_init(BAR(B_PFULL), 2);          // one arrival per CTA of the pair
-        mbar_init(BAR(B_OREADY), 1);
+        mbar_init(BAR(B_FIX), 1);          // zero-filled tail of the j = 0 V slot
+        mbar_init(BAR(B_FIX + 1), 1);      // ... and of the j = 1 V slot (each used once)
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(BAR(B_SFULL + b), 1);
+            mbar_init(BAR(B_SEMPTY + b), 4);     // two key halves in each CTA of the pair
+            mbar_init(BAR(B_OREADY + b), 1);
+        }
+        for (int q = 0; q < 4; ++q) mbar_init(BAR(B_PFULL + q), 2);   // one arrival per CTA
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -136,123 +189,150 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
+    // global row of the first key of sub-block s (pool row for paged caches)
+    auto sub_row = [&](int s, bool *bad_page) -> int {
+        const int t0 = t_begin + s * SUB;
+        if (p.page_table) {
+            const int lp = t0 / p.page_size;
+            int pg = lp < p.max_pages ? p.page_table[(size_t)g * p.max_pages + lp] : -1;
+            if (pg < 0 || pg >= p.num_pages) { *bad_page = true; pg = 0; }
+            return pg * p.page_size + (t0 - lp * p.page_size);
+        }
+        return g * p.Skv + t0;
+    };
+
     if (warp == 0) {
         // =========================== TMA producer (both CTAs) ============================
+        bool bad = false;
         if (n_tiles > 0) {
             if (lane == 0) {
                 prefetch_tmap(&tmQ);
-                prefetch_tmap(&tmK32);
-                prefetch_tmap(&tmK64);
+                prefetch_tmap(&tmK);
                 mbar_arrive_expect_tx(BAR(B_QFULL), Q_BYTES);
                 const int qrow = g * p.R + row0 + 64 * (int)rank;
                 for (int c = 0; c < NQC; ++c)
                     tma_load_2d(smem_u32(sQ + c * Q_CHUNK), &tmQ, c * 64, qrow, BAR(B_QFULL));
             }
-            bool ok = true;
-            for (int t = 0; t < n_tiles; ++t) {
-                const int stage = t % STAGES;
-                if (t >= STAGES) ok = mbar_wait(BAR(B_KVEMPTY + stage), ((t / STAGES) - 1) & 1);
-                if (!ok) { if (lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER); break; }
-                const int t0 = t_begin + t * T;
-                uint8_t *st = sKV + stage * STAGE_BYTES;
-                if (lane == 0) {
-                    long long row;
-                    if (p.page_table) {
-                        const int lp = t0 / p.page_size;
-                        int pg = lp < p.max_pages ? p.page_table[(size_t)g * p.max_pages + lp] : -1;
-                        if (pg < 0 || pg >= p.num_pages) { atomicCAS(&g_tc_error, 0, ERR_PAGE); pg = 0; }
-                        row = (long long)pg * p.page_size + (t0 - lp * p.page_size);
-                    } else {
-                        row = (long long)g * p.Skv + t0;
-                    }
-                    mbar_arrive_expect_tx(BAR(B_KVFULL + stage), STAGE_BYTES);
-                    // own 32 keys, all 576 columns (B operand of Q K^T)
-                    for (int c = 0; c < NQC; ++c)
-                        tma_load_2d(smem_u32(st + c * KA_CHUNK), &tmK32, c * 64, (int)row + 32 * (int)rank,
-                                    BAR(B_KVFULL + stage));
-                    // all 64 keys, own 256 columns of d_v (B operand of P V)
-                    for (int c = 0; c < 4; ++c)
-                        tma_load_2d(smem_u32(st + KA_BYTES + c * VB_CHUNK), &tmK64, 256 * (int)rank + c * 64, (int)row,
-                                    BAR(B_KVFULL + stage));
-                }
-                if (t0 + T > seq) {
-                    // keys past the end of the sequence: zero their V rows once the copy has landed
-                    ok = mbar_wait(BAR(B_KVFULL + stage), (t / STAGES) & 1);
-                    if (!ok) { if (lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER); break; }
-                    const int first_bad = seq > t0 ? seq - t0 : 0;
-                    const int bad_rows = T - first_bad;
-                    for (int idx = lane; idx < 4 * bad_rows * 8; idx += 32) {
-                        const int ch = idx / (bad_rows * 8), rem = idx - ch * bad_rows * 8;
-                        const int r = first_bad + rem / 8, q16 = rem & 7;
-                        *reinterpret_cast<uint4 *>(st + KA_BYTES + ch * VB_CHUNK + r * 128 + q16 * 16) = make_uint4(0, 0, 0, 0);
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(BAR(B_KVFIX));
-                }
-            }
+            // resolve the page table for the whole key range once, with every lane of the warp
+            const int n_cached = n_sub < ROWS_CACHE ? n_sub : ROWS_CACHE;
+            for (int s = lane; s < n_cached; s += 32) s_rows[s] = sub_row(s, &bad);
+            __syncwarp();
         }
+        auto row_of = [&](int s) -> int { return s < ROWS_CACHE ? s_rows[s] : sub_row(s, &bad); };
+        if (n_tiles > 0 && lane == 0) {
+            int n = 0;
+            const bool ok = walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
+                const int slot = n % NSLOT;
+                if (n >= NSLOT && !mbar_wait(BAR(B_EMPTY + slot), ((n / NSLOT) - 1) & 1)) return false;
+                TRACE(0, n);
+                ++n;
+                uint8_t *dst = sRing + slot * SLOT;
+                const uint32_t full = BAR(B_FULL + slot);
+                if (!is_v) {
+                    // K slot: own 128 keys of tile t (two sub-blocks), chunk a of d_qk
+                    const int s0 = 4 * t + 2 * (int)rank;
+                    const int present = (s0 + 1 < n_sub) ? 2 : (s0 < n_sub ? 1 : 0);
+                    mbar_arrive_expect_tx(full, present * BOX);
+                    for (int sb = 0; sb < present; ++sb)
+                        tma_load_2d(smem_u32(dst + sb * BOX), &tmK, a * 64, row_of(s0 + sb), full);
+                } else {
+                    // V slot: the 64 keys of quarter a of tile t, own d_v columns [256 r + 128 j, +128)
+                    const int s = 4 * t + a;
+                    const int row = row_of(s);
+                    mbar_arrive_expect_tx(full, SLOT);
+                    for (int cc = 0; cc < 2; ++cc)
+                        tma_load_2d(smem_u32(dst + cc * BOX), &tmK, 256 * (int)rank + 128 * j + 64 * cc, row, full);
+                    const int t0 = t_begin + s * SUB;
+                    if (t0 + SUB > seq) {
+                        // keys past the end of the sequence: zero their V rows once the copy has
+                        // landed (whole 128-byte rows, so the swizzle does not matter)
+                        if (!mbar_wait(full, ((n - 1) / NSLOT) & 1)) return false;
+                        const int first_bad = seq > t0 ? seq - t0 : 0;
+                        for (int cc = 0; cc < 2; ++cc)
+                            for (int r = first_bad; r < SUB; ++r)
+                                for (int q16 = 0; q16 < 8; ++q16)
+                                    *reinterpret_cast<uint4 *>(dst + cc * BOX + r * 128 + q16 * 16) = make_uint4(0, 0, 0, 0);
+                        fence_proxy_async_smem();
+                        mbar_arrive(BAR(B_FIX + j));  // only the last sub-block can straddle the end
+                    }
+                }
+                return true;
+            });
+            if (!ok) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
+        }
+        if (bad) atomicCAS(&g_tc_error, 0, ERR_PAGE);
+        __syncwarp();
     } else if (warp == 1) {
         if (leader) {
             // =========================== MMA issuer (leader CTA) =========================
             if (lane == 0 && n_tiles > 0) {
-                constexpr uint32_t idesc_qk = make_idesc_bf16(128, T, 0, 0);
+                constexpr uint32_t idesc_qk = make_idesc_bf16(128, 256, 0, 0);
                 constexpr uint32_t idesc_pv = make_idesc_bf16(128, 256, 0, 1);
-                const uint32_t sQ_a = smem_u32(sQ), sKV_a = smem_u32(sKV), sP_a = smem_u32(sP);
+                const uint32_t sQ_a = smem_u32(sQ), sR_a = smem_u32(sRing), sP_a = smem_u32(sP);
                 bool ok = mbar_wait(BAR(B_QFULL), 0) && mbar_wait_cluster(BAR(B_PEER_QFULL), 0);
-                auto issue_qk = [&](int t) -> bool {
-                    const int stage = t % STAGES, b = t & 1;
-                    if (!mbar_wait(BAR(B_KVFULL + stage), (t / STAGES) & 1)) return false;
-                    if (t_begin + t * T + T > seq && !mbar_wait(BAR(B_KVFIX), 0)) return false;
-                    if (!mbar_wait_cluster(BAR(B_PEER_FULL + stage), (t / STAGES) & 1)) return false;
-                    tc_fence_after_sync();
-                    const uint32_t kbase = sKV_a + stage * STAGE_BYTES;
-#pragma unroll
-                    for (int c = 0; c < NQC; ++c) {
+                int n = 0;
+                ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
+                    const int slot = n % NSLOT, ph = (n / NSLOT) & 1;
+                    TRACE(1, n);
+                    ++n;
+                    if (!is_v) {
+                        const int b = t & 1;
+                        // S[b] was last read by the softmax of tile t-2
+                        if (a == 0 && t >= 2 && !mbar_wait_cluster(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
+                        if (!mbar_wait(BAR(B_FULL + slot), ph)) return false;
+                        TRACE(5, n - 1);
+                        if (!mbar_wait_cluster(BAR(B_PEER + slot), ph)) return false;
+                        TRACE(2, n - 1);
+                        tc_fence_after_sync();
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint64_t da = make_smem_desc(sQ_a + c * Q_CHUNK + k * 32, 16, 1024, kLayoutSw128);
-                            const uint64_t db = make_smem_desc(kbase + c * KA_CHUNK + k * 32, 16, 1024, kLayoutSw128);
-                            mma_bf16_ss_2cta(tmem + S_COL0 + b * S_COLS, da, db, idesc_qk, (c | k) != 0);
+                            const uint64_t da = make_smem_desc(sQ_a + a * Q_CHUNK + k * 32, 16, 1024, kLayoutSw128);
+                            const uint64_t db = make_smem_desc(sR_a + slot * SLOT + k * 32, 16, 1024, kLayoutSw128);
+                            mma_bf16_ss_2cta(tmem + S_COL0 + b * S_COLS, da, db, idesc_qk, (a | k) != 0);
                         }
+                        mma_commit_2cta(BAR(B_EMPTY + slot), 3);
+                        if (a == NQC - 1) mma_commit_2cta(BAR(B_SFULL + b), 3);
+                    } else {
+                        if (j == 0 && !mbar_wait_cluster(BAR(B_PFULL + a), t & 1)) return false;
+                        TRACE(4, n - 1);
+                        if (!mbar_wait(BAR(B_FULL + slot), ph)) return false;
+                        if (t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
+                        TRACE(5, n - 1);
+                        if (!mbar_wait_cluster(BAR(B_PEER + slot), ph)) return false;
+                        TRACE(2, n - 1);
+                        tc_fence_after_sync();
+#pragma unroll
+                        for (int ks = 0; ks < SUB / 16; ++ks) {
+                            const uint64_t da = make_smem_desc(sP_a + a * P_Q + ks * 256, 128, P_SBO, kLayoutNone);
+                            const uint64_t db = make_smem_desc(sR_a + slot * SLOT + ks * 2048, BOX, 1024, kLayoutSw128);
+                            mma_bf16_ss_2cta(tmem + j * 128, da, db, idesc_pv, (t | a | ks) != 0);
+                        }
+                        mma_commit_2cta(BAR(B_EMPTY + slot), 3);
+                        const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
+                        if (j == 1 && a == nq - 1) mma_commit_2cta(BAR(B_OREADY + (t & 1)), 3);   // tile t folded into O
                     }
-                    mma_commit_2cta(BAR(B_SFULL + b), 3);
                     return true;
-                };
-                if (ok) ok = issue_qk(0);
-                for (int t = 0; t < n_tiles && ok; ++t) {
-                    if (t + 1 < n_tiles) ok = issue_qk(t + 1);
-                    if (!ok) break;
-                    ok = mbar_wait_cluster(BAR(B_PFULL), t & 1);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    const int stage = t % STAGES;
-                    const uint32_t vbase = sKV_a + stage * STAGE_BYTES + KA_BYTES;
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                        for (int ks = 0; ks < T / 16; ++ks) {
-                            const uint64_t da = make_smem_desc(sP_a + ks * 256, 128, P_SBO, kLayoutNone);
-                            const uint64_t db = make_smem_desc(vbase + j * 2 * VB_CHUNK + ks * 2048, VB_CHUNK, 1024, kLayoutSw128);
-                            mma_bf16_ss_2cta(tmem + j * 128, da, db, idesc_pv, (t | ks) != 0);
-                        }
-                    }
-                    mma_commit_2cta(BAR(B_KVEMPTY + stage), 3);
-                    mma_commit_2cta(BAR(B_OREADY), 3);
-                }
+                });
                 if (!ok) atomicCAS(&g_tc_error, 0, ERR_MMA);
             }
         } else {
             // =========================== load relay (peer CTA) ===========================
             if (lane == 0 && n_tiles > 0) {
                 bool ok = mbar_wait(BAR(B_QFULL), 0);
-                if (ok) mbar_arrive_cluster(map_to_cta(BAR(B_PEER_QFULL), 0));
-                for (int t = 0; t < n_tiles && ok; ++t) {
-                    const int stage = t % STAGES;
-                    ok = mbar_wait(BAR(B_KVFULL + stage), (t / STAGES) & 1);
-                    if (ok && t_begin + t * T + T > seq) ok = mbar_wait(BAR(B_KVFIX), 0);
-                    if (ok) mbar_arrive_cluster(map_to_cta(BAR(B_PEER_FULL + stage), 0));
-                }
+                if (ok) mbar_arrive_cluster_relaxed(map_to_cta(BAR(B_PEER_QFULL), 0));
+                const uint32_t peer_base = map_to_cta(BAR(B_PEER), 0);
+                int n = 0;
+                ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
+                    const int slot = n % NSLOT, ph = (n / NSLOT) & 1;
+                    ++n;
+                    TRACE(5, n - 1);
+                    if (!mbar_wait(BAR(B_FULL + slot), ph)) return false;
+                    TRACE(1, n - 1);
+                    if (is_v && t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
+                    mbar_arrive_cluster_relaxed(peer_base + 8u * slot);
+                    TRACE(2, n - 1);
+                    return true;
+                });
                 if (!ok) atomicCAS(&g_tc_error, 0, ERR_RELAY);
             }
         }
@@ -260,7 +340,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
     } else {
         // =========================== softmax + epilogue (both CTAs) ========================
         const int L = (warp & 3) * 32 + lane;          // TMEM lane owned by this thread
-        const int row = L & 63, half = L >> 6;
+        const int row = L & 63, half = L >> 6;         // key half: keys [128 half, +128) of every tile
         const int rr = row0 + 64 * (int)rank + row;
         const bool row_ok = rr < p.R;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -277,32 +357,41 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
         const float sl2 = p.scale * 1.4426950408889634f;
         float m_true = -CUDART_INF_F, m_ref = -CUDART_INF_F, l_run = 0.f;   // l_run: this thread's key half only
         const uint32_t pfull_leader = map_to_cta(BAR(B_PFULL), 0);
+        const uint32_t sempty_leader = map_to_cta(BAR(B_SEMPTY), 0);
         bool ok = true;
         uint32_t r[32];
         for (int t = 0; t < n_tiles; ++t) {
-            const int b = t & 1, tok0 = t_begin + t * T + 32 * half;
+            const int b = t & 1, tok0 = t_begin + t * T + 128 * half;
+            const uint32_t s_addr = tmem + lane_base + S_COL0 + b * S_COLS;
             // after a failed wait the loop keeps running without further waits so that the
-            // named barriers below stay matched across the 128 softmax threads
+            // named barriers below stay matched across the softmax threads
+            if (L == 0) TRACE(3, t * 8 + 0);
             if (ok) ok = mbar_wait(BAR(B_SFULL + b), (t / 2) & 1);
+            if (L == 0) TRACE(3, t * 8 + 1);
             tc_fence_after_sync();
-            tmem_ld32(tmem + lane_base + S_COL0 + b * S_COLS, r);
-            tmem_wait_ld();
+            // pass 1: maximum of this thread's 128 keys
             float tmax = -CUDART_INF_F;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                tmem_ld32(s_addr + cc * 32, r);
+                tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int tok = tok0 + j;
-                const float v = (tok >= lo && tok < upper) ? __uint_as_float(r[j]) * sl2 : -CUDART_INF_F;
-                r[j] = __float_as_uint(v);
-                tmax = fmaxf(tmax, v);
+                for (int j = 0; j < 32; ++j) {
+                    const int tok = tok0 + cc * 32 + j;
+                    const float v = (tok >= lo && tok < upper) ? __uint_as_float(r[j]) * sl2 : -CUDART_INF_F;
+                    tmax = fmaxf(tmax, v);
+                }
             }
             // the row's other key half lives in the thread 64 lanes away
             red[(t & 1) * 128 + L] = tmax;
             named_bar_sync(1, 128);
+            if (L == 0) TRACE(3, t * 8 + 2);
             tmax = fmaxf(tmax, red[(t & 1) * 128 + (L ^ 64)]);
             const float m_new = fmaxf(m_true, tmax);
             const bool need = m_new > m_ref + 8.f;
+            // P*V of tile t-1 must be complete before its P is overwritten or O rescaled
             if (t > 0) {
-                if (ok) ok = mbar_wait(BAR(B_OREADY), (t - 1) & 1);
+                if (ok) ok = mbar_wait(BAR(B_OREADY + ((t - 1) & 1)), ((t - 1) / 2) & 1);
                 tc_fence_after_sync();
             }
             if (__any_sync(0xffffffffu, need)) {
@@ -326,37 +415,52 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
                 }
             }
             m_true = m_new;
+            if (L == 0) TRACE(3, t * 8 + 3);
+            // pass 2: P = 2^(s - m_ref), quarter by quarter (this half owns quarters 2*half, 2*half+1)
             float lsum = 0.f;
-            uint32_t packed[16];
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                tmem_ld32(s_addr + cc * 32, r);
+                tmem_wait_ld();
+                uint32_t packed[16];
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                const float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
-                const float p0 = (v0 == -CUDART_INF_F) ? 0.f : fast_exp2(v0 - m_ref);
-                const float p1 = (v1 == -CUDART_INF_F) ? 0.f : fast_exp2(v1 - m_ref);
-                lsum += p0 + p1;
-                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                for (int j = 0; j < 32; j += 2) {
+                    const int tok = tok0 + cc * 32 + j;
+                    const float p0 = (tok >= lo && tok < upper) ? fast_exp2(__uint_as_float(r[j]) * sl2 - m_ref) : 0.f;
+                    const float p1 = (tok + 1 >= lo && tok + 1 < upper) ? fast_exp2(__uint_as_float(r[j + 1]) * sl2 - m_ref) : 0.f;
+                    lsum += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                }
+                const int quarter = 2 * half + (cc >> 1);
+                uint8_t *prow = sP + quarter * P_Q + (row >> 3) * P_SBO + (row & 7) * 16 + (cc & 1) * 4 * 128;
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc)
+                    *reinterpret_cast<uint4 *>(prow + kc * 128) =
+                        make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
+                if (cc & 1) {
+                    // quarter complete in this CTA once the 64 threads of this key half have written it
+                    tc_fence_before_sync();
+                    fence_proxy_async_smem();
+                    named_bar_sync(2 + half, 64);
+                    if (L == 0) TRACE(3, t * 8 + 4 + (cc >> 1));
+                    if (row == 0) {
+                        mbar_arrive_cluster(pfull_leader + 8u * quarter);
+                        if (cc == 3) mbar_arrive_cluster(sempty_leader + 8u * b);   // this half is done with S[b]
+                    }
+                }
             }
             l_run += lsum;
-            uint8_t *prow = sP + (row >> 3) * P_SBO + (row & 7) * 16 + half * 4 * 128;
-#pragma unroll
-            for (int kc = 0; kc < 4; ++kc)
-                *reinterpret_cast<uint4 *>(prow + kc * 128) =
-                    make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
-            tc_fence_before_sync();
-            fence_proxy_async_smem();
-            named_bar_sync(2, 128);
-            if (L == 0) mbar_arrive_cluster(pfull_leader);
         }
         if (ok && n_tiles > 0) {
-            ok = mbar_wait(BAR(B_OREADY), (n_tiles - 1) & 1);
+            ok = mbar_wait(BAR(B_OREADY + ((n_tiles - 1) & 1)), ((n_tiles - 1) / 2) & 1);
             tc_fence_after_sync();
         }
         if (!ok) atomicCAS(&g_tc_error, 0, ERR_SOFTMAX);
         // row sum = both key halves
         named_bar_sync(1, 128);
         red[L] = l_run;
-        named_bar_sync(2, 128);
+        named_bar_sync(1, 128);
         const float l_tot = l_run + red[L ^ 64];
         // ---- epilogue: thread L writes row `row`, d_v columns [256*half, 256*half + 256) ----
         const bool have = ok && n_tiles > 0 && l_tot > 0.f;
@@ -420,10 +524,18 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
 // --------------------------------------------------------------------------------------
 // Host side
 // --------------------------------------------------------------------------------------
+#ifdef FDMLA_TRACE
+extern "C" int fdmla_trace_fetch(long long *dst, int max_elems) {
+    const int n = 2 * 6 * tc2::TR_N;
+    if (max_elems < n) return -n;
+    return cudaMemcpyFromSymbol(dst, tc2::g_trace, sizeof(long long) * n) == cudaSuccess ? n : -1;
+}
+#endif
+
 bool fwd_tensor2_supported(const FwdProblem &p, int dtype) {
     if (dtype != FDMLA_BF16) return false;
     if (p.d_qk != 576 || p.d_v != 512 || p.V != nullptr) return false;
-    if (p.page_table && (p.page_size % tc2::T) != 0) return false;
+    if (p.page_table && (p.page_size % tc2::SUB) != 0) return false;
     if (p.G <= 0 || p.R <= 0 || p.G > 65535 || p.num_splits > 65535) return false;
     const long long kv_rows = p.page_table ? (long long)p.num_pages * p.page_size : (long long)p.G * p.Skv;
     if (kv_rows <= 0 || kv_rows > 2147483647LL || (long long)p.G * p.R > 2147483647LL) return false;
@@ -433,15 +545,14 @@ bool fwd_tensor2_supported(const FwdProblem &p, int dtype) {
 }
 
 int launch_fwd_tensor2(const FwdProblem &p, cudaStream_t stream) {
-    CUtensorMap tmQ, tmK32, tmK64;
+    CUtensorMap tmQ, tmK;
     const long long kv_rows = p.page_table ? (long long)p.num_pages * p.page_size : (long long)p.G * p.Skv;
     if (!make_tensor_map_bf16(&tmQ, p.Q, (long long)p.G * p.R, p.d_qk, 64)) return FDMLA_ERR_CUDA;
-    if (!make_tensor_map_bf16(&tmK32, p.K, kv_rows, p.d_qk, 32)) return FDMLA_ERR_CUDA;
-    if (!make_tensor_map_bf16(&tmK64, p.K, kv_rows, p.d_qk, 64)) return FDMLA_ERR_CUDA;
+    if (!make_tensor_map_bf16(&tmK, p.K, kv_rows, p.d_qk, 64)) return FDMLA_ERR_CUDA;
     if (cudaFuncSetAttribute(tc2::fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES) != cudaSuccess)
         return FDMLA_ERR_CUDA;
     dim3 grid(((p.R + 127) / 128) * 2, p.G, p.num_splits);
-    tc2::fwd_tc2_kernel<<<grid, tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK32, tmK64);
+    tc2::fwd_tc2_kernel<<<grid, tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK);
     return check_launch();
 }
 
