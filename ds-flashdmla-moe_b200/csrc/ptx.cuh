@@ -62,6 +62,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// Same for waits that are not latency critical (a producer waiting for a free ring slot):
+// backs off between polls so the spinning thread does not take issue slots from the
+// warps doing the work.
+__device__ __forceinline__ bool mbar_wait_relaxed_pace(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(64);
+    }
+    return false;
+}
 
 // ---- fences -------------------------------------------------------------------
 // generic-proxy shared-memory writes -> visible to the async proxy (TMA / tcgen05.mma)

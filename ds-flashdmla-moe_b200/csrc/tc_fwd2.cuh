@@ -86,6 +86,28 @@ __device__ long long g_trace[2][6][TR_N];
 #define TRACE(stream, idx) do { } while (0)
 #endif
 
+// Four consecutive K=16 steps of one 2-CTA MMA: descriptors advance by a_step / b_step (in
+// 16-byte units of the start-address field) per step.  acc0 == 0 makes the first step overwrite D.
+__device__ __forceinline__ void mma4_2cta(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t a_step,
+                                          uint32_t b_step, uint32_t idesc, uint32_t acc0) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 sa, sb, a1, a2, a3, b1, b2, b3;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "cvt.u64.u32 sa, %3;\n"
+        "cvt.u64.u32 sb, %4;\n"
+        "add.s64 a1, %1, sa;\n add.s64 a2, a1, sa;\n add.s64 a3, a2, sa;\n"
+        "add.s64 b1, %2, sb;\n add.s64 b2, b1, sb;\n add.s64 b3, b2, sb;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %5, p;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a1, b1, %5, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a2, b2, %5, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a3, b3, %5, 1;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(a_step), "r"(b_step), "r"(idesc), "r"(acc0)
+        : "memory");
+}
+
 // The one order in which ring slots are filled and consumed.  `f(is_v, t, a, b)` is
 // called for a K slot as (false, tile, chunk, 0) and for a V slot as (true, tile, quarter,
 // half j); it returns false to stop.  n_sub = number of 64-key sub-blocks to attend.
@@ -164,8 +186,8 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         mbar_init(BAR(B_QFULL), 1);
         mbar_init(BAR(B_PEER_QFULL), 1);
         for (int s = 0; s < NSLOT; ++s) {
-            mbar_init(BAR(B_FULL + s), 1);
-            mbar_init(BAR(B_PEER + s), 1);
+            mbar_init(BAR(B_FULL + s), leader ? 2 : 1);   // leader: own copy + the peer's "landed" arrival
+            mbar_init(BAR(B_PEER + s), 1);               // (unused)
             mbar_init(BAR(B_EMPTY + s), 1);
         }
         mbar_init(BAR(B_FIX), 1);          // zero-filled tail of the j = 0 V slot
@@ -223,7 +245,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             int n = 0;
             const bool ok = walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
                 const int slot = n % NSLOT;
-                if (n >= NSLOT && !mbar_wait(BAR(B_EMPTY + slot), ((n / NSLOT) - 1) & 1)) return false;
+                if (n >= NSLOT && !mbar_wait_relaxed_pace(BAR(B_EMPTY + slot), ((n / NSLOT) - 1) & 1)) return false;
                 TRACE(0, n);
                 ++n;
                 uint8_t *dst = sRing + slot * SLOT;
@@ -265,52 +287,44 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     } else if (warp == 1) {
         if (leader) {
             // =========================== MMA issuer (leader CTA) =========================
+            // One thread issues everything, so the loop is kept short: descriptors are a base
+            // plus a small add, the ring position is a counter with wrap-around, and each slot
+            // costs one barrier wait, four MMAs and one commit.
             if (lane == 0 && n_tiles > 0) {
                 constexpr uint32_t idesc_qk = make_idesc_bf16(128, 256, 0, 0);
                 constexpr uint32_t idesc_pv = make_idesc_bf16(128, 256, 0, 1);
-                const uint32_t sQ_a = smem_u32(sQ), sR_a = smem_u32(sRing), sP_a = smem_u32(sP);
-                bool ok = mbar_wait(BAR(B_QFULL), 0) && mbar_wait_cluster(BAR(B_PEER_QFULL), 0);
-                int n = 0;
+                const uint64_t q_desc = make_smem_desc(smem_u32(sQ), 16, 1024, kLayoutSw128);
+                const uint64_t rk_desc = make_smem_desc(smem_u32(sRing), 16, 1024, kLayoutSw128);    // ring slot as K-major B
+                const uint64_t rv_desc = make_smem_desc(smem_u32(sRing), BOX, 1024, kLayoutSw128);   // ring slot as MN-major B
+                const uint64_t p_desc = make_smem_desc(smem_u32(sP), 128, P_SBO, kLayoutNone);
+                bool ok = mbar_wait(BAR(B_QFULL), 0) && mbar_wait(BAR(B_PEER_QFULL), 0);
+                int slot = 0;
+                uint32_t ph = 0;
                 ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                    const int slot = n % NSLOT, ph = (n / NSLOT) & 1;
-                    TRACE(1, n);
-                    ++n;
+                    const uint32_t full = BAR(B_FULL + slot), empty = BAR(B_EMPTY + slot);
+                    const uint32_t slot_off = (uint32_t)slot * (SLOT >> 4);
                     if (!is_v) {
                         const int b = t & 1;
                         // S[b] was last read by the softmax of tile t-2
-                        if (a == 0 && t >= 2 && !mbar_wait_cluster(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
-                        if (!mbar_wait(BAR(B_FULL + slot), ph)) return false;
-                        TRACE(5, n - 1);
-                        if (!mbar_wait_cluster(BAR(B_PEER + slot), ph)) return false;
-                        TRACE(2, n - 1);
+                        if (a == 0 && t >= 2 && !mbar_wait(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
+                        if (!mbar_wait(full, ph)) return false;
                         tc_fence_after_sync();
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint64_t da = make_smem_desc(sQ_a + a * Q_CHUNK + k * 32, 16, 1024, kLayoutSw128);
-                            const uint64_t db = make_smem_desc(sR_a + slot * SLOT + k * 32, 16, 1024, kLayoutSw128);
-                            mma_bf16_ss_2cta(tmem + S_COL0 + b * S_COLS, da, db, idesc_qk, (a | k) != 0);
-                        }
-                        mma_commit_2cta(BAR(B_EMPTY + slot), 3);
+                        mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)a * (Q_CHUNK >> 4), rk_desc + slot_off, 2, 2,
+                                  idesc_qk, a != 0);
+                        mma_commit_2cta(empty, 3);
                         if (a == NQC - 1) mma_commit_2cta(BAR(B_SFULL + b), 3);
                     } else {
-                        if (j == 0 && !mbar_wait_cluster(BAR(B_PFULL + a), t & 1)) return false;
-                        TRACE(4, n - 1);
-                        if (!mbar_wait(BAR(B_FULL + slot), ph)) return false;
+                        if (j == 0 && !mbar_wait(BAR(B_PFULL + a), t & 1)) return false;
+                        if (!mbar_wait(full, ph)) return false;
                         if (t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
-                        TRACE(5, n - 1);
-                        if (!mbar_wait_cluster(BAR(B_PEER + slot), ph)) return false;
-                        TRACE(2, n - 1);
                         tc_fence_after_sync();
-#pragma unroll
-                        for (int ks = 0; ks < SUB / 16; ++ks) {
-                            const uint64_t da = make_smem_desc(sP_a + a * P_Q + ks * 256, 128, P_SBO, kLayoutNone);
-                            const uint64_t db = make_smem_desc(sR_a + slot * SLOT + ks * 2048, BOX, 1024, kLayoutSw128);
-                            mma_bf16_ss_2cta(tmem + j * 128, da, db, idesc_pv, (t | a | ks) != 0);
-                        }
-                        mma_commit_2cta(BAR(B_EMPTY + slot), 3);
+                        mma4_2cta(tmem + j * 128, p_desc + (uint32_t)a * (P_Q >> 4), rv_desc + slot_off, 16, 128, idesc_pv,
+                                  (t | a) != 0);
+                        mma_commit_2cta(empty, 3);
                         const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
                         if (j == 1 && a == nq - 1) mma_commit_2cta(BAR(B_OREADY + (t & 1)), 3);   // tile t folded into O
                     }
+                    if (++slot == NSLOT) { slot = 0; ph ^= 1; }
                     return true;
                 });
                 if (!ok) atomicCAS(&g_tc_error, 0, ERR_MMA);
@@ -320,7 +334,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             if (lane == 0 && n_tiles > 0) {
                 bool ok = mbar_wait(BAR(B_QFULL), 0);
                 if (ok) mbar_arrive_cluster_relaxed(map_to_cta(BAR(B_PEER_QFULL), 0));
-                const uint32_t peer_base = map_to_cta(BAR(B_PEER), 0);
+                const uint32_t peer_base = map_to_cta(BAR(B_FULL), 0);
                 int n = 0;
                 ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
                     const int slot = n % NSLOT, ph = (n / NSLOT) & 1;
@@ -369,19 +383,25 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             if (ok) ok = mbar_wait(BAR(B_SFULL + b), (t / 2) & 1);
             if (L == 0) TRACE(3, t * 8 + 1);
             tc_fence_after_sync();
-            // pass 1: maximum of this thread's 128 keys
+            // pass 1: maximum of this thread's 128 keys (no per-key masking when all are visible)
+            const bool all_visible = tok0 >= lo && tok0 + 128 <= upper && sl2 > 0.f;
             float tmax = -CUDART_INF_F;
 #pragma unroll 1
             for (int cc = 0; cc < 4; ++cc) {
                 tmem_ld32(s_addr + cc * 32, r);
                 tmem_wait_ld();
+                if (all_visible) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int tok = tok0 + cc * 32 + j;
-                    const float v = (tok >= lo && tok < upper) ? __uint_as_float(r[j]) * sl2 : -CUDART_INF_F;
-                    tmax = fmaxf(tmax, v);
+                    for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(r[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = tok0 + cc * 32 + j;
+                        if (tok >= lo && tok < upper) tmax = fmaxf(tmax, __uint_as_float(r[j]) * sl2);
+                    }
                 }
             }
+            if (all_visible) tmax *= sl2;     // fast path took the maximum of the raw scores (sl2 > 0)
             // the row's other key half lives in the thread 64 lanes away
             red[(t & 1) * 128 + L] = tmax;
             named_bar_sync(1, 128);
@@ -423,14 +443,25 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 tmem_ld32(s_addr + cc * 32, r);
                 tmem_wait_ld();
                 uint32_t packed[16];
+                if (all_visible) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int tok = tok0 + cc * 32 + j;
-                    const float p0 = (tok >= lo && tok < upper) ? fast_exp2(__uint_as_float(r[j]) * sl2 - m_ref) : 0.f;
-                    const float p1 = (tok + 1 >= lo && tok + 1 < upper) ? fast_exp2(__uint_as_float(r[j + 1]) * sl2 - m_ref) : 0.f;
-                    lsum += p0 + p1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                    for (int j = 0; j < 32; j += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_ref));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), sl2, -m_ref));
+                        lsum += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const int tok = tok0 + cc * 32 + j;
+                        const float p0 = (tok >= lo && tok < upper) ? fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_ref)) : 0.f;
+                        const float p1 = (tok + 1 >= lo && tok + 1 < upper) ? fast_exp2(fmaf(__uint_as_float(r[j + 1]), sl2, -m_ref)) : 0.f;
+                        lsum += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                    }
                 }
                 const int quarter = 2 * half + (cc >> 1);
                 uint8_t *prow = sP + quarter * P_Q + (row >> 3) * P_SBO + (row & 7) * 16 + (cc & 1) * 4 * 128;
@@ -445,8 +476,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     named_bar_sync(2 + half, 64);
                     if (L == 0) TRACE(3, t * 8 + 4 + (cc >> 1));
                     if (row == 0) {
-                        mbar_arrive_cluster(pfull_leader + 8u * quarter);
-                        if (cc == 3) mbar_arrive_cluster(sempty_leader + 8u * b);   // this half is done with S[b]
+                        // (relaxed: the 64 writers have fenced their stores towards the async proxy and
+                        // met at the named barrier; the arrival itself carries no data)
+                        mbar_arrive_cluster_relaxed(pfull_leader + 8u * quarter);
+                        if (cc == 3) mbar_arrive_cluster_relaxed(sempty_leader + 8u * b);   // this half is done with S[b]
                     }
                 }
             }
