@@ -300,24 +300,38 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 bool ok = mbar_wait(BAR(B_QFULL), 0) && mbar_wait(BAR(B_PEER_QFULL), 0);
                 int slot = 0;
                 uint32_t ph = 0;
+#ifdef FDMLA_TRACE
+                int ntrace = 0;
+#endif
                 ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
                     const uint32_t full = BAR(B_FULL + slot), empty = BAR(B_EMPTY + slot);
                     const uint32_t slot_off = (uint32_t)slot * (SLOT >> 4);
+#ifdef FDMLA_TRACE
+                    const int n = ntrace++;
+#endif
+                    TRACE(1, n);
                     if (!is_v) {
                         const int b = t & 1;
                         // S[b] was last read by the softmax of tile t-2
-                        if (a == 0 && t >= 2 && !mbar_wait(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
+                        if (a == 0) {
+                            if (t >= 2 && !mbar_wait(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
+                            tc_fence_after_sync();      // orders this tile's writes of S[b] after the softmax's reads
+                        }
                         if (!mbar_wait(full, ph)) return false;
-                        tc_fence_after_sync();
+                        TRACE(2, n);
                         mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)a * (Q_CHUNK >> 4), rk_desc + slot_off, 2, 2,
                                   idesc_qk, a != 0);
                         mma_commit_2cta(empty, 3);
                         if (a == NQC - 1) mma_commit_2cta(BAR(B_SFULL + b), 3);
                     } else {
-                        if (j == 0 && !mbar_wait(BAR(B_PFULL + a), t & 1)) return false;
+                        if (j == 0) {
+                            if (!mbar_wait(BAR(B_PFULL + a), t & 1)) return false;
+                            tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
+                        }
+                        TRACE(4, n);
                         if (!mbar_wait(full, ph)) return false;
+                        TRACE(2, n);
                         if (t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
-                        tc_fence_after_sync();
                         mma4_2cta(tmem + j * 128, p_desc + (uint32_t)a * (P_Q >> 4), rv_desc + slot_off, 16, 128, idesc_pv,
                                   (t | a) != 0);
                         mma_commit_2cta(empty, 3);
