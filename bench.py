@@ -54,6 +54,12 @@ def set_batch(b: int) -> None:
     DECODE_FLOP = 2 * B * H * SKV * (D_QK + D_V)
 
 
+def set_prefill_shape(b: int, h: int, s: int) -> None:
+    global PF_B, PF_H, PF_S, PREFILL_FLOP_CAUSAL
+    PF_B, PF_H, PF_S = b, h, s
+    PREFILL_FLOP_CAUSAL = 2 * PF_B * PF_H * (PF_S * (PF_S + 1) // 2) * (D_QK + D_V)
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -205,12 +211,17 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary causal-prefill measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--splits", type=int, default=0, help="override the decode split count (0 = library choice)")
+    ap.add_argument("--prefill-shape", default="",
+                    help="B,H,S of the prefill measurement (default 4,128,8192); a reduced shape is used for ncu captures")
+    ap.add_argument("--only-prefill", action="store_true", help="run only the prefill measurement (profiling aid)")
     ap.add_argument("--batch", type=int, default=0,
                     help="decode sequences per GPU (default 128); smaller values give the reduced case used for ncu captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.batch:
         set_batch(args.batch)
+    if args.prefill_shape:
+        set_prefill_shape(*[int(x) for x in args.prefill_shape.split(",")])
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -230,6 +241,13 @@ def main():
     from flashdmla import _lib
 
     hbm_peak, tf_burst, tf_sust, peak_src = peaks()
+    if args.only_prefill:
+        pf = bench_prefill(dev, rank, world, tf_burst)
+        if rank == 0:
+            print(json.dumps({"prefill": pf, "device_error_flag": flashdmla.device_error_flag()}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     Q, pool, table, seqlens = make_decode_inputs(dev, seed=1000 + rank)
     splits = args.splits or flashdmla.suggest_splits(B, H, SKV, D_QK, D_V, PAGE)
     ws = flashdmla.DecodeWorkspace()
@@ -329,7 +347,7 @@ def bench_prefill(dev, rank, world, tf_peak, iters=3):
         return flashdmla.flash_dmla_cache_latent(Q, K, D_V, SCALE, True)
     ms = time_steps(step, iters, 1, world) / iters
     tflops = PREFILL_FLOP_CAUSAL / (ms * 1e-3) / 1e12
-    return {"workload": "causal prefill B=4 H=128 S=8192 d=576/512, heads sharded", "ms": ms, "tflops_total": tflops,
+    return {"workload": f"causal prefill B={PF_B} H={PF_H} S={PF_S} d=576/512, heads sharded", "ms": ms, "tflops_total": tflops,
             "tflops_per_gpu": tflops / world, "frac_of_measured_bf16_peak": tflops / world / tf_peak,
             "frac_of_2250_spec": tflops / world / 2250.0, "kernel_family": flashdmla.last_kernel(),
             "tokens_per_s": PF_B * PF_S / (ms * 1e-3)}

@@ -143,21 +143,26 @@ int fdmla_fwd_on_the_fly(const void *Q, const void *K, const void *V, const void
 
 int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v, int page_size,
                                 int dtype) {
-    (void)d_qk; (void)dtype;
     if (B <= 0 || H <= 0 || max_seqlen <= 0 || page_size <= 0) return 1;
+    // Cost model in units of one key tile of one work item.  The tcgen05 kernels run one
+    // work item (128 rows x one split) per cluster of two CTAs in 256-key tiles, the other
+    // kernels one 128-row item per CTA in 32-key tiles; each item pays a fixed cost of
+    // about 1.5 tiles (Q load, pipeline fill, epilogue) and every split beyond the first
+    // adds partial results that have to be written, read back and merged.
+    const bool mla = (dtype == FDMLA_BF16 && d_qk == 576 && d_v == 512 && page_size % 64 == 0);
+    const int tile = mla ? 256 : 32;
+    const int units = mla ? kNumSMs / 2 : kNumSMs;
+    const long long items = (long long)B * ((H + 127) / 128) * ((mla || d_v <= 256) ? 1 : 2);
+    const double tiles = (double)((max_seqlen + tile - 1) / tile);
     const int pages = (max_seqlen + page_size - 1) / page_size;
-    // thread blocks per split: tcgen05 path uses 128-row tiles x d_v halves
-    long long per_split = (long long)B * ((H + 127) / 128) * (d_v > 256 ? 2 : 1);
     int best = 1;
-    double best_eff = 0.0;
-    for (int s = 1; s <= 32 && s <= pages; ++s) {
-        long long blocks = per_split * s;
-        long long waves = (blocks + kNumSMs - 1) / kNumSMs;
-        double eff = (double)blocks / (double)(waves * kNumSMs);
-        // each split adds a partial write + merge read; prefer fewer splits on ties
-        eff -= 0.004 * s;
-        if ((pages / s) < 4) break;
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+    double best_cost = 1e30;
+    const int s_max = (int)tiles < pages ? (int)tiles : pages;      // never less than one tile per split
+    for (int s = 1; s <= 64 && s <= s_max; ++s) {
+        const long long waves = (items * s + units - 1) / units;
+        double cost = (double)waves * (tiles / s + 1.5);
+        if (s > 1) cost += 0.75 + 0.02 * s * (double)waves;   // merge launch + partial traffic
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
     return best;
 }

@@ -133,6 +133,14 @@ __device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
     return true;
 }
 
+// Ring positions are static: chunk c of any K tile uses K slot c % 3 (three uses per tile),
+// V (quarter q, half j) uses V slot 3 + (2q + j) % 4 (two uses per tile).  The k-th use of a
+// slot completes phase k of its barriers.
+__device__ __forceinline__ int k_slot(int c) { return c % 3; }
+__device__ __forceinline__ int v_slot(int q, int j) { return 3 + ((2 * q + j) & 3); }
+__device__ __forceinline__ int k_use(int t, int c) { return 3 * t + c / 3; }
+__device__ __forceinline__ int v_use(int t, int q) { return 2 * t + (q >> 1); }
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK) {
     using namespace ptx;
@@ -165,7 +173,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     const int w_lo = p.kv_begin > 0 ? p.kv_begin : 0;
     const int w_hi = (p.kv_end >= 0 && p.kv_end < seq) ? p.kv_end : seq;
     int lo, hi;
-    split_window(w_lo, w_hi, p.page_table ? p.page_size : T, split, p.num_splits, &lo, &hi);
+    // splits are cut on tile boundaries where the page size allows it
+    const int gran = (p.page_table && (T % p.page_size) != 0) ? p.page_size : T;
+    split_window(w_lo, w_hi, gran, split, p.num_splits, &lo, &hi);
     const int rows_here = (p.R - row0) < 128 ? (p.R - row0) : 128;
     int blk_vis = seq;
     if (p.causal) {
@@ -242,12 +252,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         }
         auto row_of = [&](int s) -> int { return s < ROWS_CACHE ? s_rows[s] : sub_row(s, &bad); };
         if (n_tiles > 0 && lane == 0) {
-            int n = 0;
             const bool ok = walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                const int slot = n % NSLOT;
-                if (n >= NSLOT && !mbar_wait_relaxed_pace(BAR(B_EMPTY + slot), ((n / NSLOT) - 1) & 1)) return false;
-                TRACE(0, n);
-                ++n;
+                const int slot = is_v ? v_slot(a, j) : k_slot(a);
+                const int use = is_v ? v_use(t, a) : k_use(t, a);
+                if (use >= 1 && !mbar_wait_relaxed_pace(BAR(B_EMPTY + slot), (use - 1) & 1)) return false;
                 uint8_t *dst = sRing + slot * SLOT;
                 const uint32_t full = BAR(B_FULL + slot);
                 if (!is_v) {
@@ -268,7 +276,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     if (t0 + SUB > seq) {
                         // keys past the end of the sequence: zero their V rows once the copy has
                         // landed (whole 128-byte rows, so the swizzle does not matter)
-                        if (!mbar_wait(full, ((n - 1) / NSLOT) & 1)) return false;
+                        if (!mbar_wait(full, use & 1)) return false;
                         const int first_bad = seq > t0 ? seq - t0 : 0;
                         for (int cc = 0; cc < 2; ++cc)
                             for (int r = first_bad; r < SUB; ++r)
@@ -287,10 +295,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     } else if (warp == 1) {
         if (leader) {
             // =========================== MMA issuer (leader CTA) =========================
-            // One thread issues everything, so the loop is kept short: descriptors are a base
-            // plus a small add, the ring position is a counter with wrap-around, and each slot
-            // costs one barrier wait, four MMAs and one commit.
-            if (lane == 0 && n_tiles > 0) {
+            // The whole warp runs this loop converged and one elected lane issues: that keeps the
+            // descriptor arithmetic on the uniform datapath, which is what lets tcgen05.mma issue at
+            // full rate (a single diverged lane issuing the same sequence is about half as fast).
+            // Ring positions are static, so a tile unrolls into straight-line code.
+            if (n_tiles > 0) {
+                const bool elected = elect_one();
                 constexpr uint32_t idesc_qk = make_idesc_bf16(128, 256, 0, 0);
                 constexpr uint32_t idesc_pv = make_idesc_bf16(128, 256, 0, 1);
                 const uint64_t q_desc = make_smem_desc(smem_u32(sQ), 16, 1024, kLayoutSw128);
@@ -298,50 +308,60 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 const uint64_t rv_desc = make_smem_desc(smem_u32(sRing), BOX, 1024, kLayoutSw128);   // ring slot as MN-major B
                 const uint64_t p_desc = make_smem_desc(smem_u32(sP), 128, P_SBO, kLayoutNone);
                 bool ok = mbar_wait(BAR(B_QFULL), 0) && mbar_wait(BAR(B_PEER_QFULL), 0);
-                int slot = 0;
-                uint32_t ph = 0;
-#ifdef FDMLA_TRACE
-                int ntrace = 0;
-#endif
-                ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                    const uint32_t full = BAR(B_FULL + slot), empty = BAR(B_EMPTY + slot);
-                    const uint32_t slot_off = (uint32_t)slot * (SLOT >> 4);
-#ifdef FDMLA_TRACE
-                    const int n = ntrace++;
-#endif
-                    TRACE(1, n);
-                    if (!is_v) {
-                        const int b = t & 1;
-                        // S[b] was last read by the softmax of tile t-2
-                        if (a == 0) {
-                            if (t >= 2 && !mbar_wait(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
-                            tc_fence_after_sync();      // orders this tile's writes of S[b] after the softmax's reads
-                        }
-                        if (!mbar_wait(full, ph)) return false;
-                        TRACE(2, n);
-                        mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)a * (Q_CHUNK >> 4), rk_desc + slot_off, 2, 2,
-                                  idesc_qk, a != 0);
-                        mma_commit_2cta(empty, 3);
-                        if (a == NQC - 1) mma_commit_2cta(BAR(B_SFULL + b), 3);
-                    } else {
-                        if (j == 0) {
-                            if (!mbar_wait(BAR(B_PFULL + a), t & 1)) return false;
-                            tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
-                        }
-                        TRACE(4, n);
-                        if (!mbar_wait(full, ph)) return false;
-                        TRACE(2, n);
-                        if (t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
-                        mma4_2cta(tmem + j * 128, p_desc + (uint32_t)a * (P_Q >> 4), rv_desc + slot_off, 16, 128, idesc_pv,
-                                  (t | a) != 0);
-                        mma_commit_2cta(empty, 3);
-                        const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
-                        if (j == 1 && a == nq - 1) mma_commit_2cta(BAR(B_OREADY + (t & 1)), 3);   // tile t folded into O
+                // S = Q K^T, chunk c of K tile tk
+                auto k_step = [&](int tk, int c) {
+                    const int b = tk & 1, ks = k_slot(c);
+                    if (c == 0) {
+                        // S[b] was last read by the softmax of tile tk-2
+                        if (tk >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tk / 2) - 1) & 1);
+                        tc_fence_after_sync();
                     }
-                    if (++slot == NSLOT) { slot = 0; ph ^= 1; }
-                    return true;
-                });
-                if (!ok) atomicCAS(&g_tc_error, 0, ERR_MMA);
+                    ok = ok && mbar_wait(BAR(B_FULL + ks), k_use(tk, c) & 1);
+                    if (elected) {
+                        mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)c * (Q_CHUNK >> 4),
+                                  rk_desc + (uint32_t)ks * (SLOT >> 4), 2, 2, idesc_qk, c != 0);
+                        mma_commit_2cta(BAR(B_EMPTY + ks), 3);
+                        if (c == NQC - 1) mma_commit_2cta(BAR(B_SFULL + b), 3);
+                    }
+                };
+                // O += P V, quarter q, half j of this CTA's d_v columns, of tile t
+                auto v_step = [&](int t, int q, int j, bool last) {
+                    const int vs = v_slot(q, j);
+                    if (j == 0) {
+                        ok = ok && mbar_wait(BAR(B_PFULL + q), t & 1);
+                        tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
+                    }
+                    ok = ok && mbar_wait(BAR(B_FULL + vs), v_use(t, q) & 1);
+                    if (t_begin + (4 * t + q) * SUB + SUB > seq) ok = ok && mbar_wait(BAR(B_FIX + j), 0);
+                    if (elected) {
+                        mma4_2cta(tmem + j * 128, p_desc + (uint32_t)q * (P_Q >> 4), rv_desc + (uint32_t)vs * (SLOT >> 4),
+                                  16, 128, idesc_pv, (t | q) != 0);
+                        mma_commit_2cta(BAR(B_EMPTY + vs), 3);
+                        if (last) mma_commit_2cta(BAR(B_OREADY + (t & 1)), 3);   // tile t folded into O
+                    }
+                };
+#pragma unroll
+                for (int c = 0; c < NQC; ++c) k_step(0, c);
+#pragma unroll 1
+                for (int t = 0; t < n_tiles; ++t) {
+                    if (!__all_sync(0xffffffffu, ok)) break;
+                    const bool next = t + 1 < n_tiles;
+                    const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int c0 = (q == 0) ? 0 : (q == 1 ? 3 : (q == 2 ? 5 : 7));
+                        const int c1 = (q == 0) ? 3 : (q == 1 ? 5 : (q == 2 ? 7 : 9));
+                        if (next) {
+#pragma unroll
+                            for (int c = c0; c < c1; ++c) k_step(t + 1, c);
+                        }
+                        if (q < nq) {
+                            v_step(t, q, 0, false);
+                            v_step(t, q, 1, q == nq - 1);
+                        }
+                    }
+                }
+                if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_MMA);
             }
         } else {
             // =========================== load relay (peer CTA) ===========================
@@ -349,16 +369,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 bool ok = mbar_wait(BAR(B_QFULL), 0);
                 if (ok) mbar_arrive_cluster_relaxed(map_to_cta(BAR(B_PEER_QFULL), 0));
                 const uint32_t peer_base = map_to_cta(BAR(B_FULL), 0);
-                int n = 0;
                 ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                    const int slot = n % NSLOT, ph = (n / NSLOT) & 1;
-                    ++n;
-                    TRACE(5, n - 1);
-                    if (!mbar_wait(BAR(B_FULL + slot), ph)) return false;
-                    TRACE(1, n - 1);
+                    const int slot = is_v ? v_slot(a, j) : k_slot(a);
+                    const int use = is_v ? v_use(t, a) : k_use(t, a);
+                    if (!mbar_wait(BAR(B_FULL + slot), use & 1)) return false;
                     if (is_v && t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
                     mbar_arrive_cluster_relaxed(peer_base + 8u * slot);
-                    TRACE(2, n - 1);
                     return true;
                 });
                 if (!ok) atomicCAS(&g_tc_error, 0, ERR_RELAY);
