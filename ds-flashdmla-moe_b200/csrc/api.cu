@@ -76,6 +76,7 @@ const char *fdmla_status_string(int status) {
         case FDMLA_ERR_UNSUPPORTED: return "unsupported shape or dtype";
         case FDMLA_ERR_CUDA: return "CUDA error";
         case FDMLA_ERR_WORKSPACE: return "workspace missing or too small";
+        case FDMLA_ERR_SCRATCH_LIMIT: return "problem exceeds the built-in scratch of the no-allocation entry point";
         default: return "unknown status";
     }
 }

@@ -252,10 +252,17 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         }
         auto row_of = [&](int s) -> int { return s < ROWS_CACHE ? s_rows[s] : sub_row(s, &bad); };
         if (n_tiles > 0 && lane == 0) {
+#ifdef FDMLA_TRACE
+            int ptr_n = 0;
+#endif
             const bool ok = walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
                 const int slot = is_v ? v_slot(a, j) : k_slot(a);
                 const int use = is_v ? v_use(t, a) : k_use(t, a);
                 if (use >= 1 && !mbar_wait_relaxed_pace(BAR(B_EMPTY + slot), (use - 1) & 1)) return false;
+#ifdef FDMLA_TRACE
+                TRACE(0, ptr_n);
+                ++ptr_n;
+#endif
                 uint8_t *dst = sRing + slot * SLOT;
                 const uint32_t full = BAR(B_FULL + slot);
                 if (!is_v) {
@@ -308,6 +315,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 const uint64_t rv_desc = make_smem_desc(smem_u32(sRing), BOX, 1024, kLayoutSw128);   // ring slot as MN-major B
                 const uint64_t p_desc = make_smem_desc(smem_u32(sP), 128, P_SBO, kLayoutNone);
                 bool ok = mbar_wait(BAR(B_QFULL), 0) && mbar_wait(BAR(B_PEER_QFULL), 0);
+#ifdef FDMLA_TRACE
+                int ntr = 0;
+#endif
                 // S = Q K^T, chunk c of K tile tk
                 auto k_step = [&](int tk, int c) {
                     const int b = tk & 1, ks = k_slot(c);
@@ -316,7 +326,14 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         if (tk >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tk / 2) - 1) & 1);
                         tc_fence_after_sync();
                     }
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(1, ntr);
+#endif
                     ok = ok && mbar_wait(BAR(B_FULL + ks), k_use(tk, c) & 1);
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(2, ntr);
+                    ++ntr;
+#endif
                     if (elected) {
                         mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)c * (Q_CHUNK >> 4),
                                   rk_desc + (uint32_t)ks * (SLOT >> 4), 2, 2, idesc_qk, c != 0);
@@ -327,11 +344,21 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 // O += P V, quarter q, half j of this CTA's d_v columns, of tile t
                 auto v_step = [&](int t, int q, int j, bool last) {
                     const int vs = v_slot(q, j);
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(1, ntr);
+#endif
                     if (j == 0) {
                         ok = ok && mbar_wait(BAR(B_PFULL + q), t & 1);
                         tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
                     }
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(4, ntr);
+#endif
                     ok = ok && mbar_wait(BAR(B_FULL + vs), v_use(t, q) & 1);
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(2, ntr);
+                    ++ntr;
+#endif
                     if (t_begin + (4 * t + q) * SUB + SUB > seq) ok = ok && mbar_wait(BAR(B_FIX + j), 0);
                     if (elected) {
                         mma4_2cta(tmem + j * 128, p_desc + (uint32_t)q * (P_Q >> 4), rv_desc + (uint32_t)vs * (SLOT >> 4),

@@ -31,6 +31,8 @@ SIGNATURES = {
     "fdmla_fwd_on_the_fly": (_i, [_vp] * 9 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),
     "fdmla_decode_paged": (_i, [_vp] * 10 + [_i] * 10 + [_f, _i, _vp]),
     "fdmla_decode_suggest_splits": (_i, [_i] * 7),
+    "fdmla_decode_paged_noalloc_max_rows": (_sz, [_i]),
+    "fdmla_decode_paged_noalloc": (_i, [_vp] * 7 + [_i] * 8 + [_f, _i, _vp]),
     "fdmla_merge_lse": (_i, [_vp] * 6 + [_ll, _i, _i, _i, _vp]),
     "fdmla_bwd_on_the_fly_workspace_bytes": (_sz, [_i] * 7),
     "fdmla_bwd_on_the_fly": (_i, [_vp] * 15 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),

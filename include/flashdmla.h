@@ -40,6 +40,7 @@ extern "C" {
 #define FDMLA_ERR_UNSUPPORTED -2   /* shape outside what the kernels implement        */
 #define FDMLA_ERR_CUDA        -3   /* a CUDA runtime/driver call or a launch failed   */
 #define FDMLA_ERR_WORKSPACE   -4   /* workspace missing or smaller than required      */
+#define FDMLA_ERR_SCRATCH_LIMIT -5 /* problem exceeds the library's built-in scratch  */
 
 /* Kernel families, for fdmla_set_backend(): AUTO picks the tcgen05/TMA kernels
  * whenever the shape qualifies and the portable CUDA-core kernels otherwise. */
@@ -138,6 +139,34 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool,
  * with whole waves).  No reference counterpart. */
 int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,
                                 int page_size, int dtype);
+
+/*
+ * fdmla_decode_paged for callers that cannot allocate device memory.  It has no counterpart
+ * in the reference.  Same computation and same arguments as fdmla_decode_paged over the
+ * whole sequence (kv_begin = 0, no kv_end), but the split-KV partials are kept in a 32 MiB
+ * array that is part of the library image, so the caller passes no scratch buffers and the
+ * call itself never allocates or frees anything.  It is meant for code that runs where an
+ * allocation is impossible or forbidden: after all device memory has been handed to a pool
+ * the caller does not own, inside hosts that do not let an operator call the allocator, or
+ * on a latency path where an allocation would synchronise the device.
+ *   - The final O, m, l are always produced (O must not be NULL).
+ *   - num_splits * B * H must not exceed fdmla_decode_paged_noalloc_max_rows(d_v)
+ *     (16 320 rows at d_v = 512); a larger problem is refused with
+ *     FDMLA_ERR_SCRATCH_LIMIT and nothing is launched.  num_splits == 1 needs no scratch.
+ *   - The first call on a device looks up the array's device address; make that first call
+ *     outside any stream capture.
+ *   - Every call on a device shares the one array and it keeps the previous call's contents.
+ *     Nothing in it has to be cleared (each call overwrites every slot it later reads), but
+ *     two calls that overlap on the GPU (different streams, or different host threads) race
+ *     on it: serialise them, or use fdmla_decode_paged with separate buffers.
+ *   - Each GPU that loads the library holds the 32 MiB until the process exits.
+ */
+size_t fdmla_decode_paged_noalloc_max_rows(int d_v);
+int fdmla_decode_paged_noalloc(const void *Q, const void *kv_pool,
+                               const int32_t *page_table, const int32_t *seqlens,
+                               void *O, float *m, float *l, int B, int H, int d_qk,
+                               int d_v, int page_size, int max_pages, int num_pages,
+                               int num_splits, float scale, int dtype, void *stream);
 
 /*
  * Log-sum-exp merge of partial attention results over disjoint key sets.
