@@ -22,9 +22,9 @@
 //               16 KB per CTA).  D: lanes 0-63 hold d_v [0,256), lanes 64-127
 //               hold d_v [256,512)
 // All operand traffic goes through ONE ring of seven 16 KB slots per CTA, filled
-// by TMA (no multicast anywhere) in exactly the order the MMAs consume it; Q*K^T
-// of tile t+1 is interleaved with P*V of tile t so both the tensor pipe and the
-// ring stay busy.  Only the leader CTA (rank 0) issues MMAs; completion is
+// by TMA (no multicast anywhere) in exactly the order the MMAs consume it: Q*K^T
+// of tile t+1 is issued before P*V of tile t, so the tensor pipe works on the next
+// tile's scores while the softmax warps turn the current ones into P.  Only the leader CTA (rank 0) issues MMAs; completion is
 // broadcast to both CTAs' mbarriers with tcgen05.commit.  CTA 1 forwards "my
 // slot has landed" and both CTAs forward "my P quarter is written" to the leader
 // with remote mbarrier arrivals.
@@ -113,33 +113,23 @@ __device__ __forceinline__ void mma4_2cta(uint32_t d_tmem, uint64_t a_desc, uint
 // half j); it returns false to stop.  n_sub = number of 64-key sub-blocks to attend.
 template <class F>
 __device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
+    // K tile 0, then for every tile t: the whole K tile t+1 (its Q K^T runs while the softmax
+    // of tile t works), then the V quarters of tile t (their P V runs while the softmax of tile
+    // t+1 takes its row maxima).
     for (int c = 0; c < NQC; ++c)
         if (!f(false, 0, c, 0)) return false;
     for (int t = 0; t < n_tiles; ++t) {
-        const bool next = t + 1 < n_tiles;
+        if (t + 1 < n_tiles)
+            for (int c = 0; c < NQC; ++c)
+                if (!f(false, t + 1, c, 0)) return false;
         const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;     // quarters of tile t that exist
-        int c = 0;
-        for (int q = 0; q < 4; ++q) {
-            const int c_end = (q == 0) ? 3 : (q == 1 ? 5 : (q == 2 ? 7 : 9));
-            if (next)
-                for (; c < c_end; ++c)
-                    if (!f(false, t + 1, c, 0)) return false;
-            if (q < nq) {
-                if (!f(true, t, q, 0)) return false;
-                if (!f(true, t, q, 1)) return false;
-            }
+        for (int q = 0; q < nq; ++q) {
+            if (!f(true, t, q, 0)) return false;
+            if (!f(true, t, q, 1)) return false;
         }
     }
     return true;
 }
-
-// Ring positions are static: chunk c of any K tile uses K slot c % 3 (three uses per tile),
-// V (quarter q, half j) uses V slot 3 + (2q + j) % 4 (two uses per tile).  The k-th use of a
-// slot completes phase k of its barriers.
-__device__ __forceinline__ int k_slot(int c) { return c % 3; }
-__device__ __forceinline__ int v_slot(int q, int j) { return 3 + ((2 * q + j) & 3); }
-__device__ __forceinline__ int k_use(int t, int c) { return 3 * t + c / 3; }
-__device__ __forceinline__ int v_use(int t, int q) { return 2 * t + (q >> 1); }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK) {
@@ -251,16 +241,20 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             __syncwarp();
         }
         auto row_of = [&](int s) -> int { return s < ROWS_CACHE ? s_rows[s] : sub_row(s, &bad); };
-        if (n_tiles > 0 && lane == 0) {
+        if (n_tiles > 0) {
+            // The whole warp walks the ring converged and one elected lane issues the copies (the
+            // uniform datapath makes the issue several times cheaper than from a lone diverged lane).
+            const bool elected = elect_one();
+            int next_slot = 0, next_use = 0;      // ring position and how many times the ring has wrapped
 #ifdef FDMLA_TRACE
             int ptr_n = 0;
 #endif
             const bool ok = walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                const int slot = is_v ? v_slot(a, j) : k_slot(a);
-                const int use = is_v ? v_use(t, a) : k_use(t, a);
-                if (use >= 1 && !mbar_wait_relaxed_pace(BAR(B_EMPTY + slot), (use - 1) & 1)) return false;
+                const int slot = next_slot, use = next_use;
+                if (++next_slot == NSLOT) { next_slot = 0; ++next_use; }
+                if (use >= 1 && !mbar_wait(BAR(B_EMPTY + slot), (use - 1) & 1)) return false;
 #ifdef FDMLA_TRACE
-                TRACE(0, ptr_n);
+                if (lane == 0) TRACE(0, ptr_n);
                 ++ptr_n;
 #endif
                 uint8_t *dst = sRing + slot * SLOT;
@@ -269,33 +263,41 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     // K slot: own 128 keys of tile t (two sub-blocks), chunk a of d_qk
                     const int s0 = 4 * t + 2 * (int)rank;
                     const int present = (s0 + 1 < n_sub) ? 2 : (s0 < n_sub ? 1 : 0);
-                    mbar_arrive_expect_tx(full, present * BOX);
-                    for (int sb = 0; sb < present; ++sb)
-                        tma_load_2d(smem_u32(dst + sb * BOX), &tmK, a * 64, row_of(s0 + sb), full);
+                    const int r0 = present > 0 ? row_of(s0) : 0, r1 = present > 1 ? row_of(s0 + 1) : 0;
+                    if (elected) {
+                        mbar_arrive_expect_tx(full, present * BOX);
+                        if (present > 0) tma_load_2d(smem_u32(dst), &tmK, a * 64, r0, full);
+                        if (present > 1) tma_load_2d(smem_u32(dst + BOX), &tmK, a * 64, r1, full);
+                    }
                 } else {
                     // V slot: the 64 keys of quarter a of tile t, own d_v columns [256 r + 128 j, +128)
                     const int s = 4 * t + a;
                     const int row = row_of(s);
-                    mbar_arrive_expect_tx(full, SLOT);
-                    for (int cc = 0; cc < 2; ++cc)
-                        tma_load_2d(smem_u32(dst + cc * BOX), &tmK, 256 * (int)rank + 128 * j + 64 * cc, row, full);
+                    if (elected) {
+                        mbar_arrive_expect_tx(full, SLOT);
+                        tma_load_2d(smem_u32(dst), &tmK, 256 * (int)rank + 128 * j, row, full);
+                        tma_load_2d(smem_u32(dst + BOX), &tmK, 256 * (int)rank + 128 * j + 64, row, full);
+                    }
                     const int t0 = t_begin + s * SUB;
                     if (t0 + SUB > seq) {
                         // keys past the end of the sequence: zero their V rows once the copy has
                         // landed (whole 128-byte rows, so the swizzle does not matter)
                         if (!mbar_wait(full, use & 1)) return false;
                         const int first_bad = seq > t0 ? seq - t0 : 0;
-                        for (int cc = 0; cc < 2; ++cc)
-                            for (int r = first_bad; r < SUB; ++r)
-                                for (int q16 = 0; q16 < 8; ++q16)
-                                    *reinterpret_cast<uint4 *>(dst + cc * BOX + r * 128 + q16 * 16) = make_uint4(0, 0, 0, 0);
+                        const int bad_rows = SUB - first_bad;
+                        for (int idx = lane; idx < 2 * bad_rows * 8; idx += 32) {
+                            const int cc = idx / (bad_rows * 8), rem = idx - cc * bad_rows * 8;
+                            *reinterpret_cast<uint4 *>(dst + cc * BOX + (first_bad + rem / 8) * 128 + (rem & 7) * 16) =
+                                make_uint4(0, 0, 0, 0);
+                        }
                         fence_proxy_async_smem();
-                        mbar_arrive(BAR(B_FIX + j));  // only the last sub-block can straddle the end
+                        __syncwarp();
+                        if (elected) mbar_arrive(BAR(B_FIX + j));  // only the last sub-block can straddle the end
                     }
                 }
                 return true;
             });
-            if (!ok) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
+            if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
         }
         if (bad) atomicCAS(&g_tc_error, 0, ERR_PAGE);
         __syncwarp();
@@ -305,7 +307,6 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             // The whole warp runs this loop converged and one elected lane issues: that keeps the
             // descriptor arithmetic on the uniform datapath, which is what lets tcgen05.mma issue at
             // full rate (a single diverged lane issuing the same sequence is about half as fast).
-            // Ring positions are static, so a tile unrolls into straight-line code.
             if (n_tiles > 0) {
                 const bool elected = elect_one();
                 constexpr uint32_t idesc_qk = make_idesc_bf16(128, 256, 0, 0);
@@ -318,9 +319,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #ifdef FDMLA_TRACE
                 int ntr = 0;
 #endif
+                int slot = 0;               // ring position (the same in every lane) and its phase
+                uint32_t ph = 0;
+                auto advance = [&]() { if (++slot == NSLOT) { slot = 0; ph ^= 1; } };
                 // S = Q K^T, chunk c of K tile tk
                 auto k_step = [&](int tk, int c) {
-                    const int b = tk & 1, ks = k_slot(c);
+                    const int b = tk & 1, ks = slot;
                     if (c == 0) {
                         // S[b] was last read by the softmax of tile tk-2
                         if (tk >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tk / 2) - 1) & 1);
@@ -329,7 +333,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #ifdef FDMLA_TRACE
                     if (lane == 0) TRACE(1, ntr);
 #endif
-                    ok = ok && mbar_wait(BAR(B_FULL + ks), k_use(tk, c) & 1);
+                    ok = ok && mbar_wait(BAR(B_FULL + ks), ph);
 #ifdef FDMLA_TRACE
                     if (lane == 0) TRACE(2, ntr);
                     ++ntr;
@@ -340,10 +344,11 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         mma_commit_2cta(BAR(B_EMPTY + ks), 3);
                         if (c == NQC - 1) mma_commit_2cta(BAR(B_SFULL + b), 3);
                     }
+                    advance();
                 };
                 // O += P V, quarter q, half j of this CTA's d_v columns, of tile t
                 auto v_step = [&](int t, int q, int j, bool last) {
-                    const int vs = v_slot(q, j);
+                    const int vs = slot;
 #ifdef FDMLA_TRACE
                     if (lane == 0) TRACE(1, ntr);
 #endif
@@ -354,7 +359,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #ifdef FDMLA_TRACE
                     if (lane == 0) TRACE(4, ntr);
 #endif
-                    ok = ok && mbar_wait(BAR(B_FULL + vs), v_use(t, q) & 1);
+                    ok = ok && mbar_wait(BAR(B_FULL + vs), ph);
 #ifdef FDMLA_TRACE
                     if (lane == 0) TRACE(2, ntr);
                     ++ntr;
@@ -366,6 +371,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         mma_commit_2cta(BAR(B_EMPTY + vs), 3);
                         if (last) mma_commit_2cta(BAR(B_OREADY + (t & 1)), 3);   // tile t folded into O
                     }
+                    advance();
                 };
 #pragma unroll
                 for (int c = 0; c < NQC; ++c) k_step(0, c);
@@ -374,14 +380,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     if (!__all_sync(0xffffffffu, ok)) break;
                     const bool next = t + 1 < n_tiles;
                     const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
+                    if (next) {
+#pragma unroll
+                        for (int c = 0; c < NQC; ++c) k_step(t + 1, c);
+                    }
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const int c0 = (q == 0) ? 0 : (q == 1 ? 3 : (q == 2 ? 5 : 7));
-                        const int c1 = (q == 0) ? 3 : (q == 1 ? 5 : (q == 2 ? 7 : 9));
-                        if (next) {
-#pragma unroll
-                            for (int c = c0; c < c1; ++c) k_step(t + 1, c);
-                        }
                         if (q < nq) {
                             v_step(t, q, 0, false);
                             v_step(t, q, 1, q == nq - 1);
@@ -392,19 +396,21 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             }
         } else {
             // =========================== load relay (peer CTA) ===========================
-            if (lane == 0 && n_tiles > 0) {
+            // (converged warp, one elected lane signals: see the MMA issuer)
+            if (n_tiles > 0) {
+                const bool elected = elect_one();
                 bool ok = mbar_wait(BAR(B_QFULL), 0);
-                if (ok) mbar_arrive_cluster_relaxed(map_to_cta(BAR(B_PEER_QFULL), 0));
+                if (ok && elected) mbar_arrive_cluster_relaxed(map_to_cta(BAR(B_PEER_QFULL), 0));
                 const uint32_t peer_base = map_to_cta(BAR(B_FULL), 0);
+                int slot = 0, use = 0;
                 ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                    const int slot = is_v ? v_slot(a, j) : k_slot(a);
-                    const int use = is_v ? v_use(t, a) : k_use(t, a);
                     if (!mbar_wait(BAR(B_FULL + slot), use & 1)) return false;
                     if (is_v && t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
-                    mbar_arrive_cluster_relaxed(peer_base + 8u * slot);
+                    if (elected) mbar_arrive_cluster_relaxed(peer_base + 8u * slot);
+                    if (++slot == NSLOT) { slot = 0; ++use; }
                     return true;
                 });
-                if (!ok) atomicCAS(&g_tc_error, 0, ERR_RELAY);
+                if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_RELAY);
             }
         }
         __syncwarp();
