@@ -435,6 +435,23 @@ bool make_tensor_map_bf16(CUtensorMap *m, const void *base, long long rows, int 
     return make_map(m, base, rows, cols, box_rows);
 }
 
+// The same [rows, cols] bf16 tensor seen as [cols/64 chunks][rows][64 columns] (the chunk dimension
+// is the outermost box dimension although its stride, 128 B, is the smallest), so that one copy of a
+// box {64, box_rows, box_chunks} lands in shared memory as box_chunks consecutive [box_rows x 128 B]
+// swizzled tiles - the layout the MMA descriptors expect - instead of one copy per chunk.
+bool make_tensor_map_bf16_chunked(CUtensorMap *m, const void *base, long long rows, int cols, int box_rows,
+                                  int box_chunks) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc || rows <= 0 || cols % 64 != 0) return false;
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_chunks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace fdmla
 
 #include "tc_fwd2.cuh"   // 2-CTA kernel for the MLA dimensions

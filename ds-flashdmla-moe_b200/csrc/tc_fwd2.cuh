@@ -132,7 +132,10 @@ __device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK) {
+fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV) {
+    // tmQ: chunked view, box {64, 64 rows, 9 chunks}; tmK: plain 2-D, box {64, 64 rows};
+    // tmV: chunked view of the same cache, box {64, 64 rows, 2 chunks}
     using namespace ptx;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -230,10 +233,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             if (lane == 0) {
                 prefetch_tmap(&tmQ);
                 prefetch_tmap(&tmK);
+                prefetch_tmap(&tmV);
                 mbar_arrive_expect_tx(BAR(B_QFULL), Q_BYTES);
                 const int qrow = g * p.R + row0 + 64 * (int)rank;
-                for (int c = 0; c < NQC; ++c)
-                    tma_load_2d(smem_u32(sQ + c * Q_CHUNK), &tmQ, c * 64, qrow, BAR(B_QFULL));
+                tma_load_3d(smem_u32(sQ), &tmQ, 0, qrow, 0, BAR(B_QFULL));          // all 9 chunks in one copy
             }
             // resolve the page table for the whole key range once, with every lane of the warp
             const int n_cached = n_sub < ROWS_CACHE ? n_sub : ROWS_CACHE;
@@ -275,8 +278,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     const int row = row_of(s);
                     if (elected) {
                         mbar_arrive_expect_tx(full, SLOT);
-                        tma_load_2d(smem_u32(dst), &tmK, 256 * (int)rank + 128 * j, row, full);
-                        tma_load_2d(smem_u32(dst + BOX), &tmK, 256 * (int)rank + 128 * j + 64, row, full);
+                        tma_load_3d(smem_u32(dst), &tmV, 0, row, 4 * (int)rank + 2 * j, full);   // two chunks, one copy
                     }
                     const int t0 = t_begin + s * SUB;
                     if (t0 + SUB > seq) {
@@ -641,14 +643,15 @@ bool fwd_tensor2_supported(const FwdProblem &p, int dtype) {
 }
 
 int launch_fwd_tensor2(const FwdProblem &p, cudaStream_t stream) {
-    CUtensorMap tmQ, tmK;
+    CUtensorMap tmQ, tmK, tmV;
     const long long kv_rows = p.page_table ? (long long)p.num_pages * p.page_size : (long long)p.G * p.Skv;
-    if (!make_tensor_map_bf16(&tmQ, p.Q, (long long)p.G * p.R, p.d_qk, 64)) return FDMLA_ERR_CUDA;
+    if (!make_tensor_map_bf16_chunked(&tmQ, p.Q, (long long)p.G * p.R, p.d_qk, 64, 9)) return FDMLA_ERR_CUDA;
+    if (!make_tensor_map_bf16_chunked(&tmV, p.K, kv_rows, p.d_qk, 64, 2)) return FDMLA_ERR_CUDA;
     if (!make_tensor_map_bf16(&tmK, p.K, kv_rows, p.d_qk, 64)) return FDMLA_ERR_CUDA;
     if (cudaFuncSetAttribute(tc2::fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES) != cudaSuccess)
         return FDMLA_ERR_CUDA;
     dim3 grid(((p.R + 127) / 128) * 2, p.G, p.num_splits);
-    tc2::fwd_tc2_kernel<<<grid, tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK);
+    tc2::fwd_tc2_kernel<<<grid, tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
     return check_launch();
 }
 
