@@ -62,6 +62,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// Wait for two / three barriers at once: the polls are independent instructions, so their
+// latencies overlap instead of adding up.  Bounded like mbar_wait.
+__device__ __forceinline__ bool mbar_wait2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1) {
+    bool d0 = false, d1 = false;
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (!d0) d0 = mbar_try_wait(b0, p0);
+        if (!d1) d1 = mbar_try_wait(b1, p1);
+        if (d0 && d1) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ bool mbar_wait3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2) {
+    bool d0 = false, d1 = false, d2 = false;
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (!d0) d0 = mbar_try_wait(b0, p0);
+        if (!d1) d1 = mbar_try_wait(b1, p1);
+        if (!d2) d2 = mbar_try_wait(b2, p2);
+        if (d0 && d1 && d2) return true;
+    }
+    return false;
+}
 // Same for waits that are not latency critical (a producer waiting for a free ring slot):
 // backs off between polls so the spinning thread does not take issue slots from the
 // warps doing the work.

@@ -249,56 +249,80 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             // uniform datapath makes the issue several times cheaper than from a lone diverged lane).
             const bool elected = elect_one();
             int next_slot = 0, next_use = 0;      // ring position and how many times the ring has wrapped
-#ifdef FDMLA_TRACE
-            int ptr_n = 0;
-#endif
-            const bool ok = walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                const int slot = next_slot, use = next_use;
+            bool ok = true;
+            auto take = [&](int &slot, int &use) {
+                slot = next_slot; use = next_use;
                 if (++next_slot == NSLOT) { next_slot = 0; ++next_use; }
-                if (use >= 1 && !mbar_wait(BAR(B_EMPTY + slot), (use - 1) & 1)) return false;
-#ifdef FDMLA_TRACE
-                if (lane == 0) TRACE(0, ptr_n);
-                ++ptr_n;
-#endif
-                uint8_t *dst = sRing + slot * SLOT;
-                const uint32_t full = BAR(B_FULL + slot);
-                if (!is_v) {
-                    // K slot: own 128 keys of tile t (two sub-blocks), chunk a of d_qk
-                    const int s0 = 4 * t + 2 * (int)rank;
-                    const int present = (s0 + 1 < n_sub) ? 2 : (s0 < n_sub ? 1 : 0);
-                    const int r0 = present > 0 ? row_of(s0) : 0, r1 = present > 1 ? row_of(s0 + 1) : 0;
-                    if (elected) {
+            };
+            // three K slots: chunks 3*g3 .. 3*g3+2 of K tile t (own 128 keys = two sub-blocks each)
+            auto fill_k3 = [&](int t, int g3) {
+                int sl[3], us[3];
+                for (int i = 0; i < 3; ++i) take(sl[i], us[i]);
+                if (us[2] >= 1) {     // slots handed out before: wait until the MMAs that read them are done
+                    if (us[0] >= 1)
+                        ok = ok && mbar_wait3(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1,
+                                              BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
+                    else if (us[1] >= 1)
+                        ok = ok && mbar_wait2(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1, BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
+                    else
+                        ok = ok && mbar_wait(BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
+                }
+                const int s0 = 4 * t + 2 * (int)rank;
+                const int present = (s0 + 1 < n_sub) ? 2 : (s0 < n_sub ? 1 : 0);
+                const int r0 = present > 0 ? row_of(s0) : 0, r1 = present > 1 ? row_of(s0 + 1) : 0;
+                if (elected) {
+#pragma unroll
+                    for (int i = 0; i < 3; ++i) {
+                        const uint32_t full = BAR(B_FULL + sl[i]);
+                        const uint32_t dst = smem_u32(sRing + sl[i] * SLOT);
                         mbar_arrive_expect_tx(full, present * BOX);
-                        if (present > 0) tma_load_2d(smem_u32(dst), &tmK, a * 64, r0, full);
-                        if (present > 1) tma_load_2d(smem_u32(dst + BOX), &tmK, a * 64, r1, full);
-                    }
-                } else {
-                    // V slot: the 64 keys of quarter a of tile t, own d_v columns [256 r + 128 j, +128)
-                    const int s = 4 * t + a;
-                    const int row = row_of(s);
-                    if (elected) {
-                        mbar_arrive_expect_tx(full, SLOT);
-                        tma_load_3d(smem_u32(dst), &tmV, 0, row, 4 * (int)rank + 2 * j, full);   // two chunks, one copy
-                    }
-                    const int t0 = t_begin + s * SUB;
-                    if (t0 + SUB > seq) {
-                        // keys past the end of the sequence: zero their V rows once the copy has
-                        // landed (whole 128-byte rows, so the swizzle does not matter)
-                        if (!mbar_wait(full, use & 1)) return false;
-                        const int first_bad = seq > t0 ? seq - t0 : 0;
-                        const int bad_rows = SUB - first_bad;
-                        for (int idx = lane; idx < 2 * bad_rows * 8; idx += 32) {
-                            const int cc = idx / (bad_rows * 8), rem = idx - cc * bad_rows * 8;
-                            *reinterpret_cast<uint4 *>(dst + cc * BOX + (first_bad + rem / 8) * 128 + (rem & 7) * 16) =
-                                make_uint4(0, 0, 0, 0);
-                        }
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (elected) mbar_arrive(BAR(B_FIX + j));  // only the last sub-block can straddle the end
+                        if (present > 0) tma_load_2d(dst, &tmK, (3 * g3 + i) * 64, r0, full);
+                        if (present > 1) tma_load_2d(dst + BOX, &tmK, (3 * g3 + i) * 64, r1, full);
                     }
                 }
-                return true;
-            });
+            };
+            // two V slots: the 64 keys of quarter q of tile t, own d_v columns [256 r + 128 j, +128), j = 0, 1
+            auto fill_v2 = [&](int t, int q) {
+                int sl[2], us[2];
+                for (int j = 0; j < 2; ++j) take(sl[j], us[j]);
+                if (us[0] >= 1)
+                    ok = ok && mbar_wait2(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
+                else if (us[1] >= 1)
+                    ok = ok && mbar_wait(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
+                const int s = 4 * t + q;
+                const int row = row_of(s);
+                if (elected) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const uint32_t full = BAR(B_FULL + sl[j]);
+                        mbar_arrive_expect_tx(full, SLOT);
+                        tma_load_3d(smem_u32(sRing + sl[j] * SLOT), &tmV, 0, row, 4 * (int)rank + 2 * j, full);   // two chunks, one copy
+                    }
+                }
+                const int t0 = t_begin + s * SUB;
+                if (t0 + SUB > seq) {
+                    // keys past the end of the sequence: zero their V rows once the copies have
+                    // landed (whole 128-byte rows, so the swizzle does not matter)
+                    ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), us[0] & 1, BAR(B_FULL + sl[1]), us[1] & 1);
+                    const int first_bad = seq > t0 ? seq - t0 : 0;
+                    const int bad_rows = SUB - first_bad;
+                    for (int idx = lane; idx < 4 * bad_rows * 8; idx += 32) {
+                        const int cc = idx / (bad_rows * 8), rem = idx - cc * bad_rows * 8;
+                        *reinterpret_cast<uint4 *>(sRing + sl[cc >> 1] * SLOT + (cc & 1) * BOX + (first_bad + rem / 8) * 128 +
+                                                   (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (elected) { mbar_arrive(BAR(B_FIX)); mbar_arrive(BAR(B_FIX + 1)); }   // only the last sub-block can straddle the end
+                }
+            };
+            for (int g3 = 0; g3 < 3; ++g3) fill_k3(0, g3);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (t + 1 < n_tiles)
+                    for (int g3 = 0; g3 < 3; ++g3) fill_k3(t + 1, g3);
+                const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
+                for (int q = 0; q < nq; ++q) fill_v2(t, q);
+            }
             if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
         }
         if (bad) atomicCAS(&g_tc_error, 0, ERR_PAGE);
@@ -323,76 +347,65 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #endif
                 int slot = 0;               // ring position (the same in every lane) and its phase
                 uint32_t ph = 0;
-                auto advance = [&]() { if (++slot == NSLOT) { slot = 0; ph ^= 1; } };
-                // S = Q K^T, chunk c of K tile tk
-                auto k_step = [&](int tk, int c) {
-                    const int b = tk & 1, ks = slot;
-                    if (c == 0) {
+                auto take = [&](int &sl, uint32_t &p) {
+                    sl = slot; p = ph;
+                    if (++slot == NSLOT) { slot = 0; ph ^= 1; }
+                };
+                // S = Q K^T: chunks 3*g3 .. 3*g3+2 of K tile tk, three ring slots waited for together
+                auto k_group = [&](int tk, int g3) {
+                    const int b = tk & 1;
+                    int sl[3];
+                    uint32_t phs[3];
+                    for (int i = 0; i < 3; ++i) take(sl[i], phs[i]);
+                    if (g3 == 0) {
                         // S[b] was last read by the softmax of tile tk-2
                         if (tk >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tk / 2) - 1) & 1);
                         tc_fence_after_sync();
                     }
-#ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(1, ntr);
-#endif
-                    ok = ok && mbar_wait(BAR(B_FULL + ks), ph);
-#ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(2, ntr);
-                    ++ntr;
-#endif
+                    ok = ok && mbar_wait3(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1], BAR(B_FULL + sl[2]), phs[2]);
                     if (elected) {
-                        mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)c * (Q_CHUNK >> 4),
-                                  rk_desc + (uint32_t)ks * (SLOT >> 4), 2, 2, idesc_qk, c != 0);
-                        mma_commit_2cta(BAR(B_EMPTY + ks), 3);
-                        if (c == NQC - 1) mma_commit_2cta(BAR(B_SFULL + b), 3);
+#pragma unroll
+                        for (int i = 0; i < 3; ++i) {
+                            const int c = 3 * g3 + i;
+                            mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)c * (Q_CHUNK >> 4),
+                                      rk_desc + (uint32_t)sl[i] * (SLOT >> 4), 2, 2, idesc_qk, c != 0);
+                            mma_commit_2cta(BAR(B_EMPTY + sl[i]), 3);
+                        }
+                        if (g3 == 2) mma_commit_2cta(BAR(B_SFULL + b), 3);
                     }
-                    advance();
                 };
-                // O += P V, quarter q, half j of this CTA's d_v columns, of tile t
-                auto v_step = [&](int t, int q, int j, bool last) {
-                    const int vs = slot;
-#ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(1, ntr);
-#endif
-                    if (j == 0) {
-                        ok = ok && mbar_wait(BAR(B_PFULL + q), t & 1);
-                        tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
-                    }
-#ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(4, ntr);
-#endif
-                    ok = ok && mbar_wait(BAR(B_FULL + vs), ph);
-#ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(2, ntr);
-                    ++ntr;
-#endif
-                    if (t_begin + (4 * t + q) * SUB + SUB > seq) ok = ok && mbar_wait(BAR(B_FIX + j), 0);
+                // O += P V: quarter q of tile t, both halves j of this CTA's d_v columns
+                auto v_pair = [&](int t, int q, bool last) {
+                    int sl[2];
+                    uint32_t phs[2];
+                    for (int j = 0; j < 2; ++j) take(sl[j], phs[j]);
+                    ok = ok && mbar_wait(BAR(B_PFULL + q), t & 1);
+                    tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
+                    ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1]);
+                    if (t_begin + (4 * t + q) * SUB + SUB > seq) ok = ok && mbar_wait2(BAR(B_FIX), 0, BAR(B_FIX + 1), 0);
                     if (elected) {
-                        mma4_2cta(tmem + j * 128, p_desc + (uint32_t)q * (P_Q >> 4), rv_desc + (uint32_t)vs * (SLOT >> 4),
-                                  16, 128, idesc_pv, (t | q) != 0);
-                        mma_commit_2cta(BAR(B_EMPTY + vs), 3);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            mma4_2cta(tmem + j * 128, p_desc + (uint32_t)q * (P_Q >> 4), rv_desc + (uint32_t)sl[j] * (SLOT >> 4),
+                                      16, 128, idesc_pv, (t | q) != 0);
+                            mma_commit_2cta(BAR(B_EMPTY + sl[j]), 3);
+                        }
                         if (last) mma_commit_2cta(BAR(B_OREADY + (t & 1)), 3);   // tile t folded into O
                     }
-                    advance();
                 };
 #pragma unroll
-                for (int c = 0; c < NQC; ++c) k_step(0, c);
+                for (int g3 = 0; g3 < 3; ++g3) k_group(0, g3);
 #pragma unroll 1
                 for (int t = 0; t < n_tiles; ++t) {
                     if (!__all_sync(0xffffffffu, ok)) break;
-                    const bool next = t + 1 < n_tiles;
                     const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
-                    if (next) {
+                    if (t + 1 < n_tiles) {
 #pragma unroll
-                        for (int c = 0; c < NQC; ++c) k_step(t + 1, c);
+                        for (int g3 = 0; g3 < 3; ++g3) k_group(t + 1, g3);
                     }
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        if (q < nq) {
-                            v_step(t, q, 0, false);
-                            v_step(t, q, 1, q == nq - 1);
-                        }
-                    }
+                    for (int q = 0; q < 4; ++q)
+                        if (q < nq) v_pair(t, q, q == nq - 1);
                 }
                 if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_MMA);
             }
