@@ -127,6 +127,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, 
         : "memory");
 }
 
+// One 128-byte line into L2 (no register result, nothing to wait for).
+__device__ __forceinline__ void prefetch_l2(const void *ptr) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+}
+
 // ---- tensor memory --------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");

@@ -52,6 +52,7 @@ constexpr int Q_BYTES = NQC * Q_CHUNK;            // 73 728
 constexpr int SLOT = 16384;           // ring slot: 2 boxes of [64 keys x 128 B]
 constexpr int BOX = 8192;
 constexpr int NSLOT = 7;
+constexpr int PF_DIST = 1;             // decode: tiles of distance of the softmax threads' L2 prefetch (0 = off)
 constexpr int P_Q = 64 * SUB * 2;     // one P quarter: 64 rows x 64 keys bf16 = 8 192
 constexpr int P_BYTES = 4 * P_Q;
 constexpr int P_SBO = (SUB / 8) * 128;            // 1 024
@@ -250,6 +251,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             const bool elected = elect_one();
             int next_slot = 0, next_use = 0;      // ring position and how many times the ring has wrapped
             bool ok = true;
+#ifdef FDMLA_TRACE
+            int ptr_n = 0;
+#endif
             auto take = [&](int &slot, int &use) {
                 slot = next_slot; use = next_use;
                 if (++next_slot == NSLOT) { next_slot = 0; ++next_use; }
@@ -267,6 +271,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     else
                         ok = ok && mbar_wait(BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
                 }
+#ifdef FDMLA_TRACE
+                if (lane == 0) TRACE(0, ptr_n);
+                ++ptr_n;
+#endif
                 const int s0 = 4 * t + 2 * (int)rank;
                 const int present = (s0 + 1 < n_sub) ? 2 : (s0 < n_sub ? 1 : 0);
                 const int r0 = present > 0 ? row_of(s0) : 0, r1 = present > 1 ? row_of(s0 + 1) : 0;
@@ -289,6 +297,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     ok = ok && mbar_wait2(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
                 else if (us[1] >= 1)
                     ok = ok && mbar_wait(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
+#ifdef FDMLA_TRACE
+                if (lane == 0) TRACE(0, ptr_n);
+                ++ptr_n;
+#endif
                 const int s = 4 * t + q;
                 const int row = row_of(s);
                 if (elected) {
@@ -362,7 +374,14 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         if (tk >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tk / 2) - 1) & 1);
                         tc_fence_after_sync();
                     }
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(1, ntr);
+#endif
                     ok = ok && mbar_wait3(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1], BAR(B_FULL + sl[2]), phs[2]);
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(2, ntr);
+                    ++ntr;
+#endif
                     if (elected) {
 #pragma unroll
                         for (int i = 0; i < 3; ++i) {
@@ -379,9 +398,19 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     int sl[2];
                     uint32_t phs[2];
                     for (int j = 0; j < 2; ++j) take(sl[j], phs[j]);
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(1, ntr);
+#endif
                     ok = ok && mbar_wait(BAR(B_PFULL + q), t & 1);
                     tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(4, ntr);
+#endif
                     ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1]);
+#ifdef FDMLA_TRACE
+                    if (lane == 0) TRACE(2, ntr);
+                    ++ntr;
+#endif
                     if (t_begin + (4 * t + q) * SUB + SUB > seq) ok = ok && mbar_wait2(BAR(B_FIX), 0, BAR(B_FIX + 1), 0);
                     if (elected) {
 #pragma unroll
@@ -452,12 +481,30 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         const uint32_t sempty_leader = map_to_cta(BAR(B_SEMPTY), 0);
         bool ok = true;
         uint32_t r[32];
+        const bool do_prefetch = p.Sq == 1;     // decode streams the cache from HBM; prefill finds it in L2 anyway
         for (int t = 0; t < n_tiles; ++t) {
             const int b = t & 1, tok0 = t_begin + t * T + 128 * half;
             const uint32_t s_addr = tmem + lane_base + S_COL0 + b * S_COLS;
             // after a failed wait the loop keeps running without further waits so that the
             // named barriers below stay matched across the softmax threads
             if (L == 0) TRACE(3, t * 8 + 0);
+            if (PF_DIST > 0 && do_prefetch) {
+                // While this thread would only wait for S: pull one cache row of a later tile into L2.
+                // The 128 softmax threads of the CTA cover the CTA's own 128 keys of that tile (the
+                // pair covers the tile), so the TMA copies issued PF_DIST tiles from now hit L2 and
+                // the ring only has to hide the L2 latency, not the HBM latency.
+                for (int tp = (t == 0 ? 1 : t + PF_DIST); tp <= t + PF_DIST; ++tp) {
+                    const int s = 4 * tp + 2 * (int)rank + half;
+                    if (s < n_sub && t_begin + s * SUB + row < blk_hi) {
+                        bool bad_page = false;
+                        const char *src = static_cast<const char *>(p.K) + ((size_t)sub_row(s, &bad_page) + row) * (NQC * 128);
+                        if (!bad_page) {
+#pragma unroll
+                            for (int c = 0; c < NQC; ++c) prefetch_l2(src + c * 128);
+                        }
+                    }
+                }
+            }
             if (ok) ok = mbar_wait(BAR(B_SFULL + b), (t / 2) & 1);
             if (L == 0) TRACE(3, t * 8 + 1);
             tc_fence_after_sync();
