@@ -42,6 +42,10 @@ DECODE_BYTES = (B * SKV * D_QK * 2          # latent rows read once
                 + 2 * B * H * 4             # m, l
                 + B * (SKV // PAGE) * 4)    # page table            = 639 795 200
 DECODE_FLOP = 2 * B * H * SKV * (D_QK + D_V)
+# DRAM bytes per sequence of one decode launch, from the ncu capture of the B=32 case
+# (profiles/fwd_tc2_kernel_decode_b32.md: read 157.15 MB + write 4.71 MB for 32 sequences); traffic grows in
+# proportion to the sequences, so a launch of B sequences moves B times this.
+NCU_DRAM_BYTES_PER_SEQ = (157_146_624 + 4_708_864) / 32
 PF_B, PF_H, PF_S = 4, 128, 8192
 PREFILL_FLOP_CAUSAL = 2 * PF_B * PF_H * (PF_S * (PF_S + 1) // 2) * (D_QK + D_V)
 
@@ -318,8 +322,11 @@ def main():
                     "note": "paged KV pool stays resident in HBM (it is the cache); Q, page table, seqlens in, O, m, l out"},
             "gpu_launches": launches_per_step * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_src,
-                         "kernel": "fwd_tc_kernel (split-KV decode)", "kernel_ms": k_ms,
+                         "frac": achieved / hbm_peak, "traffic": NCU_DRAM_BYTES_PER_SEQ * B,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the B=32 capture, "
+                                           "scaled by the number of sequences",
+                         "peak_source": peak_src,
+                         "kernel": "fwd_tc2_kernel (2-CTA tcgen05 split-KV decode)", "kernel_ms": k_ms,
                          "algorithmic_bytes": DECODE_BYTES, "tensor_tflops": DECODE_FLOP / (k_ms * 1e-3) / 1e12,
                          "frac_of_8TBs_spec": achieved / 8000.0},
             "decode_hbm_gbs_per_gpu": DECODE_BYTES / (ms_per_step * 1e-3) / 1e9,
