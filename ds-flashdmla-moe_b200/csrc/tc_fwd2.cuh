@@ -60,7 +60,7 @@ constexpr int RED_BYTES = 2 * 128 * 4;
 constexpr int ROWS_CACHE = 1920;      // sub-block rows resolved through the page table up front
 constexpr int O_COLS = 256, S_COL0 = 256, S_COLS = 128, TMEM_COLS = 512;
 // barriers (same offsets in both CTAs)
-constexpr int B_QFULL = 0, B_PEER_QFULL = 1, B_FULL = 2, B_PEER = B_FULL + NSLOT, B_EMPTY = B_PEER + NSLOT,
+constexpr int B_QFULL = 0, B_PEER_QFULL = 1, B_QEMPTY = 2, B_OFREE = 3, B_FULL = 4, B_EMPTY = B_FULL + NSLOT,
               B_FIX = B_EMPTY + NSLOT, B_SFULL = B_FIX + 2, B_SEMPTY = B_SFULL + 2, B_PFULL = B_SEMPTY + 2,
               B_OREADY = B_PFULL + 4, NBARS = B_OREADY + 2;
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + NSLOT * SLOT + P_BYTES + RED_BYTES + ROWS_CACHE * 4 + NBARS * 8 + 16;
@@ -132,6 +132,54 @@ __device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
     return true;
 }
 
+// One unit of work of the persistent kernel: a 128-row tile of one KV group and one KV split.
+struct Item {
+    int row0, g, split;       // first row of the tile, KV group, split index
+    int seq;                  // keys of the group
+    int lo, hi;               // this split's key window
+    int blk_hi;               // end of the keys any row of the tile may see
+    int t_begin;              // first key of the first tile (lo rounded down to a tile)
+    int n_sub, n_tiles;       // 64-key sub-blocks / 256-key tiles to attend
+    int rows_here;
+    bool fix;                 // the last sub-block reaches past the end of the sequence (its V rows get zeroed)
+};
+
+__device__ __forceinline__ Item make_item(const FwdProblem &p, int idx, int n_row_tiles, bool poisoned) {
+    Item it;
+    const int per_rt = p.G * p.num_splits;
+    const int rt = idx / per_rt, rem = idx - rt * per_rt;
+    it.g = rem / p.num_splits;
+    it.split = rem - it.g * p.num_splits;
+    const int tile_idx = p.causal ? n_row_tiles - 1 - rt : rt;     // causal: the longest rows first
+    it.row0 = tile_idx * 128;
+    it.seq = p.seqlens ? p.seqlens[it.g] : p.Skv;
+    const int w_lo = p.kv_begin > 0 ? p.kv_begin : 0;
+    const int w_hi = (p.kv_end >= 0 && p.kv_end < it.seq) ? p.kv_end : it.seq;
+    // splits are cut on tile boundaries where the page size allows it
+    const int gran = (p.page_table && (T % p.page_size) != 0) ? p.page_size : T;
+    split_window(w_lo, w_hi, gran, it.split, p.num_splits, &it.lo, &it.hi);
+    it.rows_here = (p.R - it.row0) < 128 ? (p.R - it.row0) : 128;
+    int blk_vis = it.seq;
+    if (p.causal) {
+        const int r_last = it.row0 + it.rows_here - 1;
+        const int i_max = (it.row0 / p.Sq == r_last / p.Sq) ? (r_last % p.Sq) : (p.Sq - 1);
+        long long v = (long long)i_max + it.seq - p.Sq + 1;
+        blk_vis = v < 0 ? 0 : (v > it.seq ? it.seq : (int)v);
+    }
+    it.blk_hi = it.hi < blk_vis ? it.hi : blk_vis;
+    it.t_begin = (it.lo / T) * T;
+    it.n_sub = (it.blk_hi > it.lo && !poisoned) ? (it.blk_hi - it.t_begin + SUB - 1) / SUB : 0;
+    it.n_tiles = (it.n_sub + 3) / 4;
+    it.fix = it.n_sub > 0 && it.t_begin + it.n_sub * SUB > it.seq;
+    return it;
+}
+
+// The persistent grid: cluster c takes items c, 2n-1-c, 2n+c, ... (a snake over rounds of n clusters,
+// so that an order sorted by work does not always hand the same cluster the largest item of a round).
+__device__ __forceinline__ int item_of_round(int round, int cid, int n_clusters) {
+    return round * n_clusters + ((round & 1) ? n_clusters - 1 - cid : cid);
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV) {
@@ -154,48 +202,29 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const bool leader = rank == 0;
 #ifdef FDMLA_TRACE
-    const bool trace_on = blockIdx.x < 2 && blockIdx.y == 0 && blockIdx.z == 0;
+    const bool trace_on = blockIdx.x < 2;
 #endif
 
-    // ---- work item (identical in both CTAs of the pair) ---------------------------
+    // ---- the work list (identical in both CTAs of the pair and in every role) -----------
     const int n_row_tiles = (p.R + 127) / 128;
-    int tile_idx = blockIdx.x >> 1;
-    if (p.causal) tile_idx = n_row_tiles - 1 - tile_idx;
-    const int g = blockIdx.y, split = blockIdx.z;
-    const int row0 = tile_idx * 128;
-    const int seq = p.seqlens ? p.seqlens[g] : p.Skv;
-    const int w_lo = p.kv_begin > 0 ? p.kv_begin : 0;
-    const int w_hi = (p.kv_end >= 0 && p.kv_end < seq) ? p.kv_end : seq;
-    int lo, hi;
-    // splits are cut on tile boundaries where the page size allows it
-    const int gran = (p.page_table && (T % p.page_size) != 0) ? p.page_size : T;
-    split_window(w_lo, w_hi, gran, split, p.num_splits, &lo, &hi);
-    const int rows_here = (p.R - row0) < 128 ? (p.R - row0) : 128;
-    int blk_vis = seq;
-    if (p.causal) {
-        const int r_last = row0 + rows_here - 1;
-        const int i_max = (row0 / p.Sq == r_last / p.Sq) ? (r_last % p.Sq) : (p.Sq - 1);
-        long long v = (long long)i_max + seq - p.Sq + 1;
-        blk_vis = v < 0 ? 0 : (v > seq ? seq : (int)v);
-    }
-    const int blk_hi = hi < blk_vis ? hi : blk_vis;
-    const int t_begin = (lo / T) * T;
+    const int n_items = n_row_tiles * p.G * p.num_splits;
+    const int cid = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    const int n_rounds = (n_items + n_clusters - 1) / n_clusters;
     const int err_now = *reinterpret_cast<volatile int *>(&g_tc_error);
     const bool poisoned = err_now != 0 && err_now != ERR_PAGE;
-    const int n_sub = (blk_hi > lo && !poisoned) ? (blk_hi - t_begin + SUB - 1) / SUB : 0;   // sub-blocks to attend
-    const int n_tiles = (n_sub + 3) / 4;
 
     // ---- set-up ------------------------------------------------------------------------
     if (threadIdx.x == 0) {
         mbar_init(BAR(B_QFULL), 1);
         mbar_init(BAR(B_PEER_QFULL), 1);
+        mbar_init(BAR(B_QEMPTY), 1);
+        mbar_init(BAR(B_OFREE), 2);                      // one arrival per CTA of the pair
         for (int s = 0; s < NSLOT; ++s) {
             mbar_init(BAR(B_FULL + s), leader ? 2 : 1);   // leader: own copy + the peer's "landed" arrival
-            mbar_init(BAR(B_PEER + s), 1);               // (unused)
             mbar_init(BAR(B_EMPTY + s), 1);
         }
         mbar_init(BAR(B_FIX), 1);          // zero-filled tail of the j = 0 V slot
-        mbar_init(BAR(B_FIX + 1), 1);      // ... and of the j = 1 V slot (each used once)
+        mbar_init(BAR(B_FIX + 1), 1);      // ... and of the j = 1 V slot (each used once per item at most)
         for (int b = 0; b < 2; ++b) {
             mbar_init(BAR(B_SFULL + b), 1);
             mbar_init(BAR(B_SEMPTY + b), 4);     // two key halves in each CTA of the pair
@@ -215,45 +244,56 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    // global row of the first key of sub-block s (pool row for paged caches)
-    auto sub_row = [&](int s, bool *bad_page) -> int {
-        const int t0 = t_begin + s * SUB;
+    // global row of the first key of sub-block s of an item (pool row for paged caches)
+    auto sub_row = [&](const Item &it, int s, bool *bad_page) -> int {
+        const int t0 = it.t_begin + s * SUB;
         if (p.page_table) {
             const int lp = t0 / p.page_size;
-            int pg = lp < p.max_pages ? p.page_table[(size_t)g * p.max_pages + lp] : -1;
+            int pg = lp < p.max_pages ? p.page_table[(size_t)it.g * p.max_pages + lp] : -1;
             if (pg < 0 || pg >= p.num_pages) { *bad_page = true; pg = 0; }
             return pg * p.page_size + (t0 - lp * p.page_size);
         }
-        return g * p.Skv + t0;
+        return it.g * p.Skv + t0;
     };
 
+    // Every role walks the same items in the same order and keeps its own running counts of the
+    // things whose barrier phases span items: ring position, tiles (S/P/O barriers), items that
+    // loaded a Q (Q barriers), items (O-free barrier) and uses of the tail-fix barriers.
     if (warp == 0) {
         // =========================== TMA producer (both CTAs) ============================
-        bool bad = false;
-        if (n_tiles > 0) {
-            if (lane == 0) {
-                prefetch_tmap(&tmQ);
-                prefetch_tmap(&tmK);
-                prefetch_tmap(&tmV);
+        bool bad = false, ok = true;
+        const bool elected = elect_one();
+        int next_slot = 0, next_use = 0;      // ring position and how many times the ring has wrapped
+        int q_loads = 0;
+        if (lane == 0) {
+            prefetch_tmap(&tmQ);
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmV);
+        }
+#ifdef FDMLA_TRACE
+        int ptr_n = 0;
+#endif
+        for (int round = 0; round < n_rounds && ok; ++round) {
+            const int idx = item_of_round(round, cid, n_clusters);
+            if (idx >= n_items) continue;
+            const Item it = make_item(p, idx, n_row_tiles, poisoned);
+            if (it.n_tiles == 0) continue;
+            // Q of the previous item is free once its last Q K^T has completed
+            if (q_loads > 0) ok = ok && mbar_wait(BAR(B_QEMPTY), (q_loads - 1) & 1);
+            if (elected) {
                 mbar_arrive_expect_tx(BAR(B_QFULL), Q_BYTES);
-                const int qrow = g * p.R + row0 + 64 * (int)rank;
+                const int qrow = it.g * p.R + it.row0 + 64 * (int)rank;
                 tma_load_3d(smem_u32(sQ), &tmQ, 0, qrow, 0, BAR(B_QFULL));          // all 9 chunks in one copy
             }
+            ++q_loads;
             // resolve the page table for the whole key range once, with every lane of the warp
-            const int n_cached = n_sub < ROWS_CACHE ? n_sub : ROWS_CACHE;
-            for (int s = lane; s < n_cached; s += 32) s_rows[s] = sub_row(s, &bad);
+            const int n_cached = it.n_sub < ROWS_CACHE ? it.n_sub : ROWS_CACHE;
             __syncwarp();
-        }
-        auto row_of = [&](int s) -> int { return s < ROWS_CACHE ? s_rows[s] : sub_row(s, &bad); };
-        if (n_tiles > 0) {
+            for (int s = lane; s < n_cached; s += 32) s_rows[s] = sub_row(it, s, &bad);
+            __syncwarp();
+            auto row_of = [&](int s) -> int { return s < ROWS_CACHE ? s_rows[s] : sub_row(it, s, &bad); };
             // The whole warp walks the ring converged and one elected lane issues the copies (the
             // uniform datapath makes the issue several times cheaper than from a lone diverged lane).
-            const bool elected = elect_one();
-            int next_slot = 0, next_use = 0;      // ring position and how many times the ring has wrapped
-            bool ok = true;
-#ifdef FDMLA_TRACE
-            int ptr_n = 0;
-#endif
             auto take = [&](int &slot, int &use) {
                 slot = next_slot; use = next_use;
                 if (++next_slot == NSLOT) { next_slot = 0; ++next_use; }
@@ -272,11 +312,11 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         ok = ok && mbar_wait(BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
                 }
 #ifdef FDMLA_TRACE
-                if (lane == 0) TRACE(0, ptr_n);
+                if (lane == 0 && round == 0) TRACE(0, ptr_n);
                 ++ptr_n;
 #endif
                 const int s0 = 4 * t + 2 * (int)rank;
-                const int present = (s0 + 1 < n_sub) ? 2 : (s0 < n_sub ? 1 : 0);
+                const int present = (s0 + 1 < it.n_sub) ? 2 : (s0 < it.n_sub ? 1 : 0);
                 const int r0 = present > 0 ? row_of(s0) : 0, r1 = present > 1 ? row_of(s0 + 1) : 0;
                 if (elected) {
 #pragma unroll
@@ -298,7 +338,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 else if (us[1] >= 1)
                     ok = ok && mbar_wait(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
 #ifdef FDMLA_TRACE
-                if (lane == 0) TRACE(0, ptr_n);
+                if (lane == 0 && round == 0) TRACE(0, ptr_n);
                 ++ptr_n;
 #endif
                 const int s = 4 * t + q;
@@ -311,15 +351,15 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         tma_load_3d(smem_u32(sRing + sl[j] * SLOT), &tmV, 0, row, 4 * (int)rank + 2 * j, full);   // two chunks, one copy
                     }
                 }
-                const int t0 = t_begin + s * SUB;
-                if (t0 + SUB > seq) {
+                const int t0 = it.t_begin + s * SUB;
+                if (t0 + SUB > it.seq) {
                     // keys past the end of the sequence: zero their V rows once the copies have
                     // landed (whole 128-byte rows, so the swizzle does not matter)
                     ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), us[0] & 1, BAR(B_FULL + sl[1]), us[1] & 1);
-                    const int first_bad = seq > t0 ? seq - t0 : 0;
+                    const int first_bad = it.seq > t0 ? it.seq - t0 : 0;
                     const int bad_rows = SUB - first_bad;
-                    for (int idx = lane; idx < 4 * bad_rows * 8; idx += 32) {
-                        const int cc = idx / (bad_rows * 8), rem = idx - cc * bad_rows * 8;
+                    for (int idx2 = lane; idx2 < 4 * bad_rows * 8; idx2 += 32) {
+                        const int cc = idx2 / (bad_rows * 8), rem = idx2 - cc * bad_rows * 8;
                         *reinterpret_cast<uint4 *>(sRing + sl[cc >> 1] * SLOT + (cc & 1) * BOX + (first_bad + rem / 8) * 128 +
                                                    (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
                     }
@@ -329,14 +369,14 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 }
             };
             for (int g3 = 0; g3 < 3; ++g3) fill_k3(0, g3);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                if (t + 1 < n_tiles)
+            for (int t = 0; t < it.n_tiles && ok; ++t) {
+                if (t + 1 < it.n_tiles)
                     for (int g3 = 0; g3 < 3; ++g3) fill_k3(t + 1, g3);
-                const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
+                const int nq = (it.n_sub - 4 * t) < 4 ? (it.n_sub - 4 * t) : 4;
                 for (int q = 0; q < nq; ++q) fill_v2(t, q);
             }
-            if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
         }
+        if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
         if (bad) atomicCAS(&g_tc_error, 0, ERR_PAGE);
         __syncwarp();
     } else if (warp == 1) {
@@ -345,41 +385,60 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             // The whole warp runs this loop converged and one elected lane issues: that keeps the
             // descriptor arithmetic on the uniform datapath, which is what lets tcgen05.mma issue at
             // full rate (a single diverged lane issuing the same sequence is about half as fast).
-            if (n_tiles > 0) {
-                const bool elected = elect_one();
-                constexpr uint32_t idesc_qk = make_idesc_bf16(128, 256, 0, 0);
-                constexpr uint32_t idesc_pv = make_idesc_bf16(128, 256, 0, 1);
-                const uint64_t q_desc = make_smem_desc(smem_u32(sQ), 16, 1024, kLayoutSw128);
-                const uint64_t rk_desc = make_smem_desc(smem_u32(sRing), 16, 1024, kLayoutSw128);    // ring slot as K-major B
-                const uint64_t rv_desc = make_smem_desc(smem_u32(sRing), BOX, 1024, kLayoutSw128);   // ring slot as MN-major B
-                const uint64_t p_desc = make_smem_desc(smem_u32(sP), 128, P_SBO, kLayoutNone);
-                bool ok = mbar_wait(BAR(B_QFULL), 0) && mbar_wait(BAR(B_PEER_QFULL), 0);
+            const bool elected = elect_one();
+            constexpr uint32_t idesc_qk = make_idesc_bf16(128, 256, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_bf16(128, 256, 0, 1);
+            const uint64_t q_desc = make_smem_desc(smem_u32(sQ), 16, 1024, kLayoutSw128);
+            const uint64_t rk_desc = make_smem_desc(smem_u32(sRing), 16, 1024, kLayoutSw128);    // ring slot as K-major B
+            const uint64_t rv_desc = make_smem_desc(smem_u32(sRing), BOX, 1024, kLayoutSw128);   // ring slot as MN-major B
+            const uint64_t p_desc = make_smem_desc(smem_u32(sP), 128, P_SBO, kLayoutNone);
+            bool ok = true;
+            int slot = 0;               // ring position (the same in every lane) and its phase
+            uint32_t ph = 0;
+            int tg0 = 0;                // tiles of the items before the current one
+            int q_loads = 0, items_done = 0, fix_uses = 0;     // items_done: items that used the accumulator
 #ifdef FDMLA_TRACE
-                int ntr = 0;
+            int ntr = 0;
 #endif
-                int slot = 0;               // ring position (the same in every lane) and its phase
-                uint32_t ph = 0;
-                auto take = [&](int &sl, uint32_t &p) {
-                    sl = slot; p = ph;
+            for (int round = 0; round < n_rounds; ++round) {
+                const int idx = item_of_round(round, cid, n_clusters);
+                if (idx >= n_items) continue;
+                if (!__all_sync(0xffffffffu, ok)) break;
+                const Item it = make_item(p, idx, n_row_tiles, poisoned);
+                if (it.n_tiles == 0) continue;       // nothing to multiply; the softmax warps write the empty result
+                // The accumulator is needed again only after the softmax warps of both CTAs have read the
+                // previous item's O out of tensor memory.
+                bool o_free_waited = items_done == 0;
+                auto wait_o_free = [&]() {
+                    if (!o_free_waited) {
+                        ok = ok && mbar_wait(BAR(B_OFREE), (items_done - 1) & 1);
+                        tc_fence_after_sync();
+                        o_free_waited = true;
+                    }
+                };
+                ok = ok && mbar_wait(BAR(B_QFULL), q_loads & 1) && mbar_wait(BAR(B_PEER_QFULL), q_loads & 1);
+                ++q_loads;
+                auto take = [&](int &sl, uint32_t &pp) {
+                    sl = slot; pp = ph;
                     if (++slot == NSLOT) { slot = 0; ph ^= 1; }
                 };
                 // S = Q K^T: chunks 3*g3 .. 3*g3+2 of K tile tk, three ring slots waited for together
                 auto k_group = [&](int tk, int g3) {
-                    const int b = tk & 1;
+                    const int tg = tg0 + tk, b = tg & 1;
                     int sl[3];
                     uint32_t phs[3];
                     for (int i = 0; i < 3; ++i) take(sl[i], phs[i]);
                     if (g3 == 0) {
-                        // S[b] was last read by the softmax of tile tk-2
-                        if (tk >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tk / 2) - 1) & 1);
+                        // S[b] was last read by the softmax of the tile two before
+                        if (tg >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tg / 2) - 1) & 1);
                         tc_fence_after_sync();
                     }
 #ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(1, ntr);
+                    if (lane == 0 && round == 0) TRACE(1, ntr);
 #endif
                     ok = ok && mbar_wait3(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1], BAR(B_FULL + sl[2]), phs[2]);
 #ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(2, ntr);
+                    if (lane == 0 && round == 0) TRACE(2, ntr);
                     ++ntr;
 #endif
                     if (elected) {
@@ -390,28 +449,33 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                                       rk_desc + (uint32_t)sl[i] * (SLOT >> 4), 2, 2, idesc_qk, c != 0);
                             mma_commit_2cta(BAR(B_EMPTY + sl[i]), 3);
                         }
-                        if (g3 == 2) mma_commit_2cta(BAR(B_SFULL + b), 3);
+                        if (g3 == 2) {
+                            mma_commit_2cta(BAR(B_SFULL + b), 3);
+                            if (tk == it.n_tiles - 1) mma_commit_2cta(BAR(B_QEMPTY), 3);   // last use of this item's Q
+                        }
                     }
                 };
                 // O += P V: quarter q of tile t, both halves j of this CTA's d_v columns
                 auto v_pair = [&](int t, int q, bool last) {
+                    const int tg = tg0 + t;
                     int sl[2];
                     uint32_t phs[2];
                     for (int j = 0; j < 2; ++j) take(sl[j], phs[j]);
 #ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(1, ntr);
+                    if (lane == 0 && round == 0) TRACE(1, ntr);
 #endif
-                    ok = ok && mbar_wait(BAR(B_PFULL + q), t & 1);
+                    ok = ok && mbar_wait(BAR(B_PFULL + q), tg & 1);
                     tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
 #ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(4, ntr);
+                    if (lane == 0 && round == 0) TRACE(4, ntr);
 #endif
                     ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1]);
 #ifdef FDMLA_TRACE
-                    if (lane == 0) TRACE(2, ntr);
+                    if (lane == 0 && round == 0) TRACE(2, ntr);
                     ++ntr;
 #endif
-                    if (t_begin + (4 * t + q) * SUB + SUB > seq) ok = ok && mbar_wait2(BAR(B_FIX), 0, BAR(B_FIX + 1), 0);
+                    if (it.t_begin + (4 * t + q) * SUB + SUB > it.seq)
+                        ok = ok && mbar_wait2(BAR(B_FIX), fix_uses & 1, BAR(B_FIX + 1), fix_uses & 1);
                     if (elected) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
@@ -419,251 +483,277 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                                       16, 128, idesc_pv, (t | q) != 0);
                             mma_commit_2cta(BAR(B_EMPTY + sl[j]), 3);
                         }
-                        if (last) mma_commit_2cta(BAR(B_OREADY + (t & 1)), 3);   // tile t folded into O
+                        if (last) mma_commit_2cta(BAR(B_OREADY + (tg & 1)), 3);   // tile t folded into O
                     }
                 };
 #pragma unroll
                 for (int g3 = 0; g3 < 3; ++g3) k_group(0, g3);
 #pragma unroll 1
-                for (int t = 0; t < n_tiles; ++t) {
+                for (int t = 0; t < it.n_tiles; ++t) {
                     if (!__all_sync(0xffffffffu, ok)) break;
-                    const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;
-                    if (t + 1 < n_tiles) {
+                    const int nq = (it.n_sub - 4 * t) < 4 ? (it.n_sub - 4 * t) : 4;
+                    if (t + 1 < it.n_tiles) {
 #pragma unroll
                         for (int g3 = 0; g3 < 3; ++g3) k_group(t + 1, g3);
                     }
+                    if (t == 0) wait_o_free();     // the first P V of the item overwrites O
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
                         if (q < nq) v_pair(t, q, q == nq - 1);
                 }
-                if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_MMA);
+                tg0 += it.n_tiles;
+                fix_uses += it.fix ? 1 : 0;
+                ++items_done;
             }
+            if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_MMA);
         } else {
             // =========================== load relay (peer CTA) ===========================
             // (converged warp, one elected lane signals: see the MMA issuer)
-            if (n_tiles > 0) {
-                const bool elected = elect_one();
-                bool ok = mbar_wait(BAR(B_QFULL), 0);
+            const bool elected = elect_one();
+            const uint32_t peer_base = map_to_cta(BAR(B_FULL), 0);
+            int slot = 0, use = 0, q_loads = 0, fix_uses = 0;
+            bool ok = true;
+            for (int round = 0; round < n_rounds && ok; ++round) {
+                const int idx = item_of_round(round, cid, n_clusters);
+                if (idx >= n_items) continue;
+                const Item it = make_item(p, idx, n_row_tiles, poisoned);
+                if (it.n_tiles == 0) continue;
+                ok = mbar_wait(BAR(B_QFULL), q_loads & 1);
+                ++q_loads;
                 if (ok && elected) mbar_arrive_cluster_relaxed(map_to_cta(BAR(B_PEER_QFULL), 0));
-                const uint32_t peer_base = map_to_cta(BAR(B_FULL), 0);
-                int slot = 0, use = 0;
-                ok = ok && walk_slots(n_tiles, n_sub, [&](bool is_v, int t, int a, int j) -> bool {
+                ok = ok && walk_slots(it.n_tiles, it.n_sub, [&](bool is_v, int t, int a, int j) -> bool {
                     if (!mbar_wait(BAR(B_FULL + slot), use & 1)) return false;
-                    if (is_v && t_begin + (4 * t + a) * SUB + SUB > seq && !mbar_wait(BAR(B_FIX + j), 0)) return false;
+                    if (is_v && it.t_begin + (4 * t + a) * SUB + SUB > it.seq && !mbar_wait(BAR(B_FIX + j), fix_uses & 1)) return false;
                     if (elected) mbar_arrive_cluster_relaxed(peer_base + 8u * slot);
                     if (++slot == NSLOT) { slot = 0; ++use; }
                     return true;
                 });
-                if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_RELAY);
+                fix_uses += it.fix ? 1 : 0;
             }
+            if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_RELAY);
         }
         __syncwarp();
     } else {
         // =========================== softmax + epilogue (both CTAs) ========================
         const int L = (warp & 3) * 32 + lane;          // TMEM lane owned by this thread
         const int row = L & 63, half = L >> 6;         // key half: keys [128 half, +128) of every tile
-        const int rr = row0 + 64 * (int)rank + row;
-        const bool row_ok = rr < p.R;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        int upper = lo;
-        if (row_ok) {
-            long long vis = seq;
-            if (p.causal) {
-                vis = (long long)(rr % p.Sq) + seq - p.Sq + 1;
-                vis = vis < 0 ? 0 : (vis > seq ? seq : vis);
-            }
-            upper = (int)(vis < hi ? vis : hi);
-            if (upper < lo) upper = lo;
-        }
         const float sl2 = p.scale * 1.4426950408889634f;
-        float m_true = -CUDART_INF_F, m_ref = -CUDART_INF_F, l_run = 0.f;   // l_run: this thread's key half only
         const uint32_t pfull_leader = map_to_cta(BAR(B_PFULL), 0);
         const uint32_t sempty_leader = map_to_cta(BAR(B_SEMPTY), 0);
-        bool ok = true;
-        uint32_t r[32];
+        const uint32_t ofree_leader = map_to_cta(BAR(B_OFREE), 0);
         const bool do_prefetch = p.Sq == 1;     // decode streams the cache from HBM; prefill finds it in L2 anyway
-        for (int t = 0; t < n_tiles; ++t) {
-            const int b = t & 1, tok0 = t_begin + t * T + 128 * half;
-            const uint32_t s_addr = tmem + lane_base + S_COL0 + b * S_COLS;
-            // after a failed wait the loop keeps running without further waits so that the
-            // named barriers below stay matched across the softmax threads
-            if (L == 0) TRACE(3, t * 8 + 0);
-            if (PF_DIST > 0 && do_prefetch) {
-                // While this thread would only wait for S: pull one cache row of a later tile into L2.
-                // The 128 softmax threads of the CTA cover the CTA's own 128 keys of that tile (the
-                // pair covers the tile), so the TMA copies issued PF_DIST tiles from now hit L2 and
-                // the ring only has to hide the L2 latency, not the HBM latency.
-                for (int tp = (t == 0 ? 1 : t + PF_DIST); tp <= t + PF_DIST; ++tp) {
-                    const int s = 4 * tp + 2 * (int)rank + half;
-                    if (s < n_sub && t_begin + s * SUB + row < blk_hi) {
-                        bool bad_page = false;
-                        const char *src = static_cast<const char *>(p.K) + ((size_t)sub_row(s, &bad_page) + row) * (NQC * 128);
-                        if (!bad_page) {
+        bool ok = true;
+        int tg0 = 0;                            // tiles of the items before the current one
+        uint32_t r[32];
+        for (int round = 0; round < n_rounds; ++round) {
+            const int idx = item_of_round(round, cid, n_clusters);
+            if (idx >= n_items) continue;
+            const Item it = make_item(p, idx, n_row_tiles, poisoned);
+            const int rr = it.row0 + 64 * (int)rank + row;
+            const bool row_ok = rr < p.R;
+            const int lo = it.lo, hi = it.hi, seq = it.seq, n_tiles = it.n_tiles;
+            int upper = lo;
+            if (row_ok) {
+                long long vis = seq;
+                if (p.causal) {
+                    vis = (long long)(rr % p.Sq) + seq - p.Sq + 1;
+                    vis = vis < 0 ? 0 : (vis > seq ? seq : vis);
+                }
+                upper = (int)(vis < hi ? vis : hi);
+                if (upper < lo) upper = lo;
+            }
+            float m_true = -CUDART_INF_F, m_ref = -CUDART_INF_F, l_run = 0.f;   // l_run: this thread's key half only
+            for (int t = 0; t < n_tiles; ++t) {
+                const int tg = tg0 + t, b = tg & 1, tok0 = it.t_begin + t * T + 128 * half;
+                const uint32_t s_addr = tmem + lane_base + S_COL0 + b * S_COLS;
+                // after a failed wait the loop keeps running without further waits so that the
+                // named barriers below stay matched across the softmax threads
+                if (L == 0 && round == 0) TRACE(3, t * 8 + 0);
+                if (PF_DIST > 0 && do_prefetch) {
+                    // While this thread would only wait for S: pull one cache row of a later tile into L2.
+                    // The 128 softmax threads of the CTA cover the CTA's own 128 keys of that tile (the
+                    // pair covers the tile), so the TMA copies issued PF_DIST tiles from now hit L2 and
+                    // the ring only has to hide the L2 latency, not the HBM latency.
+                    for (int tp = (t == 0 ? 1 : t + PF_DIST); tp <= t + PF_DIST; ++tp) {
+                        const int s = 4 * tp + 2 * (int)rank + half;
+                        if (s < it.n_sub && it.t_begin + s * SUB + row < it.blk_hi) {
+                            bool bad_page = false;
+                            const char *src = static_cast<const char *>(p.K) + ((size_t)sub_row(it, s, &bad_page) + row) * (NQC * 128);
+                            if (!bad_page) {
 #pragma unroll
-                            for (int c = 0; c < NQC; ++c) prefetch_l2(src + c * 128);
+                                for (int c = 0; c < NQC; ++c) prefetch_l2(src + c * 128);
+                            }
                         }
                     }
                 }
-            }
-            if (ok) ok = mbar_wait(BAR(B_SFULL + b), (t / 2) & 1);
-            if (L == 0) TRACE(3, t * 8 + 1);
-            tc_fence_after_sync();
-            // pass 1: maximum of this thread's 128 keys (no per-key masking when all are visible)
-            const bool all_visible = tok0 >= lo && tok0 + 128 <= upper && sl2 > 0.f;
-            float tmax = -CUDART_INF_F;
+                if (ok) ok = mbar_wait(BAR(B_SFULL + b), (tg / 2) & 1);
+                if (L == 0 && round == 0) TRACE(3, t * 8 + 1);
+                tc_fence_after_sync();
+                // pass 1: maximum of this thread's 128 keys (no per-key masking when all are visible)
+                const bool all_visible = tok0 >= lo && tok0 + 128 <= upper && sl2 > 0.f;
+                float tmax = -CUDART_INF_F;
 #pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                tmem_ld32(s_addr + cc * 32, r);
-                tmem_wait_ld();
-                if (all_visible) {
+                for (int cc = 0; cc < 4; ++cc) {
+                    tmem_ld32(s_addr + cc * 32, r);
+                    tmem_wait_ld();
+                    if (all_visible) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(r[j]));
-                } else {
+                        for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(r[j]));
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int tok = tok0 + cc * 32 + j;
-                        if (tok >= lo && tok < upper) tmax = fmaxf(tmax, __uint_as_float(r[j]) * sl2);
+                        for (int j = 0; j < 32; ++j) {
+                            const int tok = tok0 + cc * 32 + j;
+                            if (tok >= lo && tok < upper) tmax = fmaxf(tmax, __uint_as_float(r[j]) * sl2);
+                        }
                     }
                 }
+                if (all_visible) tmax *= sl2;     // fast path took the maximum of the raw scores (sl2 > 0)
+                // the row's other key half lives in the thread 64 lanes away
+                red[(tg & 1) * 128 + L] = tmax;
+                named_bar_sync(1, 128);
+                if (L == 0 && round == 0) TRACE(3, t * 8 + 2);
+                tmax = fmaxf(tmax, red[(tg & 1) * 128 + (L ^ 64)]);
+                const float m_new = fmaxf(m_true, tmax);
+                const bool need = m_new > m_ref + 8.f;
+                // P*V of tile t-1 must be complete before its P is overwritten or O rescaled
+                if (t > 0) {
+                    if (ok) ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1);
+                    tc_fence_after_sync();
+                }
+                if (__any_sync(0xffffffffu, need)) {
+                    float alpha = 1.f;
+                    if (need) {
+                        alpha = (m_ref == -CUDART_INF_F) ? 0.f : fast_exp2(m_ref - m_new);
+                        l_run *= alpha;
+                        m_ref = m_new;
+                    }
+                    if (t > 0) {
+                        uint32_t o[32];
+#pragma unroll 1
+                        for (int cc = 0; cc < O_COLS / 32; ++cc) {
+                            tmem_ld32(tmem + lane_base + cc * 32, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                            tmem_st32(tmem + lane_base + cc * 32, o);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                m_true = m_new;
+                if (L == 0 && round == 0) TRACE(3, t * 8 + 3);
+                // pass 2: P = 2^(s - m_ref), quarter by quarter (this half owns quarters 2*half, 2*half+1)
+                float lsum = 0.f;
+#pragma unroll 1
+                for (int cc = 0; cc < 4; ++cc) {
+                    tmem_ld32(s_addr + cc * 32, r);
+                    tmem_wait_ld();
+                    uint32_t packed[16];
+                    if (all_visible) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_ref));
+                            const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), sl2, -m_ref));
+                            lsum += p0 + p1;
+                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const int tok = tok0 + cc * 32 + j;
+                            const float p0 = (tok >= lo && tok < upper) ? fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_ref)) : 0.f;
+                            const float p1 = (tok + 1 >= lo && tok + 1 < upper) ? fast_exp2(fmaf(__uint_as_float(r[j + 1]), sl2, -m_ref)) : 0.f;
+                            lsum += p0 + p1;
+                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                        }
+                    }
+                    const int quarter = 2 * half + (cc >> 1);
+                    uint8_t *prow = sP + quarter * P_Q + (row >> 3) * P_SBO + (row & 7) * 16 + (cc & 1) * 4 * 128;
+#pragma unroll
+                    for (int kc = 0; kc < 4; ++kc)
+                        *reinterpret_cast<uint4 *>(prow + kc * 128) =
+                            make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
+                    if (cc & 1) {
+                        // quarter complete in this CTA once the 64 threads of this key half have written it
+                        tc_fence_before_sync();
+                        fence_proxy_async_smem();
+                        named_bar_sync(2 + half, 64);
+                        if (L == 0 && round == 0) TRACE(3, t * 8 + 4 + (cc >> 1));
+                        if (row == 0) {
+                            // (relaxed: the 64 writers have fenced their stores towards the async proxy and
+                            // met at the named barrier; the arrival itself carries no data)
+                            mbar_arrive_cluster_relaxed(pfull_leader + 8u * quarter);
+                            if (cc == 3) mbar_arrive_cluster_relaxed(sempty_leader + 8u * b);   // this half is done with S[b]
+                        }
+                    }
+                }
+                l_run += lsum;
             }
-            if (all_visible) tmax *= sl2;     // fast path took the maximum of the raw scores (sl2 > 0)
-            // the row's other key half lives in the thread 64 lanes away
-            red[(t & 1) * 128 + L] = tmax;
-            named_bar_sync(1, 128);
-            if (L == 0) TRACE(3, t * 8 + 2);
-            tmax = fmaxf(tmax, red[(t & 1) * 128 + (L ^ 64)]);
-            const float m_new = fmaxf(m_true, tmax);
-            const bool need = m_new > m_ref + 8.f;
-            // P*V of tile t-1 must be complete before its P is overwritten or O rescaled
-            if (t > 0) {
-                if (ok) ok = mbar_wait(BAR(B_OREADY + ((t - 1) & 1)), ((t - 1) / 2) & 1);
+            if (ok && n_tiles > 0) {
+                const int tl = tg0 + n_tiles - 1;
+                ok = mbar_wait(BAR(B_OREADY + (tl & 1)), (tl / 2) & 1);
                 tc_fence_after_sync();
             }
-            if (__any_sync(0xffffffffu, need)) {
-                float alpha = 1.f;
-                if (need) {
-                    alpha = (m_ref == -CUDART_INF_F) ? 0.f : fast_exp2(m_ref - m_new);
-                    l_run *= alpha;
-                    m_ref = m_new;
-                }
-                if (t > 0) {
-                    uint32_t o[32];
+            tg0 += n_tiles;
+            // row sum = both key halves
+            named_bar_sync(1, 128);
+            red[L] = l_run;
+            named_bar_sync(1, 128);
+            const float l_tot = l_run + red[L ^ 64];
+            // ---- epilogue: thread L writes row `row`, d_v columns [256*half, 256*half + 256) ----
+            const bool have = ok && n_tiles > 0 && l_tot > 0.f;
+            const float inv = have ? 1.f / l_tot : 0.f;
+            const bool final_out = (p.num_splits == 1 && p.O != nullptr);
+            const size_t grow = (size_t)it.g * p.R + (row_ok ? rr : 0);
+            const size_t prow_idx = (size_t)it.split * p.G * p.R + grow;
+            const int col0 = 256 * half;
 #pragma unroll 1
-                    for (int cc = 0; cc < O_COLS / 32; ++cc) {
-                        tmem_ld32(tmem + lane_base + cc * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-                        tmem_st32(tmem + lane_base + cc * 32, o);
-                    }
-                    tmem_wait_st();
+            for (int cc = 0; cc < O_COLS / 32; ++cc) {
+                uint32_t o[32];
+                if (n_tiles > 0 && ok) {
+                    tmem_ld32(tmem + lane_base + cc * 32, o);
+                    tmem_wait_ld();
                 }
-            }
-            m_true = m_new;
-            if (L == 0) TRACE(3, t * 8 + 3);
-            // pass 2: P = 2^(s - m_ref), quarter by quarter (this half owns quarters 2*half, 2*half+1)
-            float lsum = 0.f;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                tmem_ld32(s_addr + cc * 32, r);
-                tmem_wait_ld();
-                uint32_t packed[16];
-                if (all_visible) {
+                if (!row_ok) continue;
+                if (final_out) {
+                    __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + grow * p.d_v + col0 + cc * 32;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_ref));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), sl2, -m_ref));
-                        lsum += p0 + p1;
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                    for (int j = 0; j < 32; j += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float a = have ? __uint_as_float(o[j + 2 * e]) * inv : 0.f;
+                            const float c = have ? __uint_as_float(o[j + 2 * e + 1]) * inv : 0.f;
+                            __nv_bfloat162 h = __floats2bfloat162_rn(a, c);
+                            w[e] = *reinterpret_cast<uint32_t *>(&h);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 } else {
+                    float *dst = p.O_part + prow_idx * p.d_v + col0 + cc * 32;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const int tok = tok0 + cc * 32 + j;
-                        const float p0 = (tok >= lo && tok < upper) ? fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_ref)) : 0.f;
-                        const float p1 = (tok + 1 >= lo && tok + 1 < upper) ? fast_exp2(fmaf(__uint_as_float(r[j + 1]), sl2, -m_ref)) : 0.f;
-                        lsum += p0 + p1;
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
-                    }
-                }
-                const int quarter = 2 * half + (cc >> 1);
-                uint8_t *prow = sP + quarter * P_Q + (row >> 3) * P_SBO + (row & 7) * 16 + (cc & 1) * 4 * 128;
-#pragma unroll
-                for (int kc = 0; kc < 4; ++kc)
-                    *reinterpret_cast<uint4 *>(prow + kc * 128) =
-                        make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
-                if (cc & 1) {
-                    // quarter complete in this CTA once the 64 threads of this key half have written it
-                    tc_fence_before_sync();
-                    fence_proxy_async_smem();
-                    named_bar_sync(2 + half, 64);
-                    if (L == 0) TRACE(3, t * 8 + 4 + (cc >> 1));
-                    if (row == 0) {
-                        // (relaxed: the 64 writers have fenced their stores towards the async proxy and
-                        // met at the named barrier; the arrival itself carries no data)
-                        mbar_arrive_cluster_relaxed(pfull_leader + 8u * quarter);
-                        if (cc == 3) mbar_arrive_cluster_relaxed(sempty_leader + 8u * b);   // this half is done with S[b]
-                    }
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4 *>(dst + j) =
+                            make_float4(have ? __uint_as_float(o[j]) * inv : 0.f, have ? __uint_as_float(o[j + 1]) * inv : 0.f,
+                                        have ? __uint_as_float(o[j + 2]) * inv : 0.f, have ? __uint_as_float(o[j + 3]) * inv : 0.f);
                 }
             }
-            l_run += lsum;
-        }
-        if (ok && n_tiles > 0) {
-            ok = mbar_wait(BAR(B_OREADY + ((n_tiles - 1) & 1)), ((n_tiles - 1) / 2) & 1);
-            tc_fence_after_sync();
+            if (row_ok && half == 0) {
+                const float m_out = have ? m_true * 0.6931471805599453f : -CUDART_INF_F;
+                const float l_out = have ? l_tot * fast_exp2(m_ref - m_true) : 0.f;
+                if (final_out) { p.m[grow] = m_out; p.l[grow] = l_out; }
+                else { p.m_part[prow_idx] = m_out; p.l_part[prow_idx] = l_out; }
+            }
+            // this CTA's softmax warps have read O out of tensor memory: the next item may overwrite it
+            // (an empty item never touched the accumulator and signals nothing)
+            tc_fence_before_sync();
+            named_bar_sync(1, 128);
+            if (L == 0 && n_tiles > 0) mbar_arrive_cluster_relaxed(ofree_leader);
         }
         if (!ok) atomicCAS(&g_tc_error, 0, ERR_SOFTMAX);
-        // row sum = both key halves
-        named_bar_sync(1, 128);
-        red[L] = l_run;
-        named_bar_sync(1, 128);
-        const float l_tot = l_run + red[L ^ 64];
-        // ---- epilogue: thread L writes row `row`, d_v columns [256*half, 256*half + 256) ----
-        const bool have = ok && n_tiles > 0 && l_tot > 0.f;
-        const float inv = have ? 1.f / l_tot : 0.f;
-        const bool final_out = (p.num_splits == 1 && p.O != nullptr);
-        const size_t grow = (size_t)g * p.R + (row_ok ? rr : 0);
-        const size_t prow_idx = (size_t)split * p.G * p.R + grow;
-        const int col0 = 256 * half;
-#pragma unroll 1
-        for (int cc = 0; cc < O_COLS / 32; ++cc) {
-            uint32_t o[32];
-            if (n_tiles > 0 && ok) {
-                tmem_ld32(tmem + lane_base + cc * 32, o);
-                tmem_wait_ld();
-            }
-            if (!row_ok) continue;
-            if (final_out) {
-                __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + grow * p.d_v + col0 + cc * 32;
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float a = have ? __uint_as_float(o[j + 2 * e]) * inv : 0.f;
-                        const float c = have ? __uint_as_float(o[j + 2 * e + 1]) * inv : 0.f;
-                        __nv_bfloat162 h = __floats2bfloat162_rn(a, c);
-                        w[e] = *reinterpret_cast<uint32_t *>(&h);
-                    }
-                    *reinterpret_cast<uint4 *>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-            } else {
-                float *dst = p.O_part + prow_idx * p.d_v + col0 + cc * 32;
-#pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4 *>(dst + j) =
-                        make_float4(have ? __uint_as_float(o[j]) * inv : 0.f, have ? __uint_as_float(o[j + 1]) * inv : 0.f,
-                                    have ? __uint_as_float(o[j + 2]) * inv : 0.f, have ? __uint_as_float(o[j + 3]) * inv : 0.f);
-            }
-        }
-        if (row_ok && half == 0) {
-            const float m_out = have ? m_true * 0.6931471805599453f : -CUDART_INF_F;
-            const float l_out = have ? l_tot * fast_exp2(m_ref - m_true) : 0.f;
-            if (final_out) { p.m[grow] = m_out; p.l[grow] = l_out; }
-            else { p.m_part[prow_idx] = m_out; p.l_part[prow_idx] = l_out; }
-        }
     }
 
     // ---- teardown: neither CTA may leave while the pair can still touch its memory --------
@@ -690,11 +780,40 @@ extern "C" int fdmla_trace_fetch(long long *dst, int max_elems) {
 }
 #endif
 
+namespace tc2 {
+// CTA pairs of fwd_tc2_kernel that are resident at the same time on the current device (cached per device).
+static int resident_clusters() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (cached[dev] > 0) return cached[dev];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 148);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, fwd_tc2_kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) return -1;
+        n = sms / 2;
+    }
+    cached[dev] = n;
+    return n;
+}
+}  // namespace tc2
+
 bool fwd_tensor2_supported(const FwdProblem &p, int dtype) {
     if (dtype != FDMLA_BF16) return false;
     if (p.d_qk != 576 || p.d_v != 512 || p.V != nullptr) return false;
     if (p.page_table && (p.page_size % tc2::SUB) != 0) return false;
-    if (p.G <= 0 || p.R <= 0 || p.G > 65535 || p.num_splits > 65535) return false;
+    if (p.G <= 0 || p.R <= 0 || p.num_splits <= 0) return false;
+    if ((long long)((p.R + 127) / 128) * p.G * p.num_splits > 2147483647LL) return false;
     const long long kv_rows = p.page_table ? (long long)p.num_pages * p.page_size : (long long)p.G * p.Skv;
     if (kv_rows <= 0 || kv_rows > 2147483647LL || (long long)p.G * p.R > 2147483647LL) return false;
     if ((reinterpret_cast<uintptr_t>(p.Q) | reinterpret_cast<uintptr_t>(p.K)) & 15) return false;
@@ -710,8 +829,13 @@ int launch_fwd_tensor2(const FwdProblem &p, cudaStream_t stream) {
     if (!make_tensor_map_bf16(&tmK, p.K, kv_rows, p.d_qk, 64)) return FDMLA_ERR_CUDA;
     if (cudaFuncSetAttribute(tc2::fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES) != cudaSuccess)
         return FDMLA_ERR_CUDA;
-    dim3 grid(((p.R + 127) / 128) * 2, p.G, p.num_splits);
-    tc2::fwd_tc2_kernel<<<grid, tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
+    // persistent grid: as many CTA pairs as the device keeps resident at once (one CTA per SM), each
+    // walking its share of the (row tile, KV group, split) items
+    const long long n_items = (long long)((p.R + 127) / 128) * p.G * p.num_splits;
+    const int resident = tc2::resident_clusters();
+    if (resident <= 0) return FDMLA_ERR_CUDA;
+    const int n_clusters = n_items < resident ? (int)n_items : resident;
+    tc2::fwd_tc2_kernel<<<dim3(2 * n_clusters), tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
     return check_launch();
 }
 
