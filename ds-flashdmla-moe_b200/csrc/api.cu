@@ -1,6 +1,7 @@
 // extern "C" entry points of libflashdmla.so: argument checks, problem
 // set-up and dispatch to the tcgen05 or the portable kernels.  Nothing here
 // allocates or synchronises; every scratch buffer comes from the caller.
+#include <cmath>
 #include "common.cuh"
 
 #include <atomic>
@@ -165,8 +166,24 @@ int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,
         if (s > 1) cost += 0.75 + 0.02 * s * (double)waves;   // merge launch + partial traffic
         if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
+    if (mla && H <= 128 && (int)tiles >= 1) {
+        // Balanced schedule of the 2-CTA kernel: the tiles of all sequences are dealt out in equal
+        // contiguous runs, so the cost is the run length plus one pipeline fill, the merge launch and
+        // the partials of the sequences that get cut (at most one per CTA pair; together about seven
+        // tile times on a B200).  The slabs only bound how often one sequence may be cut.
+        const double run = std::ceil((double)B * tiles / units);
+        int slabs = (int)std::ceil(tiles / run) + 1;
+        if (slabs < 2) slabs = 2;
+        if (slabs > 64) slabs = 64;
+        const double run_eff = std::fmax(run, std::ceil(tiles / (slabs - 1)));
+        const double cost = run_eff + 1.5 + 7.0;     // + merge launch and partial traffic, measured ~25 us
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = slabs; }
+    }
     return best;
 }
+
+static int g_decode_merge = 1;
+void fdmla_set_decode_merge(int on) { g_decode_merge = on ? 1 : 0; }
 
 int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_table,
                        const int32_t *seqlens, void *O, float *m, float *l, float *O_part,
@@ -191,9 +208,18 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_t
     p.G = B; p.R = H; p.Sq = 1; p.Skv = max_pages * page_size; p.d_qk = d_qk; p.d_v = d_v;
     p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages;
     p.num_splits = num_splits; p.kv_begin = kv_begin; p.kv_end = kv_end; p.causal = 0; p.scale = scale;
+    if (!partial_only && num_splits >= 2 && kv_begin <= 0 && kv_end < 0 && H <= 128) {
+        // A final result is wanted and there are spare slabs: the 2-CTA tensor kernel may hand out the
+        // keys as balanced runs of tiles instead of num_splits equal pieces of every sequence (other
+        // kernels ignore the hint).  It writes uncut sequences straight to O, so it needs O.
+        const int nt_max = (max_pages * page_size + 255) / 256;
+        p.balanced = 1;
+        p.quota_min = (nt_max + num_splits - 2) / (num_splits - 1);
+        p.O = O;
+    }
     int rc = run_forward(p, dtype, st);
     if (rc) return rc;
-    if (num_splits > 1 && !partial_only)
+    if (num_splits > 1 && !partial_only && g_decode_merge)
         rc = launch_merge(O_part, m_part, l_part, O, m, l, (long long)B * H, d_v, num_splits, dtype, st);
     return rc;
 }

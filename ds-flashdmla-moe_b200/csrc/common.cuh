@@ -58,6 +58,9 @@ struct FwdProblem {
     int kv_begin, kv_end;     // attended token window (kv_end < 0: unlimited)
     int causal;
     float scale;
+    // Balanced decode schedule of the 2-CTA tensor kernel (0 = off): keys are handed out as contiguous
+    // runs of 256-key tiles, at least quota_min per CTA pair; num_splits then counts the partial slabs.
+    int balanced, quota_min;
 };
 
 // Token range [lo, hi) of split `s` for a group whose attended window is

@@ -230,50 +230,73 @@ int launch_fwd_portable(const FwdProblem &p, int dtype, cudaStream_t stream) {
 }
 
 // ---------------------------------------------------------------------------
-// Log-sum-exp merge of partials: one block per row, threads over columns.
+// Log-sum-exp merge of partials: one warp per row, rows strided over a grid that
+// fills the GPU once.
 // m = max m_p; w_p = l_p exp(m_p - m); l = sum w_p; O = sum w_p O_p / l
 // (the running update of fa2_fwd.cu:93-111 applied across partial results).
+// Parts with l_p <= 0 hold nothing and are not read.  l_part[0][row] < 0 marks a
+// row whose final O, m, l have already been written (balanced decode schedule):
+// it is left alone.
 // ---------------------------------------------------------------------------
 template <typename TO>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 merge_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
              const float *__restrict__ l_part, TO *__restrict__ O, float *__restrict__ m,
              float *__restrict__ l, long long rows, int d_v, int P) {
-    const long long r = blockIdx.x;
-    float mx = -CUDART_INF_F;
-    for (int q = 0; q < P; ++q)
-        if (l_part[q * rows + r] > 0.f) mx = fmaxf(mx, m_part[q * rows + r]);
-    float ls = 0.f;
-    for (int q = 0; q < P; ++q) {
-        float lp = l_part[q * rows + r];
-        if (lp > 0.f) ls += lp * __expf(m_part[q * rows + r] - mx);
-    }
-    const float inv = ls > 0.f ? 1.f / ls : 0.f;
-    for (int c = threadIdx.x; c < d_v; c += blockDim.x) {
-        float acc = 0.f;
-        for (int q = 0; q < P; ++q) {
-            float lp = l_part[q * rows + r];
-            if (lp > 0.f) {
-                float w = lp * __expf(m_part[q * rows + r] - mx) * inv;
-                acc = fmaf(w, O_part[((size_t)q * rows + r) * d_v + c], acc);
-            }
+    const int lane = threadIdx.x & 31;
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+        if (l_part[r] < 0.f) continue;
+        float mx = -CUDART_INF_F;
+        for (int q = lane; q < P; q += 32)
+            if (l_part[q * rows + r] > 0.f) mx = fmaxf(mx, m_part[q * rows + r]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float ls = 0.f;
+        for (int q = lane; q < P; q += 32) {
+            const float lp = l_part[q * rows + r];
+            if (lp > 0.f) ls += lp * __expf(m_part[q * rows + r] - mx);
         }
-        O[(size_t)r * d_v + c] = from_f32<TO>(acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+        const float inv = ls > 0.f ? 1.f / ls : 0.f;
+        for (int c0 = 0; c0 < d_v; c0 += 128) {
+            const int c = c0 + lane * 4;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < P; ++q) {
+                const float lp = l_part[q * rows + r];         // same address in every lane
+                if (lp > 0.f) {
+                    const float w = lp * __expf(m_part[q * rows + r] - mx) * inv;
+                    const float *src = O_part + ((size_t)q * rows + r) * d_v;
+                    if (c + 3 < d_v && (d_v & 3) == 0) {
+                        const float4 v = *reinterpret_cast<const float4 *>(src + c);
+                        acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
+                        acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+                    } else {
+                        for (int e = 0; e < 4; ++e)
+                            if (c + e < d_v) acc[e] = fmaf(w, src[c + e], acc[e]);
+                    }
+                }
+            }
+            for (int e = 0; e < 4; ++e)
+                if (c + e < d_v) O[(size_t)r * d_v + c + e] = from_f32<TO>(acc[e]);
+        }
+        if (lane == 0) { m[r] = mx; l[r] = ls; }
     }
-    if (threadIdx.x == 0) { m[r] = mx; l[r] = ls; }
 }
 
 int launch_merge(const float *O_part, const float *m_part, const float *l_part, void *O,
                  float *m, float *l, long long rows, int d_v, int num_parts, int out_dtype,
                  cudaStream_t stream) {
     if (rows <= 0) return FDMLA_OK;
-    if (rows > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
+    const long long want = (rows + 7) / 8;
+    const unsigned grid = (unsigned)(want < 8LL * kNumSMs ? want : 8LL * kNumSMs);
     if (out_dtype == FDMLA_F32)
-        merge_kernel<float><<<(unsigned)rows, 128, 0, stream>>>(O_part, m_part, l_part,
-                                                              static_cast<float *>(O), m, l, rows, d_v, num_parts);
+        merge_kernel<float><<<grid, 256, 0, stream>>>(O_part, m_part, l_part, static_cast<float *>(O), m, l, rows,
+                                                      d_v, num_parts);
     else if (out_dtype == FDMLA_BF16)
-        merge_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(
-            O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O), m, l, rows, d_v, num_parts);
+        merge_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O),
+                                                             m, l, rows, d_v, num_parts);
     else
         return FDMLA_ERR_INVALID;
     return check_launch();

@@ -127,6 +127,25 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, 
         : "memory");
 }
 
+// 256-bit store (address 32-byte aligned).
+__device__ __forceinline__ void st_global_v8(void *ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
+// 2-D tiled store shared memory -> global memory (x innermost, x * elem_size a multiple of 16 B, no
+// negative coordinates); completion is tracked per issuing thread with bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// wait until the shared-memory sources of all but the newest `Pending` bulk groups of this thread have been read
+template <int Pending>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Pending) : "memory");
+}
+
 // One 128-byte line into L2 (no register result, nothing to wait for).
 __device__ __forceinline__ void prefetch_l2(const void *ptr) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));

@@ -51,7 +51,10 @@ constexpr int Q_CHUNK = 64 * 128;     // 64 rows x 128 B
 constexpr int Q_BYTES = NQC * Q_CHUNK;            // 73 728
 constexpr int SLOT = 16384;           // ring slot: 2 boxes of [64 keys x 128 B]
 constexpr int BOX = 8192;
-constexpr int NSLOT = 7;
+#ifndef FDMLA_NSLOT
+#define FDMLA_NSLOT 7
+#endif
+constexpr int NSLOT = FDMLA_NSLOT;
 constexpr int PF_DIST = 1;             // decode: tiles of distance of the softmax threads' L2 prefetch (0 = off)
 constexpr int P_Q = 64 * SUB * 2;     // one P quarter: 64 rows x 64 keys bf16 = 8 192
 constexpr int P_BYTES = 4 * P_Q;
@@ -79,6 +82,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #ifdef FDMLA_TRACE
 constexpr int TR_N = 256;
 __device__ long long g_trace[2][6][TR_N];
+__device__ int g_trace_cluster = 0;
+__device__ unsigned long long g_trace_span[256][4];     // per CTA: globaltimer at entry, after set-up, before teardown, at exit
+__device__ __forceinline__ unsigned long long gtimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 #define TRACE(stream, idx)                                                                        \
     do {                                                                                           \
         if (trace_on && (idx) < TR_N) g_trace[rank][stream][idx] = clock64();                      \
@@ -142,6 +152,8 @@ struct Item {
     int n_sub, n_tiles;       // 64-key sub-blocks / 256-key tiles to attend
     int rows_here;
     bool fix;                 // the last sub-block reaches past the end of the sequence (its V rows get zeroed)
+    bool final_out;           // the item covers every key of its rows: write O, m, l instead of a partial
+    int n_parts;              // balanced schedule: pieces the sequence is cut into (0 otherwise)
 };
 
 __device__ __forceinline__ Item make_item(const FwdProblem &p, int idx, int n_row_tiles, bool poisoned) {
@@ -171,20 +183,119 @@ __device__ __forceinline__ Item make_item(const FwdProblem &p, int idx, int n_ro
     it.n_sub = (it.blk_hi > it.lo && !poisoned) ? (it.blk_hi - it.t_begin + SUB - 1) / SUB : 0;
     it.n_tiles = (it.n_sub + 3) / 4;
     it.fix = it.n_sub > 0 && it.t_begin + it.n_sub * SUB > it.seq;
+    it.final_out = p.num_splits == 1 && p.O != nullptr;
+    it.n_parts = 0;
     return it;
 }
 
-// The persistent grid: cluster c takes items c, 2n-1-c, 2n+c, ... (a snake over rounds of n clusters,
-// so that an order sorted by work does not always hand the same cluster the largest item of a round).
-__device__ __forceinline__ int item_of_round(int round, int cid, int n_clusters) {
-    return round * n_clusters + ((round & 1) ? n_clusters - 1 - cid : cid);
+// The persistent grid walks one of two schedules.
+//  * Items: cluster c takes items c, 2n-1-c, 2n+c, ... (a snake over rounds of n clusters, so that an
+//    order sorted by work does not always hand the same cluster the largest item of a round).
+//  * Balanced (decode with a final output and spare partial slabs): the 256-key tiles of all sequences
+//    are laid end to end (an empty sequence counts as one) and cluster c takes tiles [c q, (c+1) q) of that
+//    line, q = max(ceil(total / n), quota_min).  A sequence that lies inside one cluster's run is
+//    written as the final result; one that is cut is written as partials (piece k into slab k) and merged
+//    by a second kernel.  quota_min bounds the pieces per sequence by the number of slabs.
+struct Cursor {
+    bool balanced;
+    // items
+    int round, n_rounds, cid, n_clusters, n_items, n_row_tiles;
+    // balanced
+    int g, tile0, left, quota, first_of_g;     // first_of_g: position of sequence g's first tile on the line
+};
+
+__device__ __forceinline__ int sched_tiles(const FwdProblem &p, int g) {
+    const int seq = p.seqlens ? p.seqlens[g] : p.Skv;
+    const int nt = (seq + T - 1) / T;
+    return nt > 0 ? nt : 1;
+}
+
+// Called by all 32 lanes of a warp together.
+__device__ __forceinline__ void cursor_init(Cursor &c, const FwdProblem &p, int cid, int n_clusters, int lane) {
+    c.balanced = p.balanced != 0;
+    c.cid = cid;
+    c.n_clusters = n_clusters;
+    c.round = 0;
+    c.n_row_tiles = (p.R + 127) / 128;
+    c.n_items = c.n_row_tiles * p.G * p.num_splits;
+    c.n_rounds = (c.n_items + n_clusters - 1) / n_clusters;
+    c.g = 0; c.tile0 = 0; c.left = 0; c.quota = 1; c.first_of_g = 0;
+    if (!c.balanced) return;
+    int total = 0;
+    for (int g0 = 0; g0 < p.G; g0 += 32) total += (g0 + lane < p.G) ? sched_tiles(p, g0 + lane) : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    int q = (total + n_clusters - 1) / n_clusters;
+    if (q < p.quota_min) q = p.quota_min;
+    if (q < 1) q = 1;
+    c.quota = q;
+    const long long start_ll = (long long)cid * q;
+    if (start_ll >= total) return;                    // nothing left for this cluster
+    const int start = (int)start_ll;
+    c.left = (total - start) < q ? (total - start) : q;
+    int base = 0;
+    for (int g0 = 0; g0 < p.G; g0 += 32) {
+        const int v = (g0 + lane < p.G) ? sched_tiles(p, g0 + lane) : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, base + incl > start);
+        if (hit) {
+            const int src = __ffs(hit) - 1;
+            const int first = __shfl_sync(0xffffffffu, base + incl - v, src);
+            c.g = g0 + src;
+            c.first_of_g = first;
+            c.tile0 = start - first;
+            return;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    c.left = 0;
+}
+
+// Next item of this cluster (the same in every thread that asks); false when the cluster is done.
+__device__ __forceinline__ bool cursor_next(Cursor &c, const FwdProblem &p, bool poisoned, Item &it) {
+    if (!c.balanced) {
+        while (c.round < c.n_rounds) {
+            const int idx = c.round * c.n_clusters + ((c.round & 1) ? c.n_clusters - 1 - c.cid : c.cid);
+            ++c.round;
+            if (idx < c.n_items) { it = make_item(p, idx, c.n_row_tiles, poisoned); return true; }
+        }
+        return false;
+    }
+    if (c.left <= 0 || c.g >= p.G) return false;
+    const int seq = p.seqlens ? p.seqlens[c.g] : p.Skv;
+    const int nt = sched_tiles(p, c.g);
+    const int take = c.left < nt - c.tile0 ? c.left : nt - c.tile0;
+    const int ta = c.tile0, tb = c.tile0 + take;
+    it.row0 = 0; it.g = c.g; it.seq = seq;
+    it.lo = ta * T;
+    it.hi = tb * T < seq ? tb * T : seq;
+    if (it.hi < it.lo) it.hi = it.lo;
+    it.blk_hi = it.hi;
+    it.t_begin = it.lo;
+    it.rows_here = p.R < 128 ? p.R : 128;
+    it.n_sub = (it.hi > it.lo && !poisoned) ? (it.hi - it.lo + SUB - 1) / SUB : 0;
+    it.n_tiles = (it.n_sub + 3) / 4;
+    it.fix = it.n_sub > 0 && it.t_begin + it.n_sub * SUB > seq;
+    it.final_out = ta == 0 && tb == nt;
+    it.split = c.cid - c.first_of_g / c.quota;                 // piece index within the sequence
+    it.n_parts = (c.first_of_g + nt - 1) / c.quota - c.first_of_g / c.quota + 1;
+    c.left -= take;
+    if (tb == nt) { c.first_of_g += nt; ++c.g; c.tile0 = 0; }
+    else c.tile0 = tb;
+    return true;
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-               const __grid_constant__ CUtensorMap tmV) {
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO) {
     // tmQ: chunked view, box {64, 64 rows, 9 chunks}; tmK: plain 2-D, box {64, 64 rows};
-    // tmV: chunked view of the same cache, box {64, 64 rows, 2 chunks}
+    // tmV: chunked view of the same cache, box {64, 64 rows, 2 chunks};
+    // tmO: the bf16 output [G R, 512], box {64, 64 rows} (a copy of tmK when there is no final output)
     using namespace ptx;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -202,14 +313,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const bool leader = rank == 0;
 #ifdef FDMLA_TRACE
-    const bool trace_on = blockIdx.x < 2;
+    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][0] = gtimer();
+    const bool trace_on = (int)(blockIdx.x >> 1) == g_trace_cluster;
 #endif
 
     // ---- the work list (identical in both CTAs of the pair and in every role) -----------
-    const int n_row_tiles = (p.R + 127) / 128;
-    const int n_items = n_row_tiles * p.G * p.num_splits;
     const int cid = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-    const int n_rounds = (n_items + n_clusters - 1) / n_clusters;
     const int err_now = *reinterpret_cast<volatile int *>(&g_tc_error);
     const bool poisoned = err_now != 0 && err_now != ERR_PAGE;
 
@@ -243,6 +352,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     cluster_sync_all();                      // the peer's barriers exist before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+#ifdef FDMLA_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][1] = gtimer();
+#endif
 
     // global row of the first key of sub-block s of an item (pool row for paged caches)
     auto sub_row = [&](const Item &it, int s, bool *bad_page) -> int {
@@ -273,10 +385,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #ifdef FDMLA_TRACE
         int ptr_n = 0;
 #endif
-        for (int round = 0; round < n_rounds && ok; ++round) {
-            const int idx = item_of_round(round, cid, n_clusters);
-            if (idx >= n_items) continue;
-            const Item it = make_item(p, idx, n_row_tiles, poisoned);
+        Cursor cur;
+        cursor_init(cur, p, cid, n_clusters, lane);
+        Item it;
+        for (int round = 0; ok && cursor_next(cur, p, poisoned, it); ++round) {
             if (it.n_tiles == 0) continue;
             // Q of the previous item is free once its last Q K^T has completed
             if (q_loads > 0) ok = ok && mbar_wait(BAR(B_QEMPTY), (q_loads - 1) & 1);
@@ -400,11 +512,11 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #ifdef FDMLA_TRACE
             int ntr = 0;
 #endif
-            for (int round = 0; round < n_rounds; ++round) {
-                const int idx = item_of_round(round, cid, n_clusters);
-                if (idx >= n_items) continue;
+            Cursor cur;
+            cursor_init(cur, p, cid, n_clusters, lane);
+            Item it;
+            for (int round = 0; cursor_next(cur, p, poisoned, it); ++round) {
                 if (!__all_sync(0xffffffffu, ok)) break;
-                const Item it = make_item(p, idx, n_row_tiles, poisoned);
                 if (it.n_tiles == 0) continue;       // nothing to multiply; the softmax warps write the empty result
                 // The accumulator is needed again only after the softmax warps of both CTAs have read the
                 // previous item's O out of tensor memory.
@@ -513,10 +625,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             const uint32_t peer_base = map_to_cta(BAR(B_FULL), 0);
             int slot = 0, use = 0, q_loads = 0, fix_uses = 0;
             bool ok = true;
-            for (int round = 0; round < n_rounds && ok; ++round) {
-                const int idx = item_of_round(round, cid, n_clusters);
-                if (idx >= n_items) continue;
-                const Item it = make_item(p, idx, n_row_tiles, poisoned);
+            Cursor cur;
+            cursor_init(cur, p, cid, n_clusters, lane);
+            Item it;
+            for (int round = 0; ok && cursor_next(cur, p, poisoned, it); ++round) {
                 if (it.n_tiles == 0) continue;
                 ok = mbar_wait(BAR(B_QFULL), q_loads & 1);
                 ++q_loads;
@@ -546,13 +658,14 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         bool ok = true;
         int tg0 = 0;                            // tiles of the items before the current one
         uint32_t r[32];
-        for (int round = 0; round < n_rounds; ++round) {
-            const int idx = item_of_round(round, cid, n_clusters);
-            if (idx >= n_items) continue;
-            const Item it = make_item(p, idx, n_row_tiles, poisoned);
+        Cursor cur;
+        cursor_init(cur, p, cid, n_clusters, lane);
+        Item it;
+        for (int round = 0; cursor_next(cur, p, poisoned, it); ++round) {
             const int rr = it.row0 + 64 * (int)rank + row;
             const bool row_ok = rr < p.R;
             const int lo = it.lo, hi = it.hi, seq = it.seq, n_tiles = it.n_tiles;
+            if (L == 0) TRACE(5, round * 4 + 0);
             int upper = lo;
             if (row_ok) {
                 long long vis = seq;
@@ -698,47 +811,98 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 tc_fence_after_sync();
             }
             tg0 += n_tiles;
+            if (L == 0) TRACE(5, round * 4 + 1);
             // row sum = both key halves
             named_bar_sync(1, 128);
             red[L] = l_run;
             named_bar_sync(1, 128);
             const float l_tot = l_run + red[L ^ 64];
+            if (L == 0 && round == 0) TRACE(5, 16);
             // ---- epilogue: thread L writes row `row`, d_v columns [256*half, 256*half + 256) ----
             const bool have = ok && n_tiles > 0 && l_tot > 0.f;
             const float inv = have ? 1.f / l_tot : 0.f;
-            const bool final_out = (p.num_splits == 1 && p.O != nullptr);
+            const bool final_out = it.final_out;
             const size_t grow = (size_t)it.g * p.R + (row_ok ? rr : 0);
             const size_t prow_idx = (size_t)it.split * p.G * p.R + grow;
             const int col0 = 256 * half;
+            if (final_out && it.rows_here == 128) {
+                // bf16 result of a full tile: staged in the (now idle) P buffer as 64-row x 64-column boxes in
+                // the 128-byte swizzle and written by TMA tensor stores.  Each key-half group of 64 threads
+                // (rows 0-63, 256 of the d_v columns) ping-pongs between two 8 KB boxes.
+                uint8_t *box0 = sP + half * (2 * BOX);
+                const int y = it.g * p.R + it.row0 + 64 * (int)rank;
 #pragma unroll 1
-            for (int cc = 0; cc < O_COLS / 32; ++cc) {
-                uint32_t o[32];
-                if (n_tiles > 0 && ok) {
-                    tmem_ld32(tmem + lane_base + cc * 32, o);
-                    tmem_wait_ld();
-                }
-                if (!row_ok) continue;
-                if (final_out) {
-                    __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + grow * p.d_v + col0 + cc * 32;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float a = have ? __uint_as_float(o[j + 2 * e]) * inv : 0.f;
-                            const float c = have ? __uint_as_float(o[j + 2 * e + 1]) * inv : 0.f;
-                            __nv_bfloat162 h = __floats2bfloat162_rn(a, c);
-                            w[e] = *reinterpret_cast<uint32_t *>(&h);
-                        }
-                        *reinterpret_cast<uint4 *>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int bx = 0; bx < 4; ++bx) {
+                    uint8_t *box = box0 + (bx & 1) * BOX;
+                    if (bx >= 2) {
+                        if (row == 0) bulk_wait_read<1>();      // the store that last read this box is done with it
+                        named_bar_sync(2 + half, 64);
                     }
-                } else {
-                    float *dst = p.O_part + prow_idx * p.d_v + col0 + cc * 32;
+#pragma unroll 1
+                    for (int c2 = 0; c2 < 2; ++c2) {
+                        uint32_t o[32];
+                        if (n_tiles > 0 && ok) {
+                            tmem_ld32(tmem + lane_base + (2 * bx + c2) * 32, o);
+                            tmem_wait_ld();
+                        }
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4 *>(dst + j) =
-                            make_float4(have ? __uint_as_float(o[j]) * inv : 0.f, have ? __uint_as_float(o[j + 1]) * inv : 0.f,
-                                        have ? __uint_as_float(o[j + 2]) * inv : 0.f, have ? __uint_as_float(o[j + 3]) * inv : 0.f);
+                        for (int j = 0; j < 32; j += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float a = have ? __uint_as_float(o[j + 2 * e]) * inv : 0.f;
+                                const float c = have ? __uint_as_float(o[j + 2 * e + 1]) * inv : 0.f;
+                                __nv_bfloat162 h = __floats2bfloat162_rn(a, c);
+                                w[e] = *reinterpret_cast<uint32_t *>(&h);
+                            }
+                            const int v = c2 * 4 + (j >> 3);             // 16-byte vector of the 128-byte row
+                            *reinterpret_cast<uint4 *>(box + row * 128 + ((v ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    named_bar_sync(2 + half, 64);
+                    if (row == 0) {
+                        tma_store_2d(&tmO, col0 + 64 * bx, y, smem_u32(box));
+                        bulk_commit();
+                    }
+                    if (L == 0 && round == 0) TRACE(5, 17 + bx);
+                }
+                if (row == 0) bulk_wait_read<0>();       // before the next item's P is written (barrier below)
+                if (L == 0 && round == 0) TRACE(5, 21);
+            } else {
+#pragma unroll 1
+                for (int cc = 0; cc < O_COLS / 32; ++cc) {
+                    uint32_t o[32];
+                    if (n_tiles > 0 && ok) {
+                        tmem_ld32(tmem + lane_base + cc * 32, o);
+                        tmem_wait_ld();
+                    }
+                    if (!row_ok) continue;
+                    // 32-byte stores: a lane fills whole sectors of its own row
+                    if (final_out) {
+                        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + grow * p.d_v + col0 + cc * 32;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 16) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float a = have ? __uint_as_float(o[j + 2 * e]) * inv : 0.f;
+                                const float c = have ? __uint_as_float(o[j + 2 * e + 1]) * inv : 0.f;
+                                __nv_bfloat162 h = __floats2bfloat162_rn(a, c);
+                                w[e] = *reinterpret_cast<uint32_t *>(&h);
+                            }
+                            st_global_v8(dst + j, w);
+                        }
+                    } else {
+                        float *dst = p.O_part + prow_idx * p.d_v + col0 + cc * 32;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) w[e] = have ? __float_as_uint(__uint_as_float(o[j + e]) * inv) : 0u;
+                            st_global_v8(dst + j, w);
+                        }
+                    }
                 }
             }
             if (row_ok && half == 0) {
@@ -746,12 +910,23 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 const float l_out = have ? l_tot * fast_exp2(m_ref - m_true) : 0.f;
                 if (final_out) { p.m[grow] = m_out; p.l[grow] = l_out; }
                 else { p.m_part[prow_idx] = m_out; p.l_part[prow_idx] = l_out; }
+                if (it.n_parts > 0) {
+                    // balanced schedule: tell the merge which slabs of this row hold something
+                    const size_t slab = (size_t)p.G * p.R;
+                    if (final_out) p.l_part[grow] = -1.f;                  // "O, m, l already final"
+                    else if (it.split == 0)
+                        for (int sidx = it.n_parts; sidx < p.num_splits; ++sidx) {
+                            p.l_part[sidx * slab + grow] = 0.f;
+                            p.m_part[sidx * slab + grow] = -CUDART_INF_F;
+                        }
+                }
             }
             // this CTA's softmax warps have read O out of tensor memory: the next item may overwrite it
             // (an empty item never touched the accumulator and signals nothing)
             tc_fence_before_sync();
             named_bar_sync(1, 128);
             if (L == 0 && n_tiles > 0) mbar_arrive_cluster_relaxed(ofree_leader);
+            if (L == 0) TRACE(5, round * 4 + 2);
         }
         if (!ok) atomicCAS(&g_tc_error, 0, ERR_SOFTMAX);
     }
@@ -759,12 +934,18 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     // ---- teardown: neither CTA may leave while the pair can still touch its memory --------
     tc_fence_before_sync();
     __syncthreads();
+#ifdef FDMLA_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][2] = gtimer();
+#endif
     __syncwarp();
     cluster_sync_all();
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc_2cta(tmem, TMEM_COLS);
     }
+#ifdef FDMLA_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][3] = gtimer();
+#endif
 }
 
 }  // namespace tc2
@@ -773,6 +954,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 // Host side
 // --------------------------------------------------------------------------------------
 #ifdef FDMLA_TRACE
+extern "C" int fdmla_trace_spans(unsigned long long *dst) {
+    return cudaMemcpyFromSymbol(dst, tc2::g_trace_span, sizeof(unsigned long long) * 256 * 4) == cudaSuccess ? 0 : -1;
+}
+extern "C" int fdmla_trace_select(int cluster) {
+    return cudaMemcpyToSymbol(tc2::g_trace_cluster, &cluster, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
 extern "C" int fdmla_trace_fetch(long long *dst, int max_elems) {
     const int n = 2 * 6 * tc2::TR_N;
     if (max_elems < n) return -n;
@@ -817,16 +1004,24 @@ bool fwd_tensor2_supported(const FwdProblem &p, int dtype) {
     const long long kv_rows = p.page_table ? (long long)p.num_pages * p.page_size : (long long)p.G * p.Skv;
     if (kv_rows <= 0 || kv_rows > 2147483647LL || (long long)p.G * p.R > 2147483647LL) return false;
     if ((reinterpret_cast<uintptr_t>(p.Q) | reinterpret_cast<uintptr_t>(p.K)) & 15) return false;
-    if ((reinterpret_cast<uintptr_t>(p.O) | reinterpret_cast<uintptr_t>(p.O_part)) & 15) return false;
+    if ((reinterpret_cast<uintptr_t>(p.O) | reinterpret_cast<uintptr_t>(p.O_part)) & 31) return false;    // 32-byte stores
     return true;
 }
 
-int launch_fwd_tensor2(const FwdProblem &p, cudaStream_t stream) {
-    CUtensorMap tmQ, tmK, tmV;
+int launch_fwd_tensor2(const FwdProblem &p_in, cudaStream_t stream) {
+    FwdProblem p = p_in;
+    // the balanced schedule is for one row tile per KV group, the whole key range and a final output
+    if (p.balanced && (p.R > 128 || p.causal || p.num_splits < 2 || p.quota_min < 1 || !p.O || !p.O_part || p.kv_begin > 0 ||
+                       p.kv_end >= 0))
+        p.balanced = 0;
+    if (!p.balanced && p.num_splits > 1) p.O = nullptr;      // equal splits: partials only
+    CUtensorMap tmQ, tmK, tmV, tmO;
     const long long kv_rows = p.page_table ? (long long)p.num_pages * p.page_size : (long long)p.G * p.Skv;
     if (!make_tensor_map_bf16_chunked(&tmQ, p.Q, (long long)p.G * p.R, p.d_qk, 64, 9)) return FDMLA_ERR_CUDA;
     if (!make_tensor_map_bf16_chunked(&tmV, p.K, kv_rows, p.d_qk, 64, 2)) return FDMLA_ERR_CUDA;
     if (!make_tensor_map_bf16(&tmK, p.K, kv_rows, p.d_qk, 64)) return FDMLA_ERR_CUDA;
+    tmO = tmK;
+    if (p.O && !make_tensor_map_bf16(&tmO, p.O, (long long)p.G * p.R, p.d_v, 64)) return FDMLA_ERR_CUDA;
     if (cudaFuncSetAttribute(tc2::fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES) != cudaSuccess)
         return FDMLA_ERR_CUDA;
     // persistent grid: as many CTA pairs as the device keeps resident at once (one CTA per SM), each
@@ -834,8 +1029,8 @@ int launch_fwd_tensor2(const FwdProblem &p, cudaStream_t stream) {
     const long long n_items = (long long)((p.R + 127) / 128) * p.G * p.num_splits;
     const int resident = tc2::resident_clusters();
     if (resident <= 0) return FDMLA_ERR_CUDA;
-    const int n_clusters = n_items < resident ? (int)n_items : resident;
-    tc2::fwd_tc2_kernel<<<dim3(2 * n_clusters), tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
+    const int n_clusters = (p.balanced || n_items >= resident) ? resident : (int)n_items;
+    tc2::fwd_tc2_kernel<<<dim3(2 * n_clusters), tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmO);
     return check_launch();
 }
 

@@ -31,6 +31,7 @@ SIGNATURES = {
     "fdmla_fwd_on_the_fly": (_i, [_vp] * 9 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),
     "fdmla_decode_paged": (_i, [_vp] * 10 + [_i] * 10 + [_f, _i, _vp]),
     "fdmla_decode_suggest_splits": (_i, [_i] * 7),
+    "fdmla_set_decode_merge": (None, [_i]),
     "fdmla_decode_paged_noalloc_max_rows": (_sz, [_i]),
     "fdmla_decode_paged_noalloc": (_i, [_vp] * 7 + [_i] * 8 + [_f, _i, _vp]),
     "fdmla_merge_lse": (_i, [_vp] * 6 + [_ll, _i, _i, _i, _vp]),
@@ -78,6 +79,11 @@ def set_backend(backend: int) -> None:
 def set_single_cta(on: bool) -> None:
     """Keep 576/512 shapes on the single-CTA tcgen05 kernel (A/B measurements, tests)."""
     check(lib().fdmla_set_single_cta(int(bool(on))), "fdmla_set_single_cta")
+
+
+def set_decode_merge(on: bool) -> None:
+    """Measurement switch: leave the decode partials unmerged so the attention kernel can be timed alone."""
+    lib().fdmla_set_decode_merge(int(bool(on)))
 
 
 def last_kernel() -> str:

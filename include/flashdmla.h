@@ -122,7 +122,13 @@ int fdmla_fwd_on_the_fly(const void *Q, const void *K, const void *V,
  *   results go to O_part [num_splits, B, H, d_v], m_part, l_part
  *   [num_splits, B, H] (fp32, caller-provided scratch; may be NULL when
  *   num_splits == 1) and are merged into O [B, H, d_v] (dtype), m, l [B, H].
- *   If O is NULL only the partials are produced.
+ *   If O is NULL only the partials are produced, exactly as described (piece s
+ *   of every sequence in slab s).  When O is given, the scratch contents after
+ *   the call are unspecified: with num_splits >= 2, the whole key range and
+ *   H <= 128 the tcgen05 kernel treats the slabs as room to cut sequences and
+ *   deals the 256-key tiles of all sequences out to the SMs in equal contiguous
+ *   runs; a sequence is cut at most num_splits - 1 times, uncut sequences are
+ *   written to O directly and the merge touches only the cut ones.
  *   Every page id read from page_table must be in [0, num_pages).
  * The paged cache is the "KV-cache" of README.md:15; per (b, h) the math is
  * that of vanilla_attn_forward (vanallia_attn.cu:85-99) on the gathered rows.
@@ -135,10 +141,15 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool,
                        int num_splits, int kv_begin, int kv_end, float scale,
                        int dtype, void *stream);
 
-/* Split count the library would choose for a decode problem (fills the GPU
- * with whole waves).  No reference counterpart. */
+/* Split count (number of scratch slabs) the library would choose for a decode
+ * problem.  No reference counterpart. */
 int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,
                                 int page_size, int dtype);
+
+/* Measurement switch: with on == 0, fdmla_decode_paged leaves the partials
+ * unmerged (O, m, l are then incomplete), so that the attention kernel can be
+ * timed alone.  Default 1.  No reference counterpart. */
+void fdmla_set_decode_merge(int on);
 
 /*
  * fdmla_decode_paged for callers that cannot allocate device memory.  It has no counterpart
