@@ -334,3 +334,32 @@ def test_errors_are_reported(cuda):
     # Skv = 0: every row is empty
     O, m, l = flashdmla.flash_dmla_cache_latent(Q, torch.zeros(1, 0, 16, device=cuda), 8)
     assert (O == 0).all() and torch.isneginf(m).all() and (l == 0).all()
+
+
+@pytest.mark.parametrize("heads,slabs", [(128, 2), (16, 2), (16, 3), (128, 6), (16, 64)])
+def test_paged_decode_balanced_schedule(heads, slabs, cuda):
+    """Final output with spare partial slabs on the 576/512 tensor path: the keys are dealt out as
+    contiguous runs of 256-key tiles, sequences that straddle two runs are cut and merged.  Ragged
+    lengths with empty and one-token sequences, against the oracle and against the unsplit result."""
+    import flashdmla
+    g = torch.Generator().manual_seed(77 + slabs)
+    lens = torch.randint(0, 6001, (40,), generator=g).tolist()
+    lens[3] = 0
+    lens[17] = 1
+    lens[22] = 6000
+    lens[39] = 0          # an empty sequence at the very end of the line
+    B = len(lens)
+    Q, pool, table, sl = _paged(B, heads, lens, 576, 64, torch.bfloat16, seed=5, std=0.1)
+    sc = 1 / math.sqrt(192)
+    dev = [t.to(cuda) for t in (Q, pool, table, sl)]
+    O, m, l = flashdmla.flash_dmla_paged_decode(*dev, 512, sc, num_splits=slabs)
+    assert flashdmla.last_kernel() == "tcgen05" and flashdmla.device_error_flag() == 0
+    O1, m1, l1 = flashdmla.flash_dmla_paged_decode(*dev, 512, sc, num_splits=1)
+    assert_O(O, O1.float())
+    assert_stats(m, l, m1, l1)
+    hs = slice(0, min(heads, 8))
+    Or, mr, lr = orc.decode_paged(Q[:, hs].float(), pool.float(), table, sl, 512, sc)
+    assert_O(O[:, hs], Or)
+    assert_stats(m[:, hs], l[:, hs], mr, lr)
+    for b in (3, 39):     # empty sequences: zeros, -inf, 0
+        assert (O[b] == 0).all() and (l[b] == 0).all() and torch.isinf(m[b]).all()
