@@ -65,11 +65,12 @@ constexpr int O_COLS = 256, S_COL0 = 256, S_COLS = 128, TMEM_COLS = 512;
 // barriers (same offsets in both CTAs)
 constexpr int B_QFULL = 0, B_PEER_QFULL = 1, B_QEMPTY = 2, B_OFREE = 3, B_FULL = 4, B_EMPTY = B_FULL + NSLOT,
               B_FIX = B_EMPTY + NSLOT, B_SFULL = B_FIX + 2, B_SEMPTY = B_SFULL + 2, B_PFULL = B_SEMPTY + 2,
-              B_OREADY = B_PFULL + 4, NBARS = B_OREADY + 2;
+              B_OREADY = B_PFULL + 4, B_PEMPTY = B_OREADY + 2, NBARS = B_PEMPTY + 4;
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + NSLOT * SLOT + P_BYTES + RED_BYTES + ROWS_CACHE * 4 + NBARS * 8 + 16;
 static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
 constexpr int THREADS = 192;
-enum { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_PAGE = 4, ERR_RELAY = 14 };
+enum { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_PAGE = 4, ERR_RELAY = 14,
+       ERR_SOFTMAX_P = 15, ERR_SOFTMAX_RESCALE = 16, ERR_SOFTMAX_END = 17 };   // 13: scores never arrived; 15-17: P*V never completed
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -83,6 +84,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 constexpr int TR_N = 256;
 __device__ long long g_trace[2][6][TR_N];
 __device__ int g_trace_cluster = 0;
+__device__ int g_dbg[160][8];      // per CTA: last wait each role entered (development builds only)
+#define DBG(slot, val) do { if (lane == 0) g_dbg[blockIdx.x][slot] = (val); } while (0)
 __device__ unsigned long long g_trace_span[256][4];     // per CTA: globaltimer at entry, after set-up, before teardown, at exit
 __device__ __forceinline__ unsigned long long gtimer() {
     unsigned long long t;
@@ -95,6 +98,7 @@ __device__ __forceinline__ unsigned long long gtimer() {
     } while (0)
 #else
 #define TRACE(stream, idx) do { } while (0)
+#define DBG(slot, val) do { } while (0)
 #endif
 
 // Four consecutive K=16 steps of one 2-CTA MMA: descriptors advance by a_step / b_step (in
@@ -119,6 +123,11 @@ __device__ __forceinline__ void mma4_2cta(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+// P quarters are produced in the order (0, 2), (1, 3) - the two key halves of a tile work side by
+// side - and P*V consumes them in that order, so that half of a tile's P*V is out of the way
+// before the second pair of quarters is even written.
+__device__ __forceinline__ int quarter_at(int i) { return ((i & 1) << 1) | (i >> 1); }      // 0, 2, 1, 3
+
 // The one order in which ring slots are filled and consumed.  `f(is_v, t, a, b)` is
 // called for a K slot as (false, tile, chunk, 0) and for a V slot as (true, tile, quarter,
 // half j); it returns false to stop.  n_sub = number of 64-key sub-blocks to attend.
@@ -134,7 +143,9 @@ __device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
             for (int c = 0; c < NQC; ++c)
                 if (!f(false, t + 1, c, 0)) return false;
         const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;     // quarters of tile t that exist
-        for (int q = 0; q < nq; ++q) {
+        for (int i = 0; i < 4; ++i) {
+            const int q = quarter_at(i);
+            if (q >= nq) continue;
             if (!f(true, t, q, 0)) return false;
             if (!f(true, t, q, 1)) return false;
         }
@@ -339,7 +350,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             mbar_init(BAR(B_SEMPTY + b), 4);     // two key halves in each CTA of the pair
             mbar_init(BAR(B_OREADY + b), 1);
         }
-        for (int q = 0; q < 4; ++q) mbar_init(BAR(B_PFULL + q), 2);   // one arrival per CTA
+        for (int q = 0; q < 4; ++q) {
+            mbar_init(BAR(B_PFULL + q), 2);    // one arrival per CTA
+            mbar_init(BAR(B_PEMPTY + q), 1);   // P*V of that quarter has read it
+        }
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -485,7 +499,8 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 if (t + 1 < it.n_tiles)
                     for (int g3 = 0; g3 < 3; ++g3) fill_k3(t + 1, g3);
                 const int nq = (it.n_sub - 4 * t) < 4 ? (it.n_sub - 4 * t) : 4;
-                for (int q = 0; q < nq; ++q) fill_v2(t, q);
+                for (int i = 0; i < 4; ++i)
+                    if (quarter_at(i) < nq) fill_v2(t, quarter_at(i));
             }
         }
         if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
@@ -542,13 +557,16 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     for (int i = 0; i < 3; ++i) take(sl[i], phs[i]);
                     if (g3 == 0) {
                         // S[b] was last read by the softmax of the tile two before
+                        DBG(0, tg * 100 + 10 + g3);
                         if (tg >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tg / 2) - 1) & 1);
                         tc_fence_after_sync();
                     }
 #ifdef FDMLA_TRACE
                     if (lane == 0 && round == 0) TRACE(1, ntr);
 #endif
+                    DBG(0, tg * 100 + 20 + g3);
                     ok = ok && mbar_wait3(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1], BAR(B_FULL + sl[2]), phs[2]);
+                    DBG(0, tg * 100 + 30 + g3);
 #ifdef FDMLA_TRACE
                     if (lane == 0 && round == 0) TRACE(2, ntr);
                     ++ntr;
@@ -576,12 +594,15 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #ifdef FDMLA_TRACE
                     if (lane == 0 && round == 0) TRACE(1, ntr);
 #endif
+                    DBG(0, tg * 100 + 40 + q);
                     ok = ok && mbar_wait(BAR(B_PFULL + q), tg & 1);
+                    DBG(0, tg * 100 + 50 + q);
                     tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
 #ifdef FDMLA_TRACE
                     if (lane == 0 && round == 0) TRACE(4, ntr);
 #endif
                     ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1]);
+                    DBG(0, tg * 100 + 60 + q);
 #ifdef FDMLA_TRACE
                     if (lane == 0 && round == 0) TRACE(2, ntr);
                     ++ntr;
@@ -595,6 +616,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                                       16, 128, idesc_pv, (t | q) != 0);
                             mma_commit_2cta(BAR(B_EMPTY + sl[j]), 3);
                         }
+                        mma_commit_2cta(BAR(B_PEMPTY + q), 3);                    // this P quarter may be overwritten
                         if (last) mma_commit_2cta(BAR(B_OREADY + (tg & 1)), 3);   // tile t folded into O
                     }
                 };
@@ -609,9 +631,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         for (int g3 = 0; g3 < 3; ++g3) k_group(t + 1, g3);
                     }
                     if (t == 0) wait_o_free();     // the first P V of the item overwrites O
+                    const int q_last = nq == 3 ? 1 : nq - 1;       // last quarter in the order 0, 2, 1, 3
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        if (q < nq) v_pair(t, q, q == nq - 1);
+                    for (int i = 0; i < 4; ++i) {
+                        const int q = quarter_at(i);
+                        if (q < nq) v_pair(t, q, q == q_last);
+                    }
                 }
                 tg0 += it.n_tiles;
                 fix_uses += it.fix ? 1 : 0;
@@ -656,6 +681,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         const uint32_t ofree_leader = map_to_cta(BAR(B_OFREE), 0);
         const bool do_prefetch = p.Sq == 1;     // decode streams the cache from HBM; prefill finds it in L2 anyway
         bool ok = true;
+        int fail = 0;                           // which wait gave up first
+        // P*V passes that have read this thread's two P quarters so far (a quarter past the end of the
+        // keys is written - as zeros - but never read): the phase to wait for before overwriting one
+        int p_reads[2] = {0, 0};
         int tg0 = 0;                            // tiles of the items before the current one
         uint32_t r[32];
         Cursor cur;
@@ -700,7 +729,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         }
                     }
                 }
-                if (ok) ok = mbar_wait(BAR(B_SFULL + b), (tg / 2) & 1);
+                if (ok && !(ok = mbar_wait(BAR(B_SFULL + b), (tg / 2) & 1))) fail = ERR_SOFTMAX;
                 if (L == 0 && round == 0) TRACE(3, t * 8 + 1);
                 tc_fence_after_sync();
                 // pass 1: maximum of this thread's 128 keys (no per-key masking when all are visible)
@@ -729,12 +758,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 tmax = fmaxf(tmax, red[(tg & 1) * 128 + (L ^ 64)]);
                 const float m_new = fmaxf(m_true, tmax);
                 const bool need = m_new > m_ref + 8.f;
-                // P*V of tile t-1 must be complete before its P is overwritten or O rescaled
-                if (t > 0) {
-                    if (ok) ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1);
-                    tc_fence_after_sync();
-                }
                 if (__any_sync(0xffffffffu, need)) {
+                    // O is rescaled: every P*V of tile t-1 must have been accumulated
+                    if (t > 0) {
+                        if (ok && !(ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1))) fail = ERR_SOFTMAX_RESCALE;
+                        tc_fence_after_sync();
+                    }
                     float alpha = 1.f;
                     if (need) {
                         alpha = (m_ref == -CUDART_INF_F) ? 0.f : fast_exp2(m_ref - m_new);
@@ -784,6 +813,14 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         }
                     }
                     const int quarter = 2 * half + (cc >> 1);
+                    // the last P*V that read this quarter's previous contents is done
+                    if (!(cc & 1) && p_reads[cc >> 1] > 0 && ok &&
+                        !(ok = mbar_wait(BAR(B_PEMPTY + quarter), (p_reads[cc >> 1] - 1) & 1))) {
+                        fail = ERR_SOFTMAX_P;
+#ifdef FDMLA_TRACE
+                        if (row == 0) { g_dbg[blockIdx.x][2 + half] = tg * 100 + quarter; g_dbg[blockIdx.x][4 + half] = n_tiles; }
+#endif
+                    }
                     uint8_t *prow = sP + quarter * P_Q + (row >> 3) * P_SBO + (row & 7) * 16 + (cc & 1) * 4 * 128;
 #pragma unroll
                     for (int kc = 0; kc < 4; ++kc)
@@ -793,7 +830,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         // quarter complete in this CTA once the 64 threads of this key half have written it
                         tc_fence_before_sync();
                         fence_proxy_async_smem();
-                        named_bar_sync(2 + half, 64);
+                        // The first pair of quarters waits for all 128 threads: a P*V of this tile adds to every
+                        // column of O, so no thread of either key half may still be rescaling its part of O.
+                        if (cc == 1) named_bar_sync(1, 128);
+                        else named_bar_sync(2 + half, 64);
                         if (L == 0 && round == 0) TRACE(3, t * 8 + 4 + (cc >> 1));
                         if (row == 0) {
                             // (relaxed: the 64 writers have fenced their stores towards the async proxy and
@@ -804,10 +844,13 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     }
                 }
                 l_run += lsum;
+                const int nq = (it.n_sub - 4 * t) < 4 ? (it.n_sub - 4 * t) : 4;
+                p_reads[0] += (2 * half < nq) ? 1 : 0;
+                p_reads[1] += (2 * half + 1 < nq) ? 1 : 0;
             }
             if (ok && n_tiles > 0) {
                 const int tl = tg0 + n_tiles - 1;
-                ok = mbar_wait(BAR(B_OREADY + (tl & 1)), (tl / 2) & 1);
+                if (!(ok = mbar_wait(BAR(B_OREADY + (tl & 1)), (tl / 2) & 1))) fail = ERR_SOFTMAX_END;
                 tc_fence_after_sync();
             }
             tg0 += n_tiles;
@@ -928,7 +971,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             if (L == 0 && n_tiles > 0) mbar_arrive_cluster_relaxed(ofree_leader);
             if (L == 0) TRACE(5, round * 4 + 2);
         }
-        if (!ok) atomicCAS(&g_tc_error, 0, ERR_SOFTMAX);
+        if (!ok) atomicCAS(&g_tc_error, 0, fail ? fail : ERR_SOFTMAX);
     }
 
     // ---- teardown: neither CTA may leave while the pair can still touch its memory --------
@@ -956,6 +999,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 #ifdef FDMLA_TRACE
 extern "C" int fdmla_trace_spans(unsigned long long *dst) {
     return cudaMemcpyFromSymbol(dst, tc2::g_trace_span, sizeof(unsigned long long) * 256 * 4) == cudaSuccess ? 0 : -1;
+}
+extern "C" int fdmla_trace_dbg(int *dst) {
+    return cudaMemcpyFromSymbol(dst, tc2::g_dbg, sizeof(int) * 160 * 8) == cudaSuccess ? 0 : -1;
 }
 extern "C" int fdmla_trace_select(int cluster) {
     return cudaMemcpyToSymbol(tc2::g_trace_cluster, &cluster, sizeof(int)) == cudaSuccess ? 0 : -1;
