@@ -90,7 +90,10 @@ int fdmla_set_backend(int backend) {
 int fdmla_get_backend(void) { return g_backend.load(); }
 int fdmla_set_single_cta(int on) { tensor_prefer_single_cta(on != 0); return FDMLA_OK; }
 const char *fdmla_last_kernel(void) { return t_last_kernel; }
-int fdmla_device_error_flag(int reset) { return tensor_error_flag(reset); }
+int fdmla_device_error_flag(int reset) {
+    const int fwd = tensor_error_flag(reset), bwd = bwd_tensor_error_flag(reset);
+    return fwd ? fwd : bwd;
+}
 
 int fdmla_fwd_cache_latent(const void *Q, const void *K_lat, void *O, float *m, float *l, int B,
                            int H, int Sq, int Skv, int d_qk, int d_v, float scale, int causal,
@@ -286,7 +289,18 @@ int fdmla_bwd_on_the_fly(const void *Q, const void *K, const void *V, const void
     p.dQ = dQ; p.dK = dK_lat; p.dV = dV_lat;
     p.G = B * H; p.R = Sq; p.Sq = Sq; p.Skv = Skv; p.d_qk = d_lat; p.d_v = d_lat;
     p.causal = causal ? 1 : 0; p.scale = scale;
-    rc = launch_bwd_portable(p, dtype, /*grads_f32=*/1, st);
+    const int backend = g_backend.load();
+    const bool tc_ok = bwd_tensor_supported(p, dtype, 1);
+    if (backend == FDMLA_BACKEND_TENSOR && !tc_ok) return FDMLA_ERR_UNSUPPORTED;
+    if (tc_ok && backend != FDMLA_BACKEND_PORTABLE) {
+        t_last_kernel = "tcgen05";
+        rc = launch_bwd_delta(p, dtype, st);
+        if (rc) return rc;
+        rc = launch_bwd_tensor(p, st);
+    } else {
+        t_last_kernel = "portable";
+        rc = launch_bwd_portable(p, dtype, /*grads_f32=*/1, st);
+    }
     if (rc) return rc;
     // dK = dK_lat WK^T, dV = dV_lat WV^T
     rc = launch_project(dK_lat, WK, dK, nkv, d_lat, d_model, 1, 1, dtype, st);

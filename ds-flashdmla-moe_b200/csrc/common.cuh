@@ -109,6 +109,12 @@ struct BwdProblem {
 };
 
 int launch_bwd_portable(const BwdProblem &p, int dtype, int grads_f32, cudaStream_t stream);
+// D = rowsum(dO o O) alone (the first step of launch_bwd_portable)
+int launch_bwd_delta(const BwdProblem &p, int dtype, cudaStream_t stream);
+// tcgen05 backward of the attention core: bf16, 64-wide latents with a separate V, fp32 dK/dV
+bool bwd_tensor_supported(const BwdProblem &p, int dtype, int grads_f32);
+int launch_bwd_tensor(const BwdProblem &p, cudaStream_t stream);
+int bwd_tensor_error_flag(int reset);
 int wgrad_num_partials(long long rows);
 int launch_wgrad(const void *X, const float *G, float *partials, void *dW, long long rows,
                  int d_in, int d_out, int dtype, cudaStream_t stream);

@@ -354,6 +354,22 @@ static int launch_bwd_t(const BwdProblem &p, cudaStream_t stream) {
     return FDMLA_ERR_UNSUPPORTED;
 }
 
+int launch_bwd_delta(const BwdProblem &p, int dtype, cudaStream_t stream) {
+    const long long rows = (long long)p.G * p.R;
+    if (rows <= 0) return FDMLA_OK;
+    const long long nblk = (rows + 7) / 8;
+    if (nblk > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
+    if (dtype == FDMLA_F32)
+        bwd_delta_kernel<float><<<(unsigned)nblk, 256, 0, stream>>>(static_cast<const float *>(p.O),
+                                                                   static_cast<const float *>(p.dO), p.D, rows, p.d_v);
+    else if (dtype == FDMLA_BF16)
+        bwd_delta_kernel<__nv_bfloat16><<<(unsigned)nblk, 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16 *>(p.O), static_cast<const __nv_bfloat16 *>(p.dO), p.D, rows, p.d_v);
+    else
+        return FDMLA_ERR_INVALID;
+    return check_launch();
+}
+
 // grads_f32: dK/dV are written as fp32 (latent-gradient workspaces of the
 // on-the-fly mode) instead of `dtype`.
 int launch_bwd_portable(const BwdProblem &p, int dtype, int grads_f32, cudaStream_t stream) {
