@@ -304,8 +304,11 @@ def main():
     d2h = hO.numel() * 2 + hm.numel() * 4 + hl.numel() * 4
 
     prefill = None
+    on_the_fly = None
     if not args.no_prefill:
         prefill = bench_prefill(dev, rank, world, tf_burst)
+        if rank == 0:
+            on_the_fly = bench_on_the_fly(dev, tf_burst)
 
     err = flashdmla.device_error_flag()
     if rank == 0:
@@ -333,6 +336,7 @@ def main():
                          "frac_of_8TBs_spec": achieved / 8000.0},
             "decode_hbm_gbs_per_gpu": DECODE_BYTES / (ms_per_step * 1e-3) / 1e9,
             "prefill": prefill,
+            "on_the_fly": on_the_fly,
             "device_error_flag": err,
         }
         if cpu is not None:
@@ -360,6 +364,40 @@ def bench_prefill(dev, rank, world, tf_peak, iters=3):
             "tflops_per_gpu": tflops / world, "frac_of_measured_bf16_peak": tflops / world / tf_peak,
             "frac_of_2250_spec": tflops / world / 2250.0, "kernel_family": flashdmla.last_kernel(),
             "tokens_per_s": PF_B * PF_S / (ms * 1e-3)}
+
+
+def bench_on_the_fly(dev, tf_peak, iters=3):
+    """On-the-fly mode (per-head K, V projected to 64-wide latents), B=8,H=16,S=4096, causal: forward and
+    backward through the autograd operator.  FLOP: attention 4 S(S+1)/2 64 per head forward (two GEMMs), five
+    GEMMs backward, plus the latent projections (2 forward, 2 recomputed + 2 gradient + 2 weight-gradient backward)."""
+    import flashdmla
+    B4, H4, S4, dm, dl = 8, 16, 4096, 128, 64
+    g = torch.Generator(device=dev).manual_seed(99)
+    mk = lambda *sh, s=1.0: (torch.randn(*sh, generator=g, device=dev) * s).to(torch.bfloat16)
+    Q, K, V = mk(B4, H4, S4, dl), mk(B4, H4, S4, dm), mk(B4, H4, S4, dm)
+    WK, WV = mk(dm, dl, s=0.1), mk(dm, dl, s=0.1)
+    dO = mk(B4, H4, S4, dl)
+    ts = [t.requires_grad_(True) for t in (Q, K, V, WK, WV)]
+    attn = 2.0 * B4 * H4 * (S4 * (S4 + 1) / 2) * dl            # one causal GEMM
+    proj = 2.0 * B4 * H4 * S4 * dm * dl                        # one projection-sized GEMM
+    fwd_flop, bwd_flop = 2 * attn + 2 * proj, 5 * attn + 6 * proj
+    fwd_ms, bwd_ms = [], []
+    for _ in range(iters + 1):
+        for t in ts:
+            t.grad = None
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        O, m, l = flashdmla.flash_dmla_on_the_fly(*ts, 0.125, True)
+        e[1].record()
+        O.backward(dO)
+        e[2].record()
+        torch.cuda.synchronize()
+        fwd_ms.append(e[0].elapsed_time(e[1]))
+        bwd_ms.append(e[1].elapsed_time(e[2]))
+    f, b = sorted(fwd_ms[1:])[len(fwd_ms[1:]) // 2], sorted(bwd_ms[1:])[len(bwd_ms[1:]) // 2]
+    return {"workload": f"on-the-fly B={B4} H={H4} S={S4} d_model={dm} d_lat={dl} causal (autograd operator)",
+            "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fwd_flop / (f * 1e-3) / 1e12, "bwd_tflops": bwd_flop / (b * 1e-3) / 1e12,
+            "bwd_frac_of_measured_bf16_peak": bwd_flop / (b * 1e-3) / 1e12 / tf_peak, "kernel_family": flashdmla.last_kernel()}
 
 
 if __name__ == "__main__":

@@ -15,6 +15,8 @@ static inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 static inline size_t elem_size(int dtype) { return dtype == FDMLA_F32 ? 4 : 2; }
 static inline bool dtype_ok(int dtype) { return dtype == FDMLA_F32 || dtype == FDMLA_BF16; }
 
+bool tensor_kernels_allowed() { return g_backend.load() != FDMLA_BACKEND_PORTABLE; }
+
 static int run_forward(const FwdProblem &p, int dtype, cudaStream_t stream) {
     const int backend = g_backend.load();
     const bool tc_ok = fwd_tensor_supported(p, dtype);

@@ -115,6 +115,14 @@ int launch_bwd_delta(const BwdProblem &p, int dtype, cudaStream_t stream);
 bool bwd_tensor_supported(const BwdProblem &p, int dtype, int grads_f32);
 int launch_bwd_tensor(const BwdProblem &p, cudaStream_t stream);
 int bwd_tensor_error_flag(int reset);
+// tcgen05 projections / weight-gradient partials for widths (128 -> 64) and (64 -> 128 transposed); they return
+// FDMLA_ERR_UNSUPPORTED for other shapes
+int launch_project_tensor(const void *X, const void *W, void *Y, long long rows, int d_in, int d_out, int w_transposed,
+                          int x_f32, cudaStream_t stream);
+int launch_wgrad_partial_tensor(const void *X, const float *G, float *part, long long rows, int d_in, int d_out, int n_part,
+                                cudaStream_t stream);
+// false when the caller has forced the CUDA-core kernels (fdmla_set_backend)
+bool tensor_kernels_allowed();
 int wgrad_num_partials(long long rows);
 int launch_wgrad(const void *X, const float *G, float *partials, void *dW, long long rows,
                  int d_in, int d_out, int dtype, cudaStream_t stream);

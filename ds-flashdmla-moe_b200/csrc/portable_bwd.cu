@@ -458,8 +458,13 @@ int launch_wgrad(const void *X, const float *G, float *partials, void *dW, long 
         wgrad_partial_kernel<float><<<grid, 256, bytes, stream>>>(static_cast<const float *>(X), G, partials, rows, d_in, d_out);
         wgrad_reduce_kernel<float><<<(n_out + 255) / 256, 256, 0, stream>>>(partials, static_cast<float *>(dW), n_out, n_part);
     } else if (dtype == FDMLA_BF16) {
-        cudaFuncSetAttribute(wgrad_partial_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        wgrad_partial_kernel<bf><<<grid, 256, bytes, stream>>>(static_cast<const bf *>(X), G, partials, rows, d_in, d_out);
+        int rc = tensor_kernels_allowed() ? launch_wgrad_partial_tensor(X, G, partials, rows, d_in, d_out, n_part, stream)
+                                          : FDMLA_ERR_UNSUPPORTED;
+        if (rc != FDMLA_OK && rc != FDMLA_ERR_UNSUPPORTED) return rc;
+        if (rc == FDMLA_ERR_UNSUPPORTED) {
+            cudaFuncSetAttribute(wgrad_partial_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+            wgrad_partial_kernel<bf><<<grid, 256, bytes, stream>>>(static_cast<const bf *>(X), G, partials, rows, d_in, d_out);
+        }
         wgrad_reduce_kernel<bf><<<(n_out + 255) / 256, 256, 0, stream>>>(partials, static_cast<bf *>(dW), n_out, n_part);
     } else {
         return FDMLA_ERR_INVALID;

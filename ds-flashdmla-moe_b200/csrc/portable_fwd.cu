@@ -368,6 +368,10 @@ int launch_project(const void *X, const void *W, void *Y, long long rows, int d_
                    int w_transposed, int x_f32, int dtype, cudaStream_t stream) {
     if (rows <= 0) return FDMLA_OK;
     using bf = __nv_bfloat16;
+    if (dtype == FDMLA_BF16 && tensor_kernels_allowed()) {
+        const int rc = launch_project_tensor(X, W, Y, rows, d_in, d_out, w_transposed, x_f32, stream);
+        if (rc != FDMLA_ERR_UNSUPPORTED) return rc;
+    }
     if (dtype == FDMLA_F32)
         return launch_project_t<float, float, float>(X, W, Y, rows, d_in, d_out, w_transposed, stream);
     if (dtype == FDMLA_BF16 && x_f32)

@@ -248,29 +248,44 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 tmem_wait_ld();
                 uint32_t e1[16], e2[16];
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    float pv[2], dsv[2];
+                for (int j = 0; j < 32; j += 4) {
+                    // four consecutive columns (streamed indices) at a time: their row statistics come as
+                    // one 16-byte shared-memory read per array (MODE_DKV) or from registers (MODE_DQ)
+                    const int c0 = cc * 32 + j;
+                    float m2[4], il[4], dd[4];
+                    bool vis[4];
+                    if (MODE == MODE_DKV) {
+                        const float4 a = *reinterpret_cast<const float4 *>(vb + c0);
+                        const float4 b = *reinterpret_cast<const float4 *>(vb + TILE + c0);
+                        const float4 d = *reinterpret_cast<const float4 *>(vb + 2 * TILE + c0);
+                        const int4 k = *reinterpret_cast<const int4 *>(vb + 3 * TILE + c0);
+                        m2[0] = a.x; m2[1] = a.y; m2[2] = a.z; m2[3] = a.w;
+                        il[0] = b.x; il[1] = b.y; il[2] = b.z; il[3] = b.w;
+                        dd[0] = d.x; dd[1] = d.y; dd[2] = d.z; dd[3] = d.w;
+                        vis[0] = own_ok && own_idx <= k.x; vis[1] = own_ok && own_idx <= k.y;
+                        vis[2] = own_ok && own_idx <= k.z; vis[3] = own_ok && own_idx <= k.w;
+                    } else {
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int c = cc * 32 + j + e;          // column: streamed index within the tile
-                        float m2, il, dd;
-                        bool vis;
-                        if (MODE == MODE_DKV) {
-                            m2 = vb[c]; il = vb[TILE + c]; dd = vb[2 * TILE + c];
-                            vis = own_ok && own_idx <= reinterpret_cast<const int *>(vb)[3 * TILE + c];
-                        } else {
-                            const int key = str0 + c;
-                            m2 = m2_lane; il = il_lane; dd = D_lane;
-                            vis = own_ok && key < p.Skv && (!p.causal || key <= pos_lane + off);
+                        for (int e = 0; e < 4; ++e) {
+                            const int key = str0 + c0 + e;
+                            m2[e] = m2_lane; il[e] = il_lane; dd[e] = D_lane;
+                            vis[e] = own_ok && key < p.Skv && (!p.causal || key <= pos_lane + off);
                         }
-                        const float pr = vis ? fast_exp2(fmaf(__uint_as_float(t1[j + e]), sl2, -m2)) * il : 0.f;
-                        pv[e] = pr;
-                        dsv[e] = vis ? pr * (__uint_as_float(t2[j + e]) - dd) : 0.f;
                     }
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(pv[0], pv[1]);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(dsv[0], dsv[1]);
-                    e1[j >> 1] = *reinterpret_cast<uint32_t *>(&h1);
-                    e2[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                    float pv[4], dsv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pr = vis[e] ? fast_exp2(fmaf(__uint_as_float(t1[j + e]), sl2, -m2[e])) * il[e] : 0.f;
+                        pv[e] = pr;
+                        dsv[e] = vis[e] ? pr * (__uint_as_float(t2[j + e]) - dd[e]) : 0.f;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; e += 2) {
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(pv[e], pv[e + 1]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(dsv[e], dsv[e + 1]);
+                        e1[(j + e) >> 1] = *reinterpret_cast<uint32_t *>(&h1);
+                        e2[(j + e) >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                    }
                 }
                 // A-operand layout: 8x8 core matrices, K (the streamed index) inside a core row
                 const int rowoff = (L >> 3) * E_SBO + (L & 7) * 16 + cc * 4 * 128;

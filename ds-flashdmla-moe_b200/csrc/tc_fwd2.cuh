@@ -55,6 +55,10 @@ constexpr int BOX = 8192;
 #define FDMLA_NSLOT 7
 #endif
 constexpr int NSLOT = FDMLA_NSLOT;
+#ifndef FDMLA_PEMPTY
+#define FDMLA_PEMPTY 1
+#endif
+constexpr bool USE_PEMPTY = FDMLA_PEMPTY != 0;   // per-quarter hand-back of P (else: whole tile via OREADY)
 constexpr int PF_DIST = 1;             // decode: tiles of distance of the softmax threads' L2 prefetch (0 = off)
 constexpr int P_Q = 64 * SUB * 2;     // one P quarter: 64 rows x 64 keys bf16 = 8 192
 constexpr int P_BYTES = 4 * P_Q;
@@ -616,7 +620,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                                       16, 128, idesc_pv, (t | q) != 0);
                             mma_commit_2cta(BAR(B_EMPTY + sl[j]), 3);
                         }
-                        mma_commit_2cta(BAR(B_PEMPTY + q), 3);                    // this P quarter may be overwritten
+                        if (USE_PEMPTY) mma_commit_2cta(BAR(B_PEMPTY + q), 3);    // this P quarter may be overwritten
                         if (last) mma_commit_2cta(BAR(B_OREADY + (tg & 1)), 3);   // tile t folded into O
                     }
                 };
@@ -758,9 +762,14 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 tmax = fmaxf(tmax, red[(tg & 1) * 128 + (L ^ 64)]);
                 const float m_new = fmaxf(m_true, tmax);
                 const bool need = m_new > m_ref + 8.f;
+                if (!USE_PEMPTY && t > 0) {
+                    // P*V of tile t-1 must be complete before its P is overwritten or O rescaled
+                    if (ok && !(ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1))) fail = ERR_SOFTMAX_RESCALE;
+                    tc_fence_after_sync();
+                }
                 if (__any_sync(0xffffffffu, need)) {
                     // O is rescaled: every P*V of tile t-1 must have been accumulated
-                    if (t > 0) {
+                    if (USE_PEMPTY && t > 0) {
                         if (ok && !(ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1))) fail = ERR_SOFTMAX_RESCALE;
                         tc_fence_after_sync();
                     }
@@ -814,7 +823,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     }
                     const int quarter = 2 * half + (cc >> 1);
                     // the last P*V that read this quarter's previous contents is done
-                    if (!(cc & 1) && p_reads[cc >> 1] > 0 && ok &&
+                    if (USE_PEMPTY && !(cc & 1) && p_reads[cc >> 1] > 0 && ok &&
                         !(ok = mbar_wait(BAR(B_PEMPTY + quarter), (p_reads[cc >> 1] - 1) & 1))) {
                         fail = ERR_SOFTMAX_P;
 #ifdef FDMLA_TRACE
