@@ -55,6 +55,9 @@ constexpr int BOX = 8192;
 #define FDMLA_NSLOT 7
 #endif
 constexpr int NSLOT = FDMLA_NSLOT;
+#ifndef FDMLA_TMA_EPI
+#define FDMLA_TMA_EPI 1
+#endif
 #ifndef FDMLA_PEMPTY
 #define FDMLA_PEMPTY 1
 #endif
@@ -740,17 +743,21 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 const bool all_visible = tok0 >= lo && tok0 + 128 <= upper && sl2 > 0.f;
                 float tmax = -CUDART_INF_F;
 #pragma unroll 1
-                for (int cc = 0; cc < 4; ++cc) {
-                    tmem_ld32(s_addr + cc * 32, r);
+                for (int cp = 0; cp < 4; cp += 2) {
+                    // two 32-column loads in flight per wait
+                    uint32_t r2[32];
+                    tmem_ld32(s_addr + cp * 32, r);
+                    tmem_ld32(s_addr + (cp + 1) * 32, r2);
                     tmem_wait_ld();
                     if (all_visible) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(r[j]));
+                        for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, fmaxf(__uint_as_float(r[j]), __uint_as_float(r2[j])));
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            const int tok = tok0 + cc * 32 + j;
+                            const int tok = tok0 + cp * 32 + j;
                             if (tok >= lo && tok < upper) tmax = fmaxf(tmax, __uint_as_float(r[j]) * sl2);
+                            if (tok + 32 >= lo && tok + 32 < upper) tmax = fmaxf(tmax, __uint_as_float(r2[j]) * sl2);
                         }
                     }
                 }
@@ -877,8 +884,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             const size_t grow = (size_t)it.g * p.R + (row_ok ? rr : 0);
             const size_t prow_idx = (size_t)it.split * p.G * p.R + grow;
             const int col0 = 256 * half;
-            if (final_out && it.rows_here == 128) {
-                // bf16 result of a full tile: staged in the (now idle) P buffer as 64-row x 64-column boxes in
+            if (FDMLA_TMA_EPI && final_out && it.rows_here == 128 && p.Sq == 1) {
+                // bf16 result of a full decode tile (prefill measured 2 % faster with the plain row stores
+                // below): staged in the (now idle) P buffer as 64-row x 64-column boxes in
                 // the 128-byte swizzle and written by TMA tensor stores.  Each key-half group of 64 threads
                 // (rows 0-63, 256 of the d_v columns) ping-pongs between two 8 KB boxes.
                 uint8_t *box0 = sP + half * (2 * BOX);
