@@ -43,9 +43,9 @@ DECODE_BYTES = (B * SKV * D_QK * 2          # latent rows read once
                 + B * (SKV // PAGE) * 4)    # page table            = 639 795 200
 DECODE_FLOP = 2 * B * H * SKV * (D_QK + D_V)
 # DRAM bytes per sequence of one decode launch, from the ncu capture of the B=32 case
-# (profiles/fwd_tc2_kernel_decode_b32.md: read 157.15 MB + write 4.71 MB for 32 sequences); traffic grows in
+# (profiles/fwd_tc2_kernel_decode_b32.md: read 157.63 MB + write 3.66 MB for 32 sequences); traffic grows in
 # proportion to the sequences, so a launch of B sequences moves B times this.
-NCU_DRAM_BYTES_PER_SEQ = (157_146_624 + 4_708_864) / 32
+NCU_DRAM_BYTES_PER_SEQ = (157_634_048 + 3_657_728) / 32
 PF_B, PF_H, PF_S = 4, 128, 8192
 PREFILL_FLOP_CAUSAL = 2 * PF_B * PF_H * (PF_S * (PF_S + 1) // 2) * (D_QK + D_V)
 

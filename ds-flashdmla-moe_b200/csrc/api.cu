@@ -217,10 +217,20 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_t
         // A final result is wanted and there are spare slabs: the 2-CTA tensor kernel may hand out the
         // keys as balanced runs of tiles instead of num_splits equal pieces of every sequence (other
         // kernels ignore the hint).  It writes uncut sequences straight to O, so it needs O.
+        // It does so when that is predicted to be faster than the equal pieces: the longest run of tiles a CTA
+        // pair gets, with sequences of the maximum length, against whole waves of equal pieces.
         const int nt_max = (max_pages * page_size + 255) / 256;
-        p.balanced = 1;
-        p.quota_min = (nt_max + num_splits - 2) / (num_splits - 1);
-        p.O = O;
+        const int units = kNumSMs / 2;
+        const int quota_min = (nt_max + num_splits - 2) / (num_splits - 1);
+        const long long run = ((long long)B * nt_max + units - 1) / units;
+        const double bal = (double)(run > quota_min ? run : quota_min) + 1.5;
+        const long long waves = ((long long)B * num_splits + units - 1) / units;
+        const double eq = (double)waves * ((double)nt_max / num_splits + 1.5);
+        if (bal < eq) {
+            p.balanced = 1;
+            p.quota_min = quota_min;
+            p.O = O;
+        }
     }
     int rc = run_forward(p, dtype, st);
     if (rc) return rc;
