@@ -157,6 +157,7 @@ def cpu_baseline_sample(target_s=12.0):
     """Oracle (port of the reference's naive attention) on the host cores, bounded sample."""
     from flashdmla import synthetic
     from oracle import dmla_oracle as orc
+    orc.use_all_cores()
     def run(nseq):
         Q, pool, table, sl = synthetic.paged_decode_inputs(nseq, H, [SKV] * nseq, D_QK, PAGE, seed=3, std=0.1,
                                                           dtype=torch.float32)
@@ -177,6 +178,7 @@ def run_reference(args, rank, world):
         return
     from flashdmla import synthetic
     from oracle import dmla_oracle as orc
+    orc.use_all_cores()
     probe = 2
     Q, pool, table, sl = synthetic.paged_decode_inputs(probe, H, [SKV] * probe, D_QK, PAGE, seed=3, std=0.1,
                                                       dtype=torch.float32)

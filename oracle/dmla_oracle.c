@@ -465,6 +465,17 @@ void oracle_split_range(int n, int parts, int r, int *off, int *len)
     *off = r * base + (r < rem ? r : rem);
 }
 
+/* A launcher may have pinned OpenMP to one thread (torchrun exports OMP_NUM_THREADS=1); the timed CPU
+ * baseline asks for all host cores explicitly. */
+void oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void)
 {
 #ifdef _OPENMP

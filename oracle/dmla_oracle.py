@@ -77,6 +77,17 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores() -> int:
+    """Undo a launcher's OMP_NUM_THREADS=1 for the timed CPU baseline; returns the thread count in use."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    L = lib()
+    L.oracle_set_num_threads.restype = None
+    L.oracle_set_num_threads.argtypes = [ctypes.c_int]
+    L.oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def attn_plain(Q, K, V, scale):
     """Single-head non-causal attention: the reference launchers' problem."""
     Q, K, V = _f32(Q), _f32(K), _f32(V)
