@@ -217,7 +217,8 @@ def test_merge_matches_oracle(cuda):
 
 # ----------------------------------------------------------------------------- backward
 @pytest.mark.parametrize("shape", [(2, 2, 19, 23, 24, 16, True), (1, 3, 64, 64, 128, 64, True),
-                                   (1, 2, 70, 100, 128, 64, False)])
+                                   (1, 2, 70, 100, 128, 64, False), (2, 2, 300, 333, 128, 64, True),
+                                   (1, 2, 333, 300, 128, 64, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_on_the_fly_backward(shape, dtype, backend, cuda):
     import flashdmla
