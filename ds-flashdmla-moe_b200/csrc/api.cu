@@ -177,7 +177,9 @@ int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,
         // the partials of the sequences that get cut (at most one per CTA pair; together about seven
         // tile times on a B200).  The slabs only bound how often one sequence may be cut.
         const double run = std::ceil((double)B * tiles / units);
-        int slabs = (int)std::ceil(tiles / run) + 1;
+        // twice the pieces a full-length sequence needs: ragged batches have fewer tiles than B x max, so their
+        // runs are shorter than `run` and a long sequence is cut more often
+        int slabs = 2 * (int)std::ceil(tiles / run) + 1;
         if (slabs < 2) slabs = 2;
         if (slabs > 64) slabs = 64;
         const double run_eff = std::fmax(run, std::ceil(tiles / (slabs - 1)));

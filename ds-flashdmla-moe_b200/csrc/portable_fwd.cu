@@ -285,10 +285,62 @@ merge_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
     }
 }
 
+// The same merge with one block per row (few rows, many parts: more loads in flight per row).
+template <typename TO>
+__global__ void __launch_bounds__(128)
+merge_row_block_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
+                       const float *__restrict__ l_part, TO *__restrict__ O, float *__restrict__ m,
+                       float *__restrict__ l, long long rows, int d_v, int P) {
+    const long long r = blockIdx.x;
+    if (l_part[r] < 0.f) return;
+    float mx = -CUDART_INF_F;
+    for (int q = 0; q < P; ++q)
+        if (l_part[q * rows + r] > 0.f) mx = fmaxf(mx, m_part[q * rows + r]);
+    float ls = 0.f;
+    for (int q = 0; q < P; ++q) {
+        const float lp = l_part[q * rows + r];
+        if (lp > 0.f) ls += lp * __expf(m_part[q * rows + r] - mx);
+    }
+    const float inv = ls > 0.f ? 1.f / ls : 0.f;
+    for (int c = threadIdx.x * 4; c < d_v; c += 512) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int q = 0; q < P; ++q) {
+            const float lp = l_part[q * rows + r];
+            if (lp > 0.f) {
+                const float w = lp * __expf(m_part[q * rows + r] - mx) * inv;
+                const float *src = O_part + ((size_t)q * rows + r) * d_v;
+                if (c + 3 < d_v && (d_v & 3) == 0) {
+                    const float4 v = *reinterpret_cast<const float4 *>(src + c);
+                    acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
+                    acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+                } else {
+                    for (int e = 0; e < 4; ++e)
+                        if (c + e < d_v) acc[e] = fmaf(w, src[c + e], acc[e]);
+                }
+            }
+        }
+        for (int e = 0; e < 4; ++e)
+            if (c + e < d_v) O[(size_t)r * d_v + c + e] = from_f32<TO>(acc[e]);
+    }
+    if (threadIdx.x == 0) { m[r] = mx; l[r] = ls; }
+}
+
 int launch_merge(const float *O_part, const float *m_part, const float *l_part, void *O,
                  float *m, float *l, long long rows, int d_v, int num_parts, int out_dtype,
                  cudaStream_t stream) {
     if (rows <= 0) return FDMLA_OK;
+    if (rows <= 4096) {      // a block per row keeps more of the GPU busy than a warp per row would
+        if (out_dtype == FDMLA_F32)
+            merge_row_block_kernel<float><<<(unsigned)rows, 128, 0, stream>>>(O_part, m_part, l_part, static_cast<float *>(O), m, l,
+                                                                               rows, d_v, num_parts);
+        else if (out_dtype == FDMLA_BF16)
+            merge_row_block_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(
+                O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O), m, l, rows, d_v, num_parts);
+        else
+            return FDMLA_ERR_INVALID;
+        return check_launch();
+    }
     const long long want = (rows + 7) / 8;
     const unsigned grid = (unsigned)(want < 8LL * kNumSMs ? want : 8LL * kNumSMs);
     if (out_dtype == FDMLA_F32)
