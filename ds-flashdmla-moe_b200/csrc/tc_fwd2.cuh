@@ -229,8 +229,9 @@ __device__ __forceinline__ int sched_tiles(const FwdProblem &p, int g) {
 }
 
 // Called by all 32 lanes of a warp together.
+template <bool DECODE>
 __device__ __forceinline__ void cursor_init(Cursor &c, const FwdProblem &p, int cid, int n_clusters, int lane) {
-    c.balanced = p.balanced != 0;
+    c.balanced = DECODE && p.balanced != 0;
     c.cid = cid;
     c.n_clusters = n_clusters;
     c.round = 0;
@@ -308,6 +309,9 @@ __device__ __forceinline__ bool cursor_next(Cursor &c, const FwdProblem &p, bool
     return true;
 }
 
+// DECODE (one query token per KV group row set): L2 prefetch, TMA-store epilogue and the balanced schedule
+// are compiled in; the prefill instantiation carries none of them.
+template <bool DECODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO) {
@@ -407,7 +411,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         int ptr_n = 0;
 #endif
         Cursor cur;
-        cursor_init(cur, p, cid, n_clusters, lane);
+        cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
         Item it;
         for (int round = 0; ok && cursor_next(cur, p, poisoned, it); ++round) {
             if (it.n_tiles == 0) continue;
@@ -535,7 +539,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             int ntr = 0;
 #endif
             Cursor cur;
-            cursor_init(cur, p, cid, n_clusters, lane);
+            cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
             Item it;
             for (int round = 0; cursor_next(cur, p, poisoned, it); ++round) {
                 if (!__all_sync(0xffffffffu, ok)) break;
@@ -658,7 +662,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             int slot = 0, use = 0, q_loads = 0, fix_uses = 0;
             bool ok = true;
             Cursor cur;
-            cursor_init(cur, p, cid, n_clusters, lane);
+            cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
             Item it;
             for (int round = 0; ok && cursor_next(cur, p, poisoned, it); ++round) {
                 if (it.n_tiles == 0) continue;
@@ -686,7 +690,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         const uint32_t pfull_leader = map_to_cta(BAR(B_PFULL), 0);
         const uint32_t sempty_leader = map_to_cta(BAR(B_SEMPTY), 0);
         const uint32_t ofree_leader = map_to_cta(BAR(B_OFREE), 0);
-        const bool do_prefetch = p.Sq == 1;     // decode streams the cache from HBM; prefill finds it in L2 anyway
+        constexpr bool do_prefetch = DECODE;    // decode streams the cache from HBM; prefill finds it in L2 anyway
         bool ok = true;
         int fail = 0;                           // which wait gave up first
         // P*V passes that have read this thread's two P quarters so far (a quarter past the end of the
@@ -695,7 +699,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         int tg0 = 0;                            // tiles of the items before the current one
         uint32_t r[32];
         Cursor cur;
-        cursor_init(cur, p, cid, n_clusters, lane);
+        cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
         Item it;
         for (int round = 0; cursor_next(cur, p, poisoned, it); ++round) {
             const int rr = it.row0 + 64 * (int)rank + row;
@@ -884,7 +888,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             const size_t grow = (size_t)it.g * p.R + (row_ok ? rr : 0);
             const size_t prow_idx = (size_t)it.split * p.G * p.R + grow;
             const int col0 = 256 * half;
-            if (FDMLA_TMA_EPI && final_out && it.rows_here == 128 && p.Sq == 1) {
+            if (FDMLA_TMA_EPI && DECODE && final_out && it.rows_here == 128) {
                 // bf16 result of a full decode tile (prefill measured 2 % faster with the plain row stores
                 // below): staged in the (now idle) P buffer as 64-row x 64-column boxes in
                 // the 128-byte swizzle and written by TMA tensor stores.  Each key-half group of 64 threads
@@ -1047,7 +1051,7 @@ static int resident_clusters() {
     cfg.attrs = &at;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, fwd_tc2_kernel, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, fwd_tc2_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
         cudaGetLastError();
         int sms = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) return -1;
@@ -1085,15 +1089,18 @@ int launch_fwd_tensor2(const FwdProblem &p_in, cudaStream_t stream) {
     if (!make_tensor_map_bf16(&tmK, p.K, kv_rows, p.d_qk, 64)) return FDMLA_ERR_CUDA;
     tmO = tmK;
     if (p.O && !make_tensor_map_bf16(&tmO, p.O, (long long)p.G * p.R, p.d_v, 64)) return FDMLA_ERR_CUDA;
-    if (cudaFuncSetAttribute(tc2::fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES) != cudaSuccess)
+    const bool decode = p.Sq == 1;
+    auto kern = decode ? tc2::fwd_tc2_kernel<true> : tc2::fwd_tc2_kernel<false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES) != cudaSuccess)
         return FDMLA_ERR_CUDA;
+    if (!decode) p.balanced = 0;
     // persistent grid: as many CTA pairs as the device keeps resident at once (one CTA per SM), each
     // walking its share of the (row tile, KV group, split) items
     const long long n_items = (long long)((p.R + 127) / 128) * p.G * p.num_splits;
     const int resident = tc2::resident_clusters();
     if (resident <= 0) return FDMLA_ERR_CUDA;
     const int n_clusters = (p.balanced || n_items >= resident) ? resident : (int)n_items;
-    tc2::fwd_tc2_kernel<<<dim3(2 * n_clusters), tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmO);
+    kern<<<dim3(2 * n_clusters), tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmO);
     return check_launch();
 }
 
