@@ -36,16 +36,17 @@ namespace tcb {
 constexpr int TILE = 128;                 // rows and keys per tile
 constexpr int D = 64;                     // latent width
 constexpr int OP_BYTES = TILE * D * 2;    // 16 384: one operand tile
-constexpr int E_BYTES = TILE * TILE * 2;  // 32 768: one elementwise result (A operand, K = 128)
-constexpr int E_SBO = (TILE / 8) * 128;   // 2 048: stride between 8-row groups of the un-swizzled layout
+constexpr int HALF = 64;                  // streamed indices per pipeline step (half a tile)
+constexpr int E_BYTES = TILE * HALF * 2;  // 16 384: one elementwise result of a half tile (A operand, K = 64)
+constexpr int E_SBO = (HALF / 8) * 128;   // 1 024: stride between 8-row groups of the un-swizzled layout
 constexpr int VEC_BYTES = 2 * 4 * TILE * 4;
 // barriers
-constexpr int B_OWNER = 0, B_FULL = 1, B_EMPTY = 3, B_SREADY = 5, B_PREADY = 6, B_DONE = 7, NBARS = 8;
-constexpr int SMEM_BYTES = 1024 + 2 * OP_BYTES + 4 * OP_BYTES + 2 * E_BYTES + VEC_BYTES + NBARS * 8 + 16;
+constexpr int B_OWNER = 0, B_FULL = 1, B_EMPTY = 3, B_SREADY = 5, B_PREADY = 7, B_DONE = 9, NBARS = 10;
+constexpr int SMEM_BYTES = 1024 + 2 * OP_BYTES + 4 * OP_BYTES + 4 * E_BYTES + VEC_BYTES + NBARS * 8 + 16;
 static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
 constexpr int THREADS = 160;
 // tensor memory columns
-constexpr int C_T1 = 0, C_T2 = 128, C_ACC1 = 256, C_ACC2 = 320, TMEM_COLS = 512;
+constexpr int C_T1 = 0, C_T2 = 128, C_ACC1 = 256, C_ACC2 = 320, TMEM_COLS = 512;     // T1/T2: two 64-column halves each
 enum { MODE_DKV = 0, MODE_DQ = 1 };
 enum { ERR_BWD = 21 };
 
@@ -67,9 +68,9 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
     uint8_t *sA1 = smem;                      // owner tile 1 (K or Q)
     uint8_t *sA2 = sA1 + OP_BYTES;            // owner tile 2 (V or dO)
     uint8_t *sB = sA2 + OP_BYTES;             // streamed tiles: [buf][B1 | B2]
-    uint8_t *sE1 = sB + 4 * OP_BYTES;         // P^T (MODE_DKV only)
-    uint8_t *sE2 = sE1 + E_BYTES;             // dS^T / dS
-    float *vec = reinterpret_cast<float *>(sE2 + E_BYTES);    // [buf][m, 1/l, D, last visible key][128]  (MODE_DKV)
+    uint8_t *sE1 = sB + 4 * OP_BYTES;         // P^T, one buffer per half tile (MODE_DKV only)
+    uint8_t *sE2 = sE1 + 2 * E_BYTES;         // dS^T / dS, one buffer per half tile
+    float *vec = reinterpret_cast<float *>(sE2 + 2 * E_BYTES);    // [buf][m, 1/l, D, last visible key][128]  (MODE_DKV)
     uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(vec) + VEC_BYTES);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     const uint32_t bar0 = smem_u32(bars);
@@ -106,8 +107,10 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
             mbar_init(BAR(B_FULL + b), 1);
             mbar_init(BAR(B_EMPTY + b), 1);
         }
-        mbar_init(BAR(B_SREADY), 1);
-        mbar_init(BAR(B_PREADY), 1);
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(BAR(B_SREADY + h), 1);
+            mbar_init(BAR(B_PREADY + h), 1);
+        }
         mbar_init(BAR(B_DONE), 1);
         fence_mbar_init();
     }
@@ -149,45 +152,64 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 tma_load_2d(smem_u32(sA2), mapA2, 0, own_rows_base + own0, BAR(B_OWNER));
             }
             load_stream(0);
+            if (n_stream > 1) load_stream(1);
             ok = mbar_wait(BAR(B_OWNER), 0);
-            for (int i = 0; i < n_stream; ++i) {
-                if (!__all_sync(0xffffffffu, ok)) break;
-                const int buf = i & 1;
-                const uint32_t b1 = smem_u32(sB + buf * 2 * OP_BYTES), b2 = b1 + OP_BYTES;
-                ok = ok && mbar_wait(BAR(B_FULL + buf), (i >> 1) & 1);
-                tc_fence_after_sync();
+            constexpr uint32_t idesc_th = make_idesc_bf16(128, HALF, 0, 0);
+            // Score GEMMs of one half tile (64 streamed rows): T1[h] = A1 B1[h]^T, T2[h] = A2 B2[h]^T
+            auto issue_t = [&](int i, int h) {
+                const uint32_t b1 = smem_u32(sB + (i & 1) * 2 * OP_BYTES) + h * (HALF * 128), b2 = b1 + OP_BYTES;
                 if (elected) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        mma_bf16_ss(tmem + C_T1, make_smem_desc(smem_u32(sA1) + k * 32, 16, 1024, kLayoutSw128),
-                                    make_smem_desc(b1 + k * 32, 16, 1024, kLayoutSw128), idesc_t, k != 0);
-                    }
+                    for (int k = 0; k < 4; ++k)
+                        mma_bf16_ss(tmem + C_T1 + h * HALF, make_smem_desc(smem_u32(sA1) + k * 32, 16, 1024, kLayoutSw128),
+                                    make_smem_desc(b1 + k * 32, 16, 1024, kLayoutSw128), idesc_th, k != 0);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        mma_bf16_ss(tmem + C_T2, make_smem_desc(smem_u32(sA2) + k * 32, 16, 1024, kLayoutSw128),
-                                    make_smem_desc(b2 + k * 32, 16, 1024, kLayoutSw128), idesc_t, k != 0);
-                    }
-                    mma_commit(BAR(B_SREADY));
+                    for (int k = 0; k < 4; ++k)
+                        mma_bf16_ss(tmem + C_T2 + h * HALF, make_smem_desc(smem_u32(sA2) + k * 32, 16, 1024, kLayoutSw128),
+                                    make_smem_desc(b2 + k * 32, 16, 1024, kLayoutSw128), idesc_th, k != 0);
+                    mma_commit(BAR(B_SREADY + h));
                 }
-                // the other buffer was last read by the accumulating GEMMs of tile i-1
-                if (i + 1 < n_stream) {
-                    if (i >= 1) ok = ok && mbar_wait(BAR(B_EMPTY + (buf ^ 1)), ((i - 1) >> 1) & 1);
-                    load_stream(i + 1);
-                }
-                ok = ok && mbar_wait(BAR(B_PREADY), i & 1);
-                tc_fence_after_sync();
+            };
+            // Accumulating GEMMs of one half tile: acc1 += E1[h] B2[h], acc2 += E2[h] B1[h] (reduction over its 64 rows)
+            auto issue_acc = [&](int i, int h) {
+                const uint32_t b1 = smem_u32(sB + (i & 1) * 2 * OP_BYTES) + h * (HALF * 128), b2 = b1 + OP_BYTES;
                 if (elected) {
                     if (MODE == MODE_DKV) {
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            mma_bf16_ss(tmem + C_ACC1, make_smem_desc(smem_u32(sE1) + k * 256, 128, E_SBO, kLayoutNone),
-                                        make_smem_desc(b2 + k * 2048, OP_BYTES, 1024, kLayoutSw128), idesc_acc, (i | k) != 0);
+                        for (int k = 0; k < 4; ++k)
+                            mma_bf16_ss(tmem + C_ACC1, make_smem_desc(smem_u32(sE1 + h * E_BYTES) + k * 256, 128, E_SBO, kLayoutNone),
+                                        make_smem_desc(b2 + k * 2048, OP_BYTES, 1024, kLayoutSw128), idesc_acc, (i | h | k) != 0);
                     }
 #pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        mma_bf16_ss(tmem + C_ACC2, make_smem_desc(smem_u32(sE2) + k * 256, 128, E_SBO, kLayoutNone),
-                                    make_smem_desc(b1 + k * 2048, OP_BYTES, 1024, kLayoutSw128), idesc_acc, (i | k) != 0);
-                    mma_commit(BAR(B_EMPTY + buf));
+                    for (int k = 0; k < 4; ++k)
+                        mma_bf16_ss(tmem + C_ACC2, make_smem_desc(smem_u32(sE2 + h * E_BYTES) + k * 256, 128, E_SBO, kLayoutNone),
+                                    make_smem_desc(b1 + k * 2048, OP_BYTES, 1024, kLayoutSw128), idesc_acc, (i | h | k) != 0);
+                    if (h == 1) mma_commit(BAR(B_EMPTY + (i & 1)));      // the tile's buffer has been read for the last time
+                }
+            };
+            ok = ok && mbar_wait(BAR(B_FULL), 0);
+            tc_fence_after_sync();
+            issue_t(0, 0);
+            issue_t(0, 1);
+            for (int i = 0; i < n_stream; ++i) {
+                if (!__all_sync(0xffffffffu, ok)) break;
+                for (int h = 0; h < 2; ++h) {
+                    // the elementwise warps have turned T[h] of tile i into E[h]
+                    ok = ok && mbar_wait(BAR(B_PREADY + h), i & 1);
+                    tc_fence_after_sync();
+                    issue_acc(i, h);
+                    if (i + 1 < n_stream) {
+                        // ... and T[h] is free for the next tile's half, which overlaps the other half's elementwise work
+                        if (h == 0) {
+                            ok = ok && mbar_wait(BAR(B_FULL + ((i + 1) & 1)), ((i + 1) >> 1) & 1);
+                            tc_fence_after_sync();
+                        }
+                        issue_t(i + 1, h);
+                    }
+                }
+                if (i + 2 < n_stream) {
+                    ok = ok && mbar_wait(BAR(B_EMPTY + (i & 1)), (i >> 1) & 1);
+                    load_stream(i + 2);
                 }
             }
             if (elected) mma_commit(BAR(B_DONE));
@@ -238,10 +260,13 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 reinterpret_cast<int *>(vb)[3 * TILE + L] = last_key;
                 named_bar_sync(1, 128);
             }
-            if (ok) ok = mbar_wait(BAR(B_SREADY), i & 1);
-            tc_fence_after_sync();
 #pragma unroll 1
             for (int cc = 0; cc < 4; ++cc) {
+                const int h = cc >> 1;                     // half tile this 32-column chunk belongs to
+                if (!(cc & 1)) {
+                    if (ok) ok = mbar_wait(BAR(B_SREADY + h), i & 1);
+                    tc_fence_after_sync();
+                }
                 uint32_t t1[32], t2[32];
                 tmem_ld32(tmem + lane_base + C_T1 + cc * 32, t1);
                 tmem_ld32(tmem + lane_base + C_T2 + cc * 32, t2);
@@ -287,8 +312,8 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                         e2[(j + e) >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                     }
                 }
-                // A-operand layout: 8x8 core matrices, K (the streamed index) inside a core row
-                const int rowoff = (L >> 3) * E_SBO + (L & 7) * 16 + cc * 4 * 128;
+                // A-operand layout of the half tile: 8x8 core matrices, K (the streamed index) inside a core row
+                const int rowoff = h * E_BYTES + (L >> 3) * E_SBO + (L & 7) * 16 + (cc & 1) * 4 * 128;
 #pragma unroll
                 for (int kc = 0; kc < 4; ++kc) {
                     if (MODE == MODE_DKV)
@@ -297,11 +322,13 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                     *reinterpret_cast<uint4 *>(sE2 + rowoff + kc * 128) =
                         make_uint4(e2[4 * kc], e2[4 * kc + 1], e2[4 * kc + 2], e2[4 * kc + 3]);
                 }
+                if (cc & 1) {
+                    tc_fence_before_sync();
+                    fence_proxy_async_smem();
+                    named_bar_sync(1, 128);
+                    if (L == 0) mbar_arrive(BAR(B_PREADY + h));
+                }
             }
-            tc_fence_before_sync();
-            fence_proxy_async_smem();
-            named_bar_sync(1, 128);
-            if (L == 0) mbar_arrive(BAR(B_PREADY));
         }
         if (active) {
             if (ok) ok = mbar_wait(BAR(B_DONE), 0);
