@@ -44,7 +44,8 @@ constexpr int VEC_BYTES = 2 * 4 * TILE * 4;
 constexpr int B_OWNER = 0, B_FULL = 1, B_EMPTY = 3, B_SREADY = 5, B_PREADY = 7, B_DONE = 9, NBARS = 10;
 constexpr int SMEM_BYTES = 1024 + 2 * OP_BYTES + 4 * OP_BYTES + 4 * E_BYTES + VEC_BYTES + NBARS * 8 + 16;
 static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
-constexpr int THREADS = 160;
+constexpr int THREADS = 288;              // 8 elementwise warps (two per TMEM lane quarter) + the control warp
+constexpr int CTRL_WARP = 8;
 // tensor memory columns
 constexpr int C_T1 = 0, C_T2 = 128, C_ACC1 = 256, C_ACC2 = 320, TMEM_COLS = 512;     // T1/T2: two 64-column halves each
 enum { MODE_DKV = 0, MODE_DQ = 1 };
@@ -114,7 +115,7 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
         mbar_init(BAR(B_DONE), 1);
         fence_mbar_init();
     }
-    if (warp == 4) {
+    if (warp == CTRL_WARP) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
@@ -129,7 +130,7 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
     const int own_rows_base = MODE == MODE_DKV ? g * p.Skv : g * p.R;      // global row of the group's first owner row
     const int str_rows_base = MODE == MODE_DKV ? g * p.R : g * p.Skv;
 
-    if (warp == 4) {
+    if (warp == CTRL_WARP) {
         // =========================== TMA + MMA issue ======================================
         if (active) {
             const bool elected = elect_one();
@@ -218,8 +219,11 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
         __syncwarp();
     } else {
         // =========================== elementwise + epilogue ===============================
-        const int L = warp * 32 + lane;                    // TMEM lane: key (MODE_DKV) or row (MODE_DQ) own0 + L
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        // Warps w and w + 4 share TMEM lane quarter w (a warp may only touch lanes 32 (w % 4) ...) and split
+        // the columns: column group cg takes the 32-column chunks 2 h + cg of each half tile.
+        const int L = (warp & 3) * 32 + lane;              // TMEM lane: key (MODE_DKV) or row (MODE_DQ) own0 + L
+        const int cg = warp >> 2;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const float sl2 = p.scale * 1.4426950408889634f;
         bool ok = true;
         // per-lane quantities
@@ -256,17 +260,17 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                     dv = p.D[rr];
                     last_key = p.causal ? (r % p.Sq) + off : p.Skv - 1;
                 }
-                vb[L] = mv; vb[TILE + L] = il; vb[2 * TILE + L] = dv;
-                reinterpret_cast<int *>(vb)[3 * TILE + L] = last_key;
-                named_bar_sync(1, 128);
+                if (cg == 0) {
+                    vb[L] = mv; vb[TILE + L] = il; vb[2 * TILE + L] = dv;
+                    reinterpret_cast<int *>(vb)[3 * TILE + L] = last_key;
+                }
+                named_bar_sync(1, 256);
             }
 #pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                const int h = cc >> 1;                     // half tile this 32-column chunk belongs to
-                if (!(cc & 1)) {
-                    if (ok) ok = mbar_wait(BAR(B_SREADY + h), i & 1);
-                    tc_fence_after_sync();
-                }
+            for (int h = 0; h < 2; ++h) {                  // half tile; this thread's chunk of it is cc
+                const int cc = 2 * h + cg;
+                if (ok) ok = mbar_wait(BAR(B_SREADY + h), i & 1);
+                tc_fence_after_sync();
                 uint32_t t1[32], t2[32];
                 tmem_ld32(tmem + lane_base + C_T1 + cc * 32, t1);
                 tmem_ld32(tmem + lane_base + C_T2 + cc * 32, t2);
@@ -322,12 +326,10 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                     *reinterpret_cast<uint4 *>(sE2 + rowoff + kc * 128) =
                         make_uint4(e2[4 * kc], e2[4 * kc + 1], e2[4 * kc + 2], e2[4 * kc + 3]);
                 }
-                if (cc & 1) {
-                    tc_fence_before_sync();
-                    fence_proxy_async_smem();
-                    named_bar_sync(1, 128);
-                    if (L == 0) mbar_arrive(BAR(B_PREADY + h));
-                }
+                tc_fence_before_sync();
+                fence_proxy_async_smem();
+                named_bar_sync(1, 256);
+                if (L == 0 && cg == 0) mbar_arrive(BAR(B_PREADY + h));
             }
         }
         if (active) {
@@ -340,15 +342,15 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
         if (MODE == MODE_DKV) {
             float *dv_row = static_cast<float *>(p.dV) + ((size_t)g * p.Skv + (own_ok ? own_idx : 0)) * D;
             float *dk_row = static_cast<float *>(p.dK) + ((size_t)g * p.Skv + (own_ok ? own_idx : 0)) * D;
-#pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
+            {
+                const int cc = cg;
                 uint32_t a[32], b[32];
                 if (have) {
                     tmem_ld32(tmem + lane_base + C_ACC1 + cc * 32, a);
                     tmem_ld32(tmem + lane_base + C_ACC2 + cc * 32, b);
                     tmem_wait_ld();
                 }
-                if (!own_ok) continue;
+                if (own_ok) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
                     *reinterpret_cast<float4 *>(dv_row + cc * 32 + j) =
@@ -359,17 +361,18 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                                            __uint_as_float(b[j + 2]) * p.scale, __uint_as_float(b[j + 3]) * p.scale)
                              : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
+                }
             }
         } else {
             __nv_bfloat16 *dq_row = static_cast<__nv_bfloat16 *>(p.dQ) + ((size_t)g * p.R + (own_ok ? own_idx : 0)) * D;
-#pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
+            {
+                const int cc = cg;
                 uint32_t b[32];
                 if (have) {
                     tmem_ld32(tmem + lane_base + C_ACC2 + cc * 32, b);
                     tmem_wait_ld();
                 }
-                if (!own_ok) continue;
+                if (own_ok) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint32_t w[4];
@@ -382,13 +385,14 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                     }
                     *reinterpret_cast<uint4 *>(dq_row + cc * 32 + j) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+                }
             }
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == CTRL_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, TMEM_COLS);
     }
