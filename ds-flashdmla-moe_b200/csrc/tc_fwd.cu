@@ -188,7 +188,10 @@ fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
         }
     } else if (warp == 1) {
         // =========================== MMA issuer =====================================
-        if (lane == 0 && n_tiles > 0) {
+        // The whole warp runs the loop converged and one elected lane issues (descriptor arithmetic on the
+        // uniform datapath: about twice the issue rate of a lone lane of a diverged warp).
+        if (n_tiles > 0) {
+            const bool elected = elect_one();
             constexpr uint32_t idesc_qk = make_idesc_bf16(128, T, 0, 0);
             constexpr uint32_t idesc_pv = make_idesc_bf16(128, C::O_COLS, 0, 1);
             const uint32_t sQ_a = smem_u32(sQ), sKV_a = smem_u32(sKV), sP_a = smem_u32(sP);
@@ -200,38 +203,43 @@ fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
                 if (t >= 2 && !mbar_wait(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
                 tc_fence_after_sync();
                 const uint32_t kbase = sKV_a + stage * C::STAGE_BYTES;
+                if (elected) {
 #pragma unroll
-                for (int c = 0; c < C::NQC; ++c) {
+                    for (int c = 0; c < C::NQC; ++c) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint64_t da = make_smem_desc(sQ_a + c * C::Q_CHUNK + k * 32, 16, 1024, kLayoutSw128);
-                        const uint64_t db = make_smem_desc(kbase + c * C::KV_CHUNK + k * 32, 16, 1024, kLayoutSw128);
-                        mma_bf16_ss(tmem + C::S_COL0 + b * T, da, db, idesc_qk, (c | k) != 0);
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t da = make_smem_desc(sQ_a + c * C::Q_CHUNK + k * 32, 16, 1024, kLayoutSw128);
+                            const uint64_t db = make_smem_desc(kbase + c * C::KV_CHUNK + k * 32, 16, 1024, kLayoutSw128);
+                            mma_bf16_ss(tmem + C::S_COL0 + b * T, da, db, idesc_qk, (c | k) != 0);
+                        }
                     }
+                    mma_commit(BAR(B_SFULL + b));
                 }
-                mma_commit(BAR(B_SFULL + b));
                 return true;
             };
             if (ok) ok = issue_qk(0);
-            for (int t = 0; t < n_tiles && ok; ++t) {
+            for (int t = 0; t < n_tiles; ++t) {
+                if (!__all_sync(0xffffffffu, ok)) break;
                 if (t + 1 < n_tiles) ok = issue_qk(t + 1);
-                if (!ok) break;
+                if (!__all_sync(0xffffffffu, ok)) break;
                 ok = mbar_wait(BAR(B_PFULL), t & 1);
-                if (!ok) break;
+                if (!__all_sync(0xffffffffu, ok)) break;
                 tc_fence_after_sync();
                 const int stage = t % STAGES;
                 const uint32_t vbase = sKV_a + stage * C::STAGE_BYTES +
                                        (C::SEPV ? C::K_BYTES : vsplit * C::NVC * C::KV_CHUNK);
+                if (elected) {
 #pragma unroll
-                for (int ks = 0; ks < T / 16; ++ks) {
-                    const uint64_t da = make_smem_desc(sP_a + ks * 256, 128, C::P_SBO, kLayoutNone);
-                    const uint64_t db = make_smem_desc(vbase + ks * 2048, C::KV_CHUNK, 1024, kLayoutSw128);
-                    mma_bf16_ss(tmem, da, db, idesc_pv, (t | ks) != 0);
+                    for (int ks = 0; ks < T / 16; ++ks) {
+                        const uint64_t da = make_smem_desc(sP_a + ks * 256, 128, C::P_SBO, kLayoutNone);
+                        const uint64_t db = make_smem_desc(vbase + ks * 2048, C::KV_CHUNK, 1024, kLayoutSw128);
+                        mma_bf16_ss(tmem, da, db, idesc_pv, (t | ks) != 0);
+                    }
+                    mma_commit(BAR(B_KVEMPTY + stage));
+                    mma_commit(BAR(B_OREADY));
                 }
-                mma_commit(BAR(B_KVEMPTY + stage));
-                mma_commit(BAR(B_OREADY));
             }
-            if (!ok) atomicCAS(&g_tc_error, 0, ERR_MMA);
+            if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_MMA);
         }
         __syncwarp();
     } else {
