@@ -185,8 +185,8 @@ def run_reference(args, rank, world):
     t = time.perf_counter()
     orc.decode_paged(Q, pool, table, sl, D_V, SCALE)
     t1 = (time.perf_counter() - t) / probe
-    budget = 150.0 / max(1, args.steps + args.warmup)           # whole run within a few minutes
-    nseq = int(max(1, min(B, min(2.0, budget) / max(t1, 1e-3))))
+    per_step_s = 150.0 / max(1, args.steps + args.warmup)       # whole run within a few minutes
+    nseq = int(max(1, min(B, min(2.0, per_step_s) / max(t1, 1e-3))))
     Q, pool, table, sl = synthetic.paged_decode_inputs(nseq, H, [SKV] * nseq, D_QK, PAGE, seed=3, std=0.1,
                                                       dtype=torch.float32)
     for _ in range(args.warmup):
