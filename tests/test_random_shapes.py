@@ -72,3 +72,42 @@ def test_tensor_forward_agrees_with_cuda_core_forward_on_random_shapes(cuda):
             assert float((m - mr).abs().max()) < 1e-3 and float(((l - lr).abs() / lr).max()) < 2e-3, what
     finally:
         flashdmla.set_backend(flashdmla.BACKEND_AUTO)
+
+
+def test_tensor_backward_agrees_with_cuda_core_backward_on_random_shapes(cuda):
+    """On-the-fly mode with 64-wide latents: O and the five gradients from the tcgen05 kernels against the
+    CUDA-core kernels.  Gradients that are zero in exact arithmetic (one visible key) are compared against a
+    noise floor instead of their own norm."""
+    import flashdmla
+    rnd = random.Random(13)
+
+    def run(ts, dO, causal):
+        for t in ts:
+            t.grad = None
+        O, m, l = flashdmla.flash_dmla_on_the_fly(*ts, 0.125, causal)
+        O.backward(dO)
+        return [O.detach().float()] + [t.grad.float() for t in ts]
+    try:
+        for case in range(60):
+            B, H = rnd.choice([1, 2]), rnd.choice([1, 2, 5])
+            Sq = rnd.choice([1, 17, 64, 128, 129, 300, 513])
+            Skv = rnd.choice([Sq, Sq + 5, Sq + 256, 64, 700])
+            causal = rnd.choice([True, False])
+            if causal and Skv < Sq:
+                Skv = Sq
+            what = f"case {case}: B={B} H={H} Sq={Sq} Skv={Skv} causal={causal}"
+            g = torch.Generator(device=cuda).manual_seed(case)
+            mk = lambda *sh, s=1.0: (torch.randn(*sh, generator=g, device=cuda) * s).to(torch.bfloat16)
+            ts = [mk(B, H, Sq, 64), mk(B, H, Skv, 128), mk(B, H, Skv, 128), mk(128, 64, s=0.1), mk(128, 64, s=0.1)]
+            ts = [t.requires_grad_(True) for t in ts]
+            dO = mk(B, H, Sq, 64)
+            flashdmla.set_backend(flashdmla.BACKEND_AUTO)
+            a = run(ts, dO, causal)
+            assert flashdmla.last_kernel() == "tcgen05" and flashdmla.device_error_flag() == 0, what
+            flashdmla.set_backend(flashdmla.BACKEND_PORTABLE)
+            b = run(ts, dO, causal)
+            for x, y, name in zip(a, b, ("O", "dQ", "dK", "dV", "dWK", "dWV")):
+                den = max(float(y.norm()), 0.05 * math.sqrt(y.numel()))
+                assert float((x - y).norm()) / den < 3e-2, f"{what}: {name}"
+    finally:
+        flashdmla.set_backend(flashdmla.BACKEND_AUTO)
