@@ -62,7 +62,13 @@ constexpr int NSLOT = FDMLA_NSLOT;
 #define FDMLA_PEMPTY 1
 #endif
 constexpr bool USE_PEMPTY = FDMLA_PEMPTY != 0;   // per-quarter hand-back of P (else: whole tile via OREADY)
-constexpr int PF_DIST = 1;             // decode: tiles of distance of the softmax threads' L2 prefetch (0 = off)
+#ifndef FDMLA_PF_DIST
+#define FDMLA_PF_DIST 1
+#endif
+#ifndef FDMLA_PF_STEP
+#define FDMLA_PF_STEP 1
+#endif
+constexpr int PF_DIST = FDMLA_PF_DIST;  // decode: tiles of distance of the softmax threads' L2 prefetch (0 = off)
 constexpr int P_Q = 64 * SUB * 2;     // one P quarter: 64 rows x 64 keys bf16 = 8 192
 constexpr int P_BYTES = 4 * P_Q;
 constexpr int P_SBO = (SUB / 8) * 128;            // 1 024
@@ -735,7 +741,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                             const char *src = static_cast<const char *>(p.K) + ((size_t)sub_row(it, s, &bad_page) + row) * (NQC * 128);
                             if (!bad_page) {
 #pragma unroll
-                                for (int c = 0; c < NQC; ++c) prefetch_l2(src + c * 128);
+                                for (int c = 0; c < NQC; c += FDMLA_PF_STEP) prefetch_l2(src + c * 128);
                             }
                         }
                     }
