@@ -10,7 +10,13 @@ Two patterns, as the path shards:
     NCCL/NVLink and merged with the log-sum-exp rule.  The reference's MPI
     wrapper all-gathers the keys and values themselves on the host
     (fa2_fwd_mpi.cu:65-74); gathering the partials moves (d_v+2) floats per
-    row instead of the whole cache.
+    row instead of the whole cache;
+  * context-parallel prefill - the sequence dimension of a causal prefill is cut
+    into chunks, every rank owns the queries and the latent rows of its chunks,
+    the bf16 latent rows are all-gathered once (the counterpart of the
+    reference's host all-gather of K and V, fa2_fwd_mpi.cu:65-74: 1152 bytes per
+    token here, against H (d_v + 2) floats per token for gathered partials) and
+    every rank attends its own query chunks over the key prefix they may see.
 """
 from __future__ import annotations
 
@@ -100,3 +106,94 @@ def sequence_parallel_decode(Q, local_pool, local_page_table, local_seqlens, d_v
     if validate:          # synchronises; meant for debugging and for the failure-detection tests
         check_partials(O_p, m_p, l_p)
     return merge_fn(O_p, m_p, l_p, out_dtype or Q.dtype)
+
+
+# --------------------------------------------------------------------------- #
+# context-parallel causal prefill
+# --------------------------------------------------------------------------- #
+def context_chunks(world: int, rank: int, zigzag: bool = True) -> List[int]:
+    """Sequence chunks a rank owns, in the order they sit in its local tensors.
+
+    zigzag: the sequence is cut into 2*world chunks and rank r owns chunks r and
+    2*world-1-r.  Chunk c attends (c+1) chunks of keys, so every rank does
+    (r+1) + (2*world-r) = 2*world+1 chunk-blocks of work: the causal triangle is
+    balanced.  Otherwise: world chunks, rank r owns chunk r (the contiguous
+    split of fa2_fwd_mpi.cu:47-53; rank world-1 then does world times the work
+    of rank 0)."""
+    if not (0 <= rank < world):
+        raise ValueError("rank out of range")
+    return [rank, 2 * world - 1 - rank] if zigzag else [rank]
+
+
+def assemble_context(gathered: torch.Tensor, zigzag: bool = True) -> torch.Tensor:
+    """[world, B, S_local, d] as all-gathered (rank-major) -> [B, S, d] in sequence order."""
+    world, B, s_loc, d = gathered.shape
+    if not zigzag:
+        return gathered.permute(1, 0, 2, 3).reshape(B, world * s_loc, d)
+    if s_loc % 2:
+        raise ValueError("zigzag layout needs an even local length")
+    lc = s_loc // 2
+    first = gathered[:, :, :lc].permute(1, 0, 2, 3)                 # chunks 0 .. world-1
+    second = gathered[:, :, lc:].flip(0).permute(1, 0, 2, 3)        # chunks world .. 2 world-1
+    return torch.cat([first, second], dim=1).reshape(B, 2 * world * lc, d)
+
+
+def shard_context(x: torch.Tensor, world: int, rank: int, zigzag: bool = True, dim: int = -2) -> torch.Tensor:
+    """A rank's local part of a tensor whose dimension `dim` is the full sequence (the inverse
+    of assemble_context; for laying out inputs and for comparing results)."""
+    n_chunks = 2 * world if zigzag else world
+    S = x.shape[dim]
+    if S % n_chunks:
+        raise ValueError(f"sequence length {S} is not a multiple of {n_chunks} chunks")
+    lc = S // n_chunks
+    return torch.cat([x.narrow(dim, c * lc, lc) for c in context_chunks(world, rank, zigzag)], dim=dim).contiguous()
+
+
+def context_parallel_prefill(Q_local, K_lat_local, d_v, scale=None, group: Optional[dist.ProcessGroup] = None,
+                             zigzag: bool = True, attn_fn: Optional[Callable] = None,
+                             gather_fn: Optional[Callable] = None, world: Optional[int] = None,
+                             rank: Optional[int] = None):
+    """Causal cache-latent prefill with the sequence sharded across ranks (forward only).
+
+    Q_local [B,H,S_local,d_qk] and K_lat_local [B,S_local,d_qk] hold this rank's
+    chunks (context_chunks order).  Returns O [B,H,S_local,d_v], m, l [B,H,S_local]
+    for the same rows.  One all-gather of the latent rows; no other exchange.
+    attn_fn(Q, K_lat, d_v, scale) -> (O, m, l) defaults to the CUDA operator with
+    causal=True (bottom-right aligned, so a chunk of queries against the key prefix
+    that ends with the same chunk is exactly its slice of the full causal problem);
+    gather_fn(local) -> [world, ...] defaults to all_gather_into_tensor.  Tests
+    inject stand-ins for both.
+    """
+    if world is None:
+        world = dist.get_world_size(group)
+    if rank is None:
+        rank = dist.get_rank(group)
+    if attn_fn is None:
+        from . import ops
+
+        def attn_fn(Q, K, d_v, scale):
+            return ops.flash_dmla_cache_latent(Q, K, d_v, scale, causal=True)
+    if gather_fn is None:
+        def gather_fn(local):
+            flat = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+            dist.all_gather_into_tensor(flat, local.contiguous(), group=group)
+            return flat.view((world,) + tuple(local.shape))
+    if Q_local.dim() != 4 or K_lat_local.dim() != 3 or Q_local.shape[2] != K_lat_local.shape[1]:
+        raise ValueError("expected Q_local [B,H,S_local,d_qk] and K_lat_local [B,S_local,d_qk]")
+    chunks = context_chunks(world, rank, zigzag)
+    s_loc = Q_local.shape[2]
+    if s_loc % len(chunks):
+        raise ValueError("zigzag layout needs an even local length")
+    lc = s_loc // len(chunks)
+    if scale is None:
+        scale = 1.0 / (Q_local.shape[3] ** 0.5)
+    K_full = assemble_context(gather_fn(K_lat_local), zigzag)
+    outs = []
+    with torch.no_grad():
+        for i, c in enumerate(chunks):
+            q = Q_local[:, :, i * lc:(i + 1) * lc].contiguous()
+            k = K_full[:, :(c + 1) * lc].contiguous()
+            outs.append(attn_fn(q, k, d_v, scale))
+    if len(outs) == 1:
+        return outs[0]
+    return tuple(torch.cat([o[j] for o in outs], dim=2) for j in range(3))

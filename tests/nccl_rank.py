@@ -1,0 +1,70 @@
+"""One NCCL rank of the multi-GPU exchange checks (launched by test_multi_gpu.py through
+torch.distributed.run, one process per GPU).  Every rank builds the same seeded global problem,
+keeps its shard, runs the product path with the real collective and compares its result with
+the CPU oracle on the unsharded problem.  Exits non-zero on any mismatch."""
+import math
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "ds-flashdmla-moe_b200"), os.path.join(ROOT, "tests")]
+
+from helpers import assert_O, assert_stats          # noqa: E402
+from oracle import dmla_oracle as orc               # noqa: E402
+
+
+def context_parallel_case(dev, world, rank):
+    from flashdmla import device_error_flag, last_kernel
+    from flashdmla.parallel import context_parallel_prefill, shard_context
+    g = torch.Generator().manual_seed(33)
+    Q = (torch.randn(1, 16, 1024, 576, generator=g) * 0.1).to(torch.bfloat16)
+    K = (torch.randn(1, 1024, 576, generator=g) * 0.1).to(torch.bfloat16)
+    sc = 1 / math.sqrt(192)
+    Of, mf, lf = (torch.from_numpy(x) for x in orc.fwd_cache_latent(Q.float().numpy(), K.float().numpy(), 512, sc, causal=True))
+    for zigzag in (True, False):
+        O, m, l = context_parallel_prefill(shard_context(Q, world, rank, zigzag).to(dev),
+                                           shard_context(K, world, rank, zigzag, dim=1).to(dev), 512, sc, zigzag=zigzag)
+        assert last_kernel() == "tcgen05" and device_error_flag() == 0
+        assert_O(O, shard_context(Of, world, rank, zigzag))
+        assert_stats(m, l, shard_context(mf, world, rank, zigzag, dim=-1), shard_context(lf, world, rank, zigzag, dim=-1))
+
+
+def sequence_parallel_case(dev, world, rank):
+    from flashdmla import synthetic
+    from flashdmla.parallel import sequence_parallel_decode, split_sequence_pages
+    lens, H, ps = [5000, 333, 64, 2049, 1], 128, 64
+    Q, pool, table, sl = synthetic.paged_decode_inputs(len(lens), H, lens, 576, ps, seed=12)
+    parts = split_sequence_pages(lens, ps, world, rank)
+    ltable = torch.zeros(len(lens), max(1, max(n for _, n, _ in parts)), dtype=torch.int32)
+    llens = torch.zeros(len(lens), dtype=torch.int32)
+    for b, (first, n, ntok) in enumerate(parts):
+        ltable[b, :n] = table[b, first:first + n]
+        llens[b] = ntok
+    sc = 1 / math.sqrt(192)
+    O, m, l = sequence_parallel_decode(Q.to(dev), pool.to(dev), ltable.to(dev), llens.to(dev), 512, sc, validate=True)
+    Of, mf, lf = orc.decode_paged(Q.float().numpy(), pool.float().numpy(), table.numpy(), sl.numpy(), 512, sc)
+    assert_O(O, Of)
+    assert_stats(m, l, mf, lf)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    try:
+        orc.build()
+        context_parallel_case(dev, world, rank)
+        sequence_parallel_case(dev, world, rank)
+        torch.cuda.synchronize()
+        dist.barrier()
+        print(f"rank {rank} of {world}: exchange checks passed", flush=True)
+    finally:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
