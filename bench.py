@@ -286,6 +286,16 @@ def main():
                                         SCALE, _lib.BF16, stream), "fdmla_decode_paged")
     _lib.set_decode_merge(False)         # the same call as a step, minus the merge launch
     k_ms = time_steps(kernel_only, args.steps, 3, world) / args.steps
+    # control: the same launch with every sequence's page table aliased onto the pages of 8 sequences
+    # (38 MB of distinct cache rows, resident in L2), i.e. the kernel with HBM taken out of the picture
+    alias_table = table[:8].repeat((B + 7) // 8, 1)[:B].contiguous()
+
+    def kernel_l2_resident():
+        _lib.check(L.fdmla_decode_paged(Q.data_ptr(), pool.data_ptr(), alias_table.data_ptr(), seqlens.data_ptr(),
+                                        O.data_ptr(), m.data_ptr(), l.data_ptr(), Op.data_ptr(), mp.data_ptr(),
+                                        lp.data_ptr(), B, H, D_QK, D_V, PAGE, SKV // PAGE, pool.shape[0], splits, 0, -1,
+                                        SCALE, _lib.BF16, stream), "fdmla_decode_paged")
+    k_l2_ms = time_steps(kernel_l2_resident, args.steps, 3, world) / args.steps
     _lib.set_decode_merge(True)
     achieved = DECODE_BYTES / (k_ms * 1e-3) / 1e9
 
@@ -393,6 +403,7 @@ def main():
                          "peak_source": peak_src,
                          "kernel": "fwd_tc2_kernel (2-CTA tcgen05 split-KV decode)", "kernel_ms": k_ms,
                          "algorithmic_bytes": DECODE_BYTES, "tensor_tflops": DECODE_FLOP / (k_ms * 1e-3) / 1e12,
+                         "kernel_ms_l2_resident_control": k_l2_ms,
                          "frac_of_8TBs_spec": achieved / 8000.0},
             "decode_hbm_gbs_per_gpu": DECODE_BYTES / (ms_per_step * 1e-3) / 1e9,
             "prefill": prefill,
