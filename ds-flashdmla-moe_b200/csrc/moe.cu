@@ -1,0 +1,224 @@
+// MoE FFN plumbing around the expert GEMMs: top-k gate, per-expert packing (bucket + exclusive scan),
+// row gather and weighted combine.  These are the pieces the reference lists as csrc/moe/router_topk.cu,
+// pack_dispatch.cu and combine_scatter.cu (README.md:17-20, 48-53; none of them is shipped).  All four are
+// HBM-bound integer / row-copy work on CUDA cores; the packing is deterministic (assignments keep their
+// token order inside an expert), so its outputs are compared bit for bit.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/flashdmla.h"
+
+namespace fdmla {
+namespace moe {
+
+constexpr int PACK_BLOCK = 256;       // assignments per block of the packing pass
+
+// ---- gate: one warp per token --------------------------------------------------------------------
+// p = softmax(logits) over E experts; the k largest win (ties: lower index), listed by descending p;
+// w = p / sum of the selected p.
+__global__ void route_topk_kernel(const float *__restrict__ logits, int *__restrict__ idx, float *__restrict__ w,
+                                  int T, int E, int k) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float *row = logits + (size_t)t * E;
+    float mx = -CUDART_INF_F;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += __expf(row[e] - mx);
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    // k rounds of arg-max over the logits (same order as over p); winners are excluded by index
+    float sel_sum = 0.f;
+    float my_w = 0.f;                 // lane j keeps the j-th winner
+    int my_i = -1;
+    unsigned long long taken_lo = 0;  // this lane's own experts already taken (bit per stride step, E <= 2048)
+    for (int j = 0; j < k; ++j) {
+        float bv = -CUDART_INF_F;
+        int bi = 0x7fffffff;
+        for (int e = lane, s = 0; e < E; e += 32, ++s) {
+            if ((taken_lo >> s) & 1ull) continue;
+            const float v = row[e];
+            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken_lo |= 1ull << (bi >> 5);
+        const float pj = __expf(bv - mx) / sum;
+        sel_sum += pj;
+        if (lane == j) { my_w = pj; my_i = bi; }
+    }
+    if (lane < k) {
+        idx[(size_t)t * k + lane] = my_i;
+        w[(size_t)t * k + lane] = my_w / sel_sum;
+    }
+}
+
+// ---- packing, pass 1: per-block expert counts and each assignment's rank inside its block ----------
+__global__ void __launch_bounds__(PACK_BLOCK) pack_count_kernel(const int *__restrict__ idx, int *__restrict__ blk_counts,
+                                                                int *__restrict__ local_rank, int A, int E) {
+    __shared__ int s_e[PACK_BLOCK];
+    extern __shared__ int s_hist[];
+    const int a = blockIdx.x * PACK_BLOCK + threadIdx.x;
+    int e = -1;
+    if (a < A) {
+        e = idx[a];
+        if (e < 0 || e >= E) e = -1;          // a bad expert id is dropped, never written through
+    }
+    s_e[threadIdx.x] = e;
+    for (int i = threadIdx.x; i < E; i += PACK_BLOCK) s_hist[i] = 0;
+    __syncthreads();
+    if (e >= 0) {
+        int r = 0;
+        for (int i = 0; i < (int)threadIdx.x; ++i) r += (s_e[i] == e);
+        local_rank[a] = r;
+        atomicAdd(&s_hist[e], 1);
+    } else if (a < A) {
+        local_rank[a] = -1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < E; i += PACK_BLOCK) blk_counts[(size_t)blockIdx.x * E + i] = s_hist[i];
+}
+
+// ---- pass 2 (one block): per expert, running sum over the blocks; then the scan over experts --------
+__global__ void pack_scan_kernel(int *__restrict__ blk_counts, int *__restrict__ offsets, int n_blocks, int E, int capacity) {
+    extern __shared__ int s_tot[];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int run = 0;
+        for (int b = 0; b < n_blocks; ++b) {
+            const int c = blk_counts[(size_t)b * E + e];
+            blk_counts[(size_t)b * E + e] = run;           // becomes the block's first rank inside the expert
+            run += c;
+        }
+        s_tot[e] = run < capacity ? run : capacity;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) { offsets[e] = run; run += s_tot[e]; }
+        offsets[E] = run;
+    }
+}
+
+// ---- pass 3: packed position of every assignment and the token of every packed row ------------------
+__global__ void __launch_bounds__(PACK_BLOCK) pack_assign_kernel(const int *__restrict__ idx, const int *__restrict__ blk_first,
+                                                                 const int *__restrict__ local_rank, const int *__restrict__ offsets,
+                                                                 int *__restrict__ pos, int *__restrict__ perm, int A, int E, int k,
+                                                                 int capacity) {
+    const int a = blockIdx.x * PACK_BLOCK + threadIdx.x;
+    if (a >= A) return;
+    const int lr = local_rank[a];
+    int p = -1;
+    if (lr >= 0) {
+        const int e = idx[a];
+        const int r = blk_first[(size_t)blockIdx.x * E + e] + lr;
+        if (r < capacity) {
+            p = offsets[e] + r;
+            perm[p] = a / k;
+        }
+    }
+    pos[a] = p;
+}
+
+// ---- gather: packed[r] = x[perm[r]] (16-byte vectors) -----------------------------------------------
+__global__ void gather_rows_kernel(const uint4 *__restrict__ x, const int *__restrict__ perm, const int *__restrict__ offsets,
+                                   uint4 *__restrict__ packed, int E, int vec_per_row) {
+    const int n_rows = offsets[E];
+    const long long total = (long long)n_rows * vec_per_row;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / vec_per_row), v = (int)(i - (long long)r * vec_per_row);
+        packed[i] = x[(size_t)perm[r] * vec_per_row + v];
+    }
+}
+
+// ---- combine: out[t] = sum_j w'[t,j] y[pos[t,j]] (+ shared[t]); w' = kept weights rescaled to sum 1 ---
+template <typename TX>
+__global__ void combine_kernel(const TX *__restrict__ y, const int *__restrict__ pos, const float *__restrict__ w,
+                               const TX *__restrict__ shared, TX *__restrict__ out, int T, int k, int d) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    float kept_sum = 0.f;
+    for (int j = 0; j < k; ++j) kept_sum += pos[(size_t)t * k + j] >= 0 ? w[(size_t)t * k + j] : 0.f;
+    const float inv = kept_sum > 0.f ? 1.f / kept_sum : 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < k; ++j) {
+            const int p = pos[(size_t)t * k + j];
+            if (p >= 0) acc += w[(size_t)t * k + j] * inv * (float)y[(size_t)p * d + c];
+        }
+        if (shared) acc += (float)shared[(size_t)t * d + c];
+        out[(size_t)t * d + c] = (TX)acc;
+    }
+}
+
+static int launch_ok() { return cudaGetLastError() == cudaSuccess ? FDMLA_OK : FDMLA_ERR_CUDA; }
+
+}  // namespace moe
+}  // namespace fdmla
+
+using namespace fdmla::moe;
+
+extern "C" int fdmla_moe_route_topk(const float *logits, int *idx, float *w, int T, int E, int k, void *stream) {
+    if (!logits || !idx || !w || T < 0 || E <= 0 || k <= 0) return FDMLA_ERR_INVALID;
+    if (k > E || k > 32 || E > 2048) return FDMLA_ERR_UNSUPPORTED;
+    if (T == 0) return FDMLA_OK;
+    const int warps = 4;
+    route_topk_kernel<<<(T + warps - 1) / warps, warps * 32, 0, (cudaStream_t)stream>>>(logits, idx, w, T, E, k);
+    return launch_ok();
+}
+
+extern "C" size_t fdmla_moe_pack_workspace_bytes(int T, int k, int E) {
+    if (T < 0 || k <= 0 || E <= 0) return 0;
+    const long long A = (long long)T * k, nb = (A + PACK_BLOCK - 1) / PACK_BLOCK;
+    return (size_t)((nb > 0 ? nb : 1) * E + (A > 0 ? A : 1)) * sizeof(int);
+}
+
+extern "C" int fdmla_moe_pack(const int *idx, int *pos, int *perm, int *offsets, void *workspace, size_t workspace_bytes,
+                              int T, int k, int E, int capacity, void *stream) {
+    if (!idx || !pos || !perm || !offsets || T < 0 || k <= 0 || E <= 0 || capacity < 0) return FDMLA_ERR_INVALID;
+    if (E > 8192) return FDMLA_ERR_UNSUPPORTED;                  // the per-block histogram lives in shared memory
+    if (!workspace || workspace_bytes < fdmla_moe_pack_workspace_bytes(T, k, E)) return FDMLA_ERR_WORKSPACE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int A = T * k, nb = (A + PACK_BLOCK - 1) / PACK_BLOCK;
+    int *blk = static_cast<int *>(workspace), *lrank = blk + (size_t)(nb > 0 ? nb : 1) * E;
+    if (nb > 0) pack_count_kernel<<<nb, PACK_BLOCK, E * sizeof(int), s>>>(idx, blk, lrank, A, E);
+    pack_scan_kernel<<<1, 256, E * sizeof(int), s>>>(blk, offsets, nb, E, capacity);
+    if (nb > 0) pack_assign_kernel<<<nb, PACK_BLOCK, 0, s>>>(idx, blk, lrank, offsets, pos, perm, A, E, k, capacity);
+    return launch_ok();
+}
+
+extern "C" int fdmla_moe_gather(const void *x, const int *perm, const int *offsets, void *packed, int max_rows, int E, int d,
+                                int dtype, void *stream) {
+    if (!x || !perm || !offsets || !packed || max_rows < 0 || E <= 0 || d <= 0) return FDMLA_ERR_INVALID;
+    const int esz = dtype == FDMLA_BF16 ? 2 : (dtype == FDMLA_F32 ? 4 : 0);
+    if (!esz) return FDMLA_ERR_INVALID;
+    if ((d * esz) % 16 || ((uintptr_t)x | (uintptr_t)packed) % 16) return FDMLA_ERR_UNSUPPORTED;
+    if (max_rows == 0) return FDMLA_OK;
+    const int vec = d * esz / 16;
+    long long blocks = ((long long)max_rows * vec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    gather_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4 *>(x), perm, offsets,
+                                                                      static_cast<uint4 *>(packed), E, vec);
+    return launch_ok();
+}
+
+extern "C" int fdmla_moe_combine(const void *y, const int *pos, const float *w, const void *shared, void *out, int T, int k,
+                                 int d, int dtype, void *stream) {
+    if (!y || !pos || !w || !out || T < 0 || k <= 0 || d <= 0) return FDMLA_ERR_INVALID;
+    if (dtype != FDMLA_BF16 && dtype != FDMLA_F32) return FDMLA_ERR_INVALID;
+    if (T == 0) return FDMLA_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FDMLA_BF16)
+        combine_kernel<__nv_bfloat16><<<T, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(y), pos, w,
+                                                        static_cast<const __nv_bfloat16 *>(shared),
+                                                        static_cast<__nv_bfloat16 *>(out), T, k, d);
+    else
+        combine_kernel<float><<<T, 256, 0, s>>>(static_cast<const float *>(y), pos, w, static_cast<const float *>(shared),
+                                                static_cast<float *>(out), T, k, d);
+    return launch_ok();
+}

@@ -8,12 +8,13 @@ from ._lib import (BACKEND_AUTO, BACKEND_PORTABLE, BACKEND_TENSOR, FlashDMLAErro
                    device_error_flag, last_kernel, set_backend, set_single_cta)
 from .cache import PagedLatentCache
 from .mla import AbsorbedMLA, rope
+from .moe import MoEFFN
 from .ops import (DecodeWorkspace, FlashDMLACacheLatentFn, FlashDMLAOnTheFlyFn, cache_append,
                   cache_gather, flash_dmla_cache_latent, flash_dmla_on_the_fly,
                   flash_dmla_paged_decode, merge_partials, suggest_splits)
 
 __all__ = [
-    "PagedLatentCache", "AbsorbedMLA", "rope", "BACKEND_AUTO", "BACKEND_PORTABLE", "BACKEND_TENSOR", "FlashDMLAError", "LIB_PATH",
+    "PagedLatentCache", "AbsorbedMLA", "MoEFFN", "rope", "BACKEND_AUTO", "BACKEND_PORTABLE", "BACKEND_TENSOR", "FlashDMLAError", "LIB_PATH",
     "device_error_flag", "last_kernel", "set_backend", "set_single_cta", "DecodeWorkspace", "FlashDMLACacheLatentFn",
     "FlashDMLAOnTheFlyFn", "cache_append", "cache_gather", "flash_dmla_cache_latent",
     "flash_dmla_on_the_fly", "flash_dmla_paged_decode", "merge_partials", "suggest_splits",

@@ -41,6 +41,11 @@ SIGNATURES = {
     "fdmla_bwd_cache_latent": (_i, [_vp] * 9 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),
     "fdmla_cache_append": (_i, [_vp] * 4 + [_i] * 7 + [_vp]),
     "fdmla_cache_gather": (_i, [_vp] * 4 + [_i] * 7 + [_vp]),
+    "fdmla_moe_route_topk": (_i, [_vp] * 3 + [_i] * 3 + [_vp]),
+    "fdmla_moe_pack_workspace_bytes": (_sz, [_i] * 3),
+    "fdmla_moe_pack": (_i, [_vp] * 5 + [_sz] + [_i] * 4 + [_vp]),
+    "fdmla_moe_gather": (_i, [_vp] * 4 + [_i] * 4 + [_vp]),
+    "fdmla_moe_combine": (_i, [_vp] * 5 + [_i] * 4 + [_vp]),
 }
 
 _lib = None

@@ -249,6 +249,56 @@ int fdmla_cache_gather(const void *kv_pool, const int32_t *page_table,
                        int d_qk, int page_size, int max_pages, int num_pages,
                        int dtype, void *stream);
 
+/* --------------------------------------------------------------------------
+ * MoE FFN plumbing (the "unfused reference path" of README.md:17-20: Top-K gate
+ * -> per-expert packing (bucket + exclusive scan) -> expert MLP -> combine and
+ * shared-expert add; the reference lists csrc/moe/router_topk.cu,
+ * pack_dispatch.cu, combine_scatter.cu at README.md:48-53 but ships none).
+ * The expert MLP itself is a plain grouped GEMM and is left to the caller's
+ * GEMM library; these four calls are what surrounds it.
+ * -------------------------------------------------------------------------- */
+
+/*
+ * Gate.  logits [T, E] fp32.  p = softmax(logits); the k largest win (ties:
+ * lower expert index), listed by descending p; w = p / sum of the selected p.
+ *   idx [T, k] int32, w [T, k] fp32.  k <= 32, E <= 2048.
+ */
+int fdmla_moe_route_topk(const float *logits, int32_t *idx, float *w, int T,
+                         int E, int k, void *stream);
+
+/*
+ * Packing.  Assignment a = t * k + j goes to expert idx[a]; inside an expert
+ * the assignments keep their order; an expert keeps its first `capacity`
+ * assignments and drops the rest.
+ *   offsets [E + 1]: exclusive scan of the kept counts (offsets[E] = packed rows)
+ *   pos     [T, k]:  packed row of every assignment, -1 if dropped
+ *   perm    [>= min(T k, E capacity)]: token of every packed row
+ * Deterministic (no atomics decide an order).  Workspace: see below.
+ */
+size_t fdmla_moe_pack_workspace_bytes(int T, int k, int E);
+int fdmla_moe_pack(const int32_t *idx, int32_t *pos, int32_t *perm,
+                   int32_t *offsets, void *workspace, size_t workspace_bytes,
+                   int T, int k, int E, int capacity, void *stream);
+
+/*
+ * packed[r, :] = x[perm[r], :] for r < offsets[E] (read on the device);
+ * max_rows only sizes the launch.  Rows of d elements, d * elem size a
+ * multiple of 16 bytes.
+ */
+int fdmla_moe_gather(const void *x, const int32_t *perm, const int32_t *offsets,
+                     void *packed, int max_rows, int E, int d, int dtype,
+                     void *stream);
+
+/*
+ * out[t, :] = sum_j w'[t, j] * y[pos[t, j], :] (+ shared[t, :] if not NULL),
+ * w' = the weights of the kept assignments rescaled to sum to 1 ("gate weight
+ * renormalization under capacity; overflow tokens are masked", README.md:20).
+ * fp32 accumulation; y, shared, out in `dtype`.
+ */
+int fdmla_moe_combine(const void *y, const int32_t *pos, const float *w,
+                      const void *shared, void *out, int T, int k, int d,
+                      int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

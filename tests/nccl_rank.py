@@ -50,6 +50,17 @@ def sequence_parallel_case(dev, world, rank):
     assert_stats(m, l, mf, lf)
 
 
+def expert_parallel_case(dev, world, rank):
+    from flashdmla.moe import MoEFFN
+    layer = MoEFFN(d_model=128, d_ff=256, n_experts=10, top_k=3, capacity_factor=1.0, device=dev, seed=4)    # same weights on every rank
+    x = (torch.randn(150 + 7 * rank, 128, generator=torch.Generator().manual_seed(50 + rank)) * 0.5).to(torch.bfloat16).to(dev)
+    cap = layer.capacity(x.shape[0])
+    got = layer.forward_ep(x, capacity=cap)               # experts sharded 10 -> world ranks, rows over NCCL all-to-all
+    want = layer.forward(x, capacity=cap)                 # all experts here
+    err = float((got.float() - want.float()).norm() / want.float().norm())
+    assert err < 5e-3, err                                # same arithmetic, other GEMM batch shapes
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -59,6 +70,7 @@ def main():
         orc.build()
         context_parallel_case(dev, world, rank)
         sequence_parallel_case(dev, world, rank)
+        expert_parallel_case(dev, world, rank)
         torch.cuda.synchronize()
         dist.barrier()
         print(f"rank {rank} of {world}: exchange checks passed", flush=True)
