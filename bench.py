@@ -374,10 +374,12 @@ def main():
 
     prefill = None
     on_the_fly = None
+    moe_plumbing = None
     if not args.no_prefill:
         prefill = bench_prefill(dev, rank, world, tf_burst)
         if rank == 0:
             on_the_fly = bench_on_the_fly(dev, tf_burst)
+            moe_plumbing = bench_moe_plumbing(dev, hbm_peak)
 
     err = flashdmla.device_error_flag()
     if rank == 0:
@@ -408,6 +410,7 @@ def main():
             "decode_hbm_gbs_per_gpu": DECODE_BYTES / (ms_per_step * 1e-3) / 1e9,
             "prefill": prefill,
             "on_the_fly": on_the_fly,
+            "moe_plumbing": moe_plumbing,
             "device_error_flag": err,
         }
         if cpu is not None:
@@ -469,6 +472,43 @@ def bench_on_the_fly(dev, tf_peak, iters=3):
     return {"workload": f"on-the-fly B={B4} H={H4} S={S4} d_model={dm} d_lat={dl} causal (autograd operator)",
             "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fwd_flop / (f * 1e-3) / 1e12, "bwd_tflops": bwd_flop / (b * 1e-3) / 1e12,
             "bwd_frac_of_measured_bf16_peak": bwd_flop / (b * 1e-3) / 1e12 / tf_peak, "kernel_family": flashdmla.last_kernel()}
+
+
+def bench_moe_plumbing(dev, hbm_peak, iters=5):
+    """The MoE kernels around the expert GEMMs at T=4096 tokens, E=256 experts, top-8, d=7168 bf16 (the shape of a
+    DeepSeek-V3 MoE layer; capacity factor 1.25): gate, packing, row gather, weighted combine.  Algorithmic bytes:
+    gate T E 4; gather 2 x rows x d x 2; combine (rows + 2 T) x d x 2 (packed rows and the shared output in, the
+    result out)."""
+    from flashdmla import moe
+    T, E, k, d = 4096, 256, 8, 7168
+    g = torch.Generator(device=dev).manual_seed(123)
+    logits = torch.randn(T, E, generator=g, device=dev)
+    x = (torch.randn(T, d, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    cap = int(1.25 * T * k / E)
+    idx, w = moe.route_topk(logits, k)
+    pos, perm, offs = moe.pack(idx, E, cap)
+    rows = int(offs[-1])
+    xp = moe.gather(x, perm, offs)
+    sh = torch.zeros_like(x)
+
+    def t_of(fn):
+        ts = []
+        for _ in range(iters + 2):
+            a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b2.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b2))
+        ts = sorted(ts[2:])
+        return ts[len(ts) // 2]
+    gate_ms = t_of(lambda: moe.route_topk(logits, k))
+    pack_ms = t_of(lambda: moe.pack(idx, E, cap))
+    gather_ms = t_of(lambda: moe.gather(x, perm, offs))
+    comb_ms = t_of(lambda: moe.combine(xp, pos, w, sh))
+    gb = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9
+    return {"workload": f"MoE plumbing T={T} E={E} top-{k} d={d} bf16, capacity {cap} ({rows} packed rows)",
+            "gate_ms": gate_ms, "pack_ms": pack_ms, "gather_ms": gather_ms, "combine_ms": comb_ms,
+            "gather_gbs": gb(2.0 * rows * d * 2, gather_ms), "combine_gbs": gb((rows + 2.0 * T) * d * 2, comb_ms),
+            "gather_frac_of_hbm": gb(2.0 * rows * d * 2, gather_ms) / hbm_peak,
+            "combine_frac_of_hbm": gb((rows + 2.0 * T) * d * 2, comb_ms) / hbm_peak}
 
 
 if __name__ == "__main__":
