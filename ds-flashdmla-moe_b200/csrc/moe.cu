@@ -156,6 +156,56 @@ __global__ void combine_kernel(const TX *__restrict__ y, const int *__restrict__
     }
 }
 
+// bf16 rows whose length is a multiple of 8 and whose bases are 16-byte aligned: 16-byte vectors, the k source
+// rows of a token read side by side
+__global__ void combine_bf16x8_kernel(const __nv_bfloat16 *__restrict__ y, const int *__restrict__ pos, const float *__restrict__ w,
+                                      const __nv_bfloat16 *__restrict__ shared, __nv_bfloat16 *__restrict__ out, int T, int k,
+                                      int d) {
+    __shared__ int s_pos[32];
+    __shared__ float s_w[32];
+    const int t = blockIdx.x;
+    if (threadIdx.x < k) {
+        const int p = pos[(size_t)t * k + threadIdx.x];
+        s_pos[threadIdx.x] = p;
+        s_w[threadIdx.x] = p >= 0 ? w[(size_t)t * k + threadIdx.x] : 0.f;
+    }
+    __syncthreads();
+    float kept_sum = 0.f;
+    for (int j = 0; j < k; ++j) kept_sum += s_w[j];
+    const float inv = kept_sum > 0.f ? 1.f / kept_sum : 0.f;
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < k; ++j) {
+            const int p = s_pos[j];
+            if (p < 0) continue;
+            const uint4 v = *reinterpret_cast<const uint4 *>(y + (size_t)p * d + c);
+            const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+            const float wj = s_w[j] * inv;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h[e]);
+                acc[2 * e] += wj * f.x;
+                acc[2 * e + 1] += wj * f.y;
+            }
+        }
+        if (shared) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(shared + (size_t)t * d + c);
+            const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h[e]);
+                acc[2 * e] += f.x;
+                acc[2 * e + 1] += f.y;
+            }
+        }
+        uint4 o;
+        __nv_bfloat162 *ho = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ho[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        *reinterpret_cast<uint4 *>(out + (size_t)t * d + c) = o;
+    }
+}
+
 static int launch_ok() { return cudaGetLastError() == cudaSuccess ? FDMLA_OK : FDMLA_ERR_CUDA; }
 
 }  // namespace moe
@@ -213,7 +263,13 @@ extern "C" int fdmla_moe_combine(const void *y, const int *pos, const float *w, 
     if (dtype != FDMLA_BF16 && dtype != FDMLA_F32) return FDMLA_ERR_INVALID;
     if (T == 0) return FDMLA_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == FDMLA_BF16)
+    const bool vec_ok = dtype == FDMLA_BF16 && d % 8 == 0 && k <= 32 &&
+                        (((uintptr_t)y | (uintptr_t)out | (uintptr_t)shared) % 16) == 0;
+    if (vec_ok)
+        combine_bf16x8_kernel<<<T, d >= 2048 ? 256 : 128, 0, s>>>(static_cast<const __nv_bfloat16 *>(y), pos, w,
+                                                                  static_cast<const __nv_bfloat16 *>(shared),
+                                                                  static_cast<__nv_bfloat16 *>(out), T, k, d);
+    else if (dtype == FDMLA_BF16)
         combine_kernel<__nv_bfloat16><<<T, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(y), pos, w,
                                                         static_cast<const __nv_bfloat16 *>(shared),
                                                         static_cast<__nv_bfloat16 *>(out), T, k, d);
