@@ -477,8 +477,8 @@ def bench_on_the_fly(dev, tf_peak, iters=3):
 def bench_moe_plumbing(dev, hbm_peak, iters=5):
     """The MoE kernels around the expert GEMMs at T=4096 tokens, E=256 experts, top-8, d=7168 bf16 (the shape of a
     DeepSeek-V3 MoE layer; capacity factor 1.25): gate, packing, row gather, weighted combine.  Algorithmic bytes:
-    gate T E 4; gather 2 x rows x d x 2; combine (rows + 2 T) x d x 2 (packed rows and the shared output in, the
-    result out)."""
+    gate T E 4; gather (T + rows) x d x 2 (every token row once from HBM - its other reads hit L2 - and the packed
+    rows out); combine (rows + 2 T) x d x 2 (packed rows and the shared output in, the result out)."""
     from flashdmla import moe
     T, E, k, d = 4096, 256, 8, 7168
     g = torch.Generator(device=dev).manual_seed(123)
@@ -506,8 +506,8 @@ def bench_moe_plumbing(dev, hbm_peak, iters=5):
     gb = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9
     return {"workload": f"MoE plumbing T={T} E={E} top-{k} d={d} bf16, capacity {cap} ({rows} packed rows)",
             "gate_ms": gate_ms, "pack_ms": pack_ms, "gather_ms": gather_ms, "combine_ms": comb_ms,
-            "gather_gbs": gb(2.0 * rows * d * 2, gather_ms), "combine_gbs": gb((rows + 2.0 * T) * d * 2, comb_ms),
-            "gather_frac_of_hbm": gb(2.0 * rows * d * 2, gather_ms) / hbm_peak,
+            "gather_gbs": gb((T + rows) * d * 2.0, gather_ms), "combine_gbs": gb((rows + 2.0 * T) * d * 2, comb_ms),
+            "gather_frac_of_hbm": gb((T + rows) * d * 2.0, gather_ms) / hbm_peak,
             "combine_frac_of_hbm": gb((rows + 2.0 * T) * d * 2, comb_ms) / hbm_peak}
 
 
