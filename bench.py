@@ -220,6 +220,7 @@ def main():
     ap.add_argument("--prefill-shape", default="",
                     help="B,H,S of the prefill measurement (default 4,128,8192); a reduced shape is used for ncu captures")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill measurement (profiling aid)")
+    ap.add_argument("--only-moe", action="store_true", help="run only the MoE plumbing measurement (profiling aid)")
     ap.add_argument("--batch", type=int, default=0,
                     help="decode sequences per GPU (default 128); smaller values give the reduced case used for ncu captures")
     args = ap.parse_args()
@@ -251,6 +252,13 @@ def main():
         pf = bench_prefill(dev, rank, world, tf_burst)
         if rank == 0:
             print(json.dumps({"prefill": pf, "device_error_flag": flashdmla.device_error_flag()}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.only_moe:
+        mp_ = bench_moe_plumbing(dev, hbm_peak)
+        if rank == 0:
+            print(json.dumps({"moe_plumbing": mp_}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
