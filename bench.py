@@ -510,10 +510,12 @@ def bench_moe_plumbing(dev, hbm_peak, iters=5):
     gate_ms = t_of(lambda: moe.route_topk(logits, k))
     pack_ms = t_of(lambda: moe.pack(idx, E, cap))
     gather_ms = t_of(lambda: moe.gather(x, perm, offs))
+    scatter_ms = t_of(lambda: moe.scatter(x, pos, perm.shape[0]))
     comb_ms = t_of(lambda: moe.combine(xp, pos, w, sh))
     gb = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9
     return {"workload": f"MoE plumbing T={T} E={E} top-{k} d={d} bf16, capacity {cap} ({rows} packed rows)",
-            "gate_ms": gate_ms, "pack_ms": pack_ms, "gather_ms": gather_ms, "combine_ms": comb_ms,
+            "gate_ms": gate_ms, "pack_ms": pack_ms, "gather_ms": gather_ms, "scatter_ms": scatter_ms, "combine_ms": comb_ms,
+            "scatter_gbs": gb((T + rows) * d * 2.0, scatter_ms), "scatter_frac_of_hbm": gb((T + rows) * d * 2.0, scatter_ms) / hbm_peak,
             "gather_gbs": gb((T + rows) * d * 2.0, gather_ms), "combine_gbs": gb((rows + 2.0 * T) * d * 2, comb_ms),
             "gather_frac_of_hbm": gb((T + rows) * d * 2.0, gather_ms) / hbm_peak,
             "combine_frac_of_hbm": gb((rows + 2.0 * T) * d * 2, comb_ms) / hbm_peak}

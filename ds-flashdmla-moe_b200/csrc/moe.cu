@@ -85,24 +85,43 @@ __global__ void __launch_bounds__(PACK_BLOCK) pack_count_kernel(const int *__res
     for (int i = threadIdx.x; i < E; i += PACK_BLOCK) blk_counts[(size_t)blockIdx.x * E + i] = s_hist[i];
 }
 
-// ---- pass 2 (one block): per expert, running sum over the blocks; then the scan over experts --------
-__global__ void pack_scan_kernel(int *__restrict__ blk_counts, int *__restrict__ offsets, int n_blocks, int E, int capacity) {
-    extern __shared__ int s_tot[];
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int run = 0;
-        for (int b = 0; b < n_blocks; ++b) {
-            const int c = blk_counts[(size_t)b * E + e];
-            blk_counts[(size_t)b * E + e] = run;           // becomes the block's first rank inside the expert
-            run += c;
+// ---- pass 2a: one warp per expert turns the per-block counts into each block's first rank inside the expert -
+__global__ void pack_scan_blocks_kernel(int *__restrict__ blk_counts, int *__restrict__ totals, int n_blocks, int E, int capacity) {
+    const int lane = threadIdx.x & 31;
+    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (e >= E) return;
+    int run = 0;
+    for (int b0 = 0; b0 < n_blocks; b0 += 32) {
+        const int b = b0 + lane;
+        const int c = b < n_blocks ? blk_counts[(size_t)b * E + e] : 0;
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
         }
-        s_tot[e] = run < capacity ? run : capacity;
+        if (b < n_blocks) blk_counts[(size_t)b * E + e] = run + incl - c;
+        run += __shfl_sync(0xffffffffu, incl, 31);
     }
+    if (lane == 0) totals[e] = run < capacity ? run : capacity;
+}
+
+// ---- pass 2b (one block): exclusive scan of the kept counts over the experts -------------------------------
+__global__ void pack_scan_experts_kernel(const int *__restrict__ totals, int *__restrict__ offsets, int E) {
+    __shared__ int s_part[256];
+    const int per = (E + 255) / 256, lo = threadIdx.x * per, hi = lo + per < E ? lo + per : E;
+    int sum = 0;
+    for (int e = lo; e < hi; ++e) sum += totals[e];
+    s_part[threadIdx.x] = sum;
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
-        for (int e = 0; e < E; ++e) { offsets[e] = run; run += s_tot[e]; }
+        for (int i = 0; i < 256; ++i) { const int c = s_part[i]; s_part[i] = run; run += c; }
         offsets[E] = run;
     }
+    __syncthreads();
+    int run = s_part[threadIdx.x];
+    for (int e = lo; e < hi; ++e) { offsets[e] = run; run += totals[e]; }
 }
 
 // ---- pass 3: packed position of every assignment and the token of every packed row ------------------
@@ -133,6 +152,26 @@ __global__ void gather_rows_kernel(const uint4 *__restrict__ x, const int *__res
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / vec_per_row), v = (int)(i - (long long)r * vec_per_row);
         packed[i] = x[(size_t)perm[r] * vec_per_row + v];
+    }
+}
+
+// ---- scatter: packed[pos[t,j]] = x[t] for every kept assignment: each token row is read once and written to
+// its (up to k) packed rows, so HBM sees T + rows rows instead of the 2 x rows of the gather above when the
+// packed rows stream the token rows out of L2 ---------------------------------------------------------------
+__global__ void scatter_rows_kernel(const uint4 *__restrict__ x, const int *__restrict__ pos, uint4 *__restrict__ packed, int T,
+                                    int k, int vec_per_row) {
+    __shared__ int s_pos[32];
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        __syncthreads();
+        if (threadIdx.x < k) s_pos[threadIdx.x] = pos[(size_t)t * k + threadIdx.x];
+        __syncthreads();
+        for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+            const uint4 val = x[(size_t)t * vec_per_row + v];
+            for (int j = 0; j < k; ++j) {
+                const int p = s_pos[j];
+                if (p >= 0) packed[(size_t)p * vec_per_row + v] = val;
+            }
+        }
     }
 }
 
@@ -225,7 +264,7 @@ extern "C" int fdmla_moe_route_topk(const float *logits, int *idx, float *w, int
 extern "C" size_t fdmla_moe_pack_workspace_bytes(int T, int k, int E) {
     if (T < 0 || k <= 0 || E <= 0) return 0;
     const long long A = (long long)T * k, nb = (A + PACK_BLOCK - 1) / PACK_BLOCK;
-    return (size_t)((nb > 0 ? nb : 1) * E + (A > 0 ? A : 1)) * sizeof(int);
+    return (size_t)((nb > 0 ? nb : 1) * E + (A > 0 ? A : 1) + E) * sizeof(int);
 }
 
 extern "C" int fdmla_moe_pack(const int *idx, int *pos, int *perm, int *offsets, void *workspace, size_t workspace_bytes,
@@ -235,9 +274,10 @@ extern "C" int fdmla_moe_pack(const int *idx, int *pos, int *perm, int *offsets,
     if (!workspace || workspace_bytes < fdmla_moe_pack_workspace_bytes(T, k, E)) return FDMLA_ERR_WORKSPACE;
     cudaStream_t s = (cudaStream_t)stream;
     const int A = T * k, nb = (A + PACK_BLOCK - 1) / PACK_BLOCK;
-    int *blk = static_cast<int *>(workspace), *lrank = blk + (size_t)(nb > 0 ? nb : 1) * E;
+    int *blk = static_cast<int *>(workspace), *lrank = blk + (size_t)(nb > 0 ? nb : 1) * E, *totals = lrank + (A > 0 ? A : 1);
     if (nb > 0) pack_count_kernel<<<nb, PACK_BLOCK, E * sizeof(int), s>>>(idx, blk, lrank, A, E);
-    pack_scan_kernel<<<1, 256, E * sizeof(int), s>>>(blk, offsets, nb, E, capacity);
+    pack_scan_blocks_kernel<<<(E + 7) / 8, 256, 0, s>>>(blk, totals, nb, E, capacity);
+    pack_scan_experts_kernel<<<1, 256, 0, s>>>(totals, offsets, E);
     if (nb > 0) pack_assign_kernel<<<nb, PACK_BLOCK, 0, s>>>(idx, blk, lrank, offsets, pos, perm, A, E, k, capacity);
     return launch_ok();
 }
@@ -254,6 +294,19 @@ extern "C" int fdmla_moe_gather(const void *x, const int *perm, const int *offse
     if (blocks > 148 * 16) blocks = 148 * 16;
     gather_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4 *>(x), perm, offsets,
                                                                       static_cast<uint4 *>(packed), E, vec);
+    return launch_ok();
+}
+
+extern "C" int fdmla_moe_scatter(const void *x, const int *pos, void *packed, int T, int k, int d, int dtype, void *stream) {
+    if (!x || !pos || !packed || T < 0 || k <= 0 || d <= 0) return FDMLA_ERR_INVALID;
+    const int esz = dtype == FDMLA_BF16 ? 2 : (dtype == FDMLA_F32 ? 4 : 0);
+    if (!esz) return FDMLA_ERR_INVALID;
+    if (k > 32 || (d * esz) % 16 || ((uintptr_t)x | (uintptr_t)packed) % 16) return FDMLA_ERR_UNSUPPORTED;
+    if (T == 0) return FDMLA_OK;
+    const int vec = d * esz / 16;
+    const int blocks = T < 148 * 8 ? T : 148 * 8;
+    scatter_rows_kernel<<<blocks, vec >= 256 ? 256 : 128, 0, (cudaStream_t)stream>>>(static_cast<const uint4 *>(x), pos,
+                                                                                    static_cast<uint4 *>(packed), T, k, vec);
     return launch_ok();
 }
 

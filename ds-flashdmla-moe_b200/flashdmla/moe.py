@@ -3,7 +3,7 @@ the reference describes at README.md:17-20, and its single-node expert paralleli
 
     idx, w          = route_topk(logits, k)                  # gate
     pos, perm, offs = pack(idx, E, capacity)                 # bucket + exclusive scan, deterministic
-    xp              = gather(x, perm, offs)                  # rows in expert order
+    xp              = scatter(x, pos, rows)                  # rows in expert order (or gather(x, perm, offs))
     yp              = expert MLP on xp[offs[e]:offs[e+1]]    # plain GEMMs (torch.matmul = vendor library)
     out             = combine(yp, pos, w, shared)            # renormalised weights, shared expert added
 
@@ -71,6 +71,17 @@ def gather(x: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor) -> torch.
     return packed
 
 
+def scatter(x: torch.Tensor, pos: torch.Tensor, n_rows: int) -> torch.Tensor:
+    """x [T,d], pos [T,k] -> packed [n_rows, d] (the same rows as `gather`, each token row read once)."""
+    _need_cuda(x, pos)
+    x = x.contiguous()
+    packed = torch.empty(n_rows, x.shape[1], dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_lib.lib().fdmla_moe_scatter(_ptr(x), _ptr(pos.contiguous()), _ptr(packed), pos.shape[0], pos.shape[1],
+                                           x.shape[1], _dtype_code(x), _stream(x)), "fdmla_moe_scatter")
+    return packed
+
+
 def combine(y: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, shared: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y [rows,d], pos [T,k], w [T,k] -> out [T,d] (+ shared [T,d])."""
     _need_cuda(y, pos, w, shared)
@@ -131,7 +142,7 @@ class MoEFFN:
         """x [T,d] -> [T,d], all experts on this GPU."""
         cap = self.capacity(x.shape[0]) if capacity is None else int(capacity)
         idx, w, pos, perm, offsets = self._route(x, cap)
-        xp = gather(x, perm, offsets)
+        xp = scatter(x, pos, perm.shape[0])
         yp = torch.zeros_like(xp)
         offs = offsets.tolist()                    # the expert GEMMs are launched per expert from the host
         for e in range(self.E):

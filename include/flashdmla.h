@@ -290,6 +290,14 @@ int fdmla_moe_gather(const void *x, const int32_t *perm, const int32_t *offsets,
                      void *stream);
 
 /*
+ * The same packed rows written from the token side: packed[pos[t, j], :] =
+ * x[t, :] for every kept assignment.  Every token row is read once (the
+ * gather reads it once per assignment).  k <= 32.
+ */
+int fdmla_moe_scatter(const void *x, const int32_t *pos, void *packed, int T,
+                      int k, int d, int dtype, void *stream);
+
+/*
  * out[t, :] = sum_j w'[t, j] * y[pos[t, j], :] (+ shared[t, :] if not NULL),
  * w' = the weights of the kept assignments rescaled to sum to 1 ("gate weight
  * renormalization under capacity; overflow tokens are masked", README.md:20).

@@ -45,7 +45,7 @@ def test_argument_validation_needs_no_gpu():
     L = _lib.lib()
     assert L.fdmla_moe_route_topk(None, None, None, 4, 8, 2, None) == -1
     assert L.fdmla_moe_route_topk(1, 1, 1, 4, 8, 9, None) == -2          # k > E
-    assert L.fdmla_moe_pack_workspace_bytes(1000, 8, 256) == ((1000 * 8 + 255) // 256 * 256 + 8000) * 4
+    assert L.fdmla_moe_pack_workspace_bytes(1000, 8, 256) == ((1000 * 8 + 255) // 256 * 256 + 8000 + 256) * 4
     assert L.fdmla_moe_pack(1, 1, 1, 1, None, 0, 4, 2, 8, 3, None) == -4
     assert L.fdmla_moe_gather(16, 16, 16, 16, 4, 8, 7, 1, None) == -2    # 14-byte rows
     assert L.fdmla_moe_combine(1, 1, 1, None, 1, 4, 2, 8, 5, None) == -1
@@ -148,6 +148,8 @@ def test_gate_and_packing_match_the_oracle_bit_for_bit(cuda, T, k, E, cap, skew)
     x = torch.randn(T, 64, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
     xp = moe.gather(x.to(cuda), perm, offs).cpu()
     assert torch.equal(xp[: offs_r[-1]], x[torch.from_numpy(perm_r).long()])
+    xs = moe.scatter(x.to(cuda), pos, perm.shape[0]).cpu()          # the same rows, written from the token side
+    assert torch.equal(xs[: offs_r[-1]], xp[: offs_r[-1]])
 
 
 @pytest.mark.gpu
