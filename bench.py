@@ -513,7 +513,14 @@ def bench_moe_plumbing(dev, hbm_peak, iters=5):
     scatter_ms = t_of(lambda: moe.scatter(x, pos, perm.shape[0]))
     comb_ms = t_of(lambda: moe.combine(xp, pos, w, sh))
     gb = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9
-    return {"workload": f"MoE plumbing T={T} E={E} top-{k} d={d} bf16, capacity {cap} ({rows} packed rows)",
+    # a whole layer (padded packing, expert MLPs as three batched library GEMMs, shared expert), smaller model
+    layer = moe.MoEFFN(d_model=4096, d_ff=1024, n_experts=64, top_k=8, capacity_factor=1.25, device=dev, seed=1)
+    xl = (torch.randn(T, 4096, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    layer_ms = t_of(lambda: layer.forward_batched(xl))
+    del layer
+    return {"layer_batched_ms": layer_ms,
+            "layer_workload": "MoEFFN.forward_batched T=4096 d=4096 d_ff=1024 E=64 top-8 + shared expert, bf16",
+            "workload": f"MoE plumbing T={T} E={E} top-{k} d={d} bf16, capacity {cap} ({rows} packed rows)",
             "gate_ms": gate_ms, "pack_ms": pack_ms, "gather_ms": gather_ms, "scatter_ms": scatter_ms, "combine_ms": comb_ms,
             "scatter_gbs": gb((T + rows) * d * 2.0, scatter_ms), "scatter_frac_of_hbm": gb((T + rows) * d * 2.0, scatter_ms) / hbm_peak,
             "gather_gbs": gb((T + rows) * d * 2.0, gather_ms), "combine_gbs": gb((rows + 2.0 * T) * d * 2, comb_ms),

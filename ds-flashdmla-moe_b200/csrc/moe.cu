@@ -107,8 +107,13 @@ __global__ void pack_scan_blocks_kernel(int *__restrict__ blk_counts, int *__res
 }
 
 // ---- pass 2b (one block): exclusive scan of the kept counts over the experts -------------------------------
-__global__ void pack_scan_experts_kernel(const int *__restrict__ totals, int *__restrict__ offsets, int E) {
+// (padded: every expert owns `capacity` rows, offsets[e] = e * capacity, so that the packed rows are an [E, capacity, d] batch)
+__global__ void pack_scan_experts_kernel(const int *__restrict__ totals, int *__restrict__ offsets, int E, int capacity, int padded) {
     __shared__ int s_part[256];
+    if (padded) {
+        for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = e * capacity;
+        return;
+    }
     const int per = (E + 255) / 256, lo = threadIdx.x * per, hi = lo + per < E ? lo + per : E;
     int sum = 0;
     for (int e = lo; e < hi; ++e) sum += totals[e];
@@ -268,8 +273,9 @@ extern "C" size_t fdmla_moe_pack_workspace_bytes(int T, int k, int E) {
 }
 
 extern "C" int fdmla_moe_pack(const int *idx, int *pos, int *perm, int *offsets, void *workspace, size_t workspace_bytes,
-                              int T, int k, int E, int capacity, void *stream) {
+                              int T, int k, int E, int capacity, int padded, void *stream) {
     if (!idx || !pos || !perm || !offsets || T < 0 || k <= 0 || E <= 0 || capacity < 0) return FDMLA_ERR_INVALID;
+    if (padded && (long long)E * capacity > 0x7fffffffLL) return FDMLA_ERR_UNSUPPORTED;
     if (E > 8192) return FDMLA_ERR_UNSUPPORTED;                  // the per-block histogram lives in shared memory
     if (!workspace || workspace_bytes < fdmla_moe_pack_workspace_bytes(T, k, E)) return FDMLA_ERR_WORKSPACE;
     cudaStream_t s = (cudaStream_t)stream;
@@ -277,7 +283,7 @@ extern "C" int fdmla_moe_pack(const int *idx, int *pos, int *perm, int *offsets,
     int *blk = static_cast<int *>(workspace), *lrank = blk + (size_t)(nb > 0 ? nb : 1) * E, *totals = lrank + (A > 0 ? A : 1);
     if (nb > 0) pack_count_kernel<<<nb, PACK_BLOCK, E * sizeof(int), s>>>(idx, blk, lrank, A, E);
     pack_scan_blocks_kernel<<<(E + 7) / 8, 256, 0, s>>>(blk, totals, nb, E, capacity);
-    pack_scan_experts_kernel<<<1, 256, 0, s>>>(totals, offsets, E);
+    pack_scan_experts_kernel<<<1, 256, 0, s>>>(totals, offsets, E, capacity, padded);
     if (nb > 0) pack_assign_kernel<<<nb, PACK_BLOCK, 0, s>>>(idx, blk, lrank, offsets, pos, perm, A, E, k, capacity);
     return launch_ok();
 }

@@ -43,7 +43,7 @@ SIGNATURES = {
     "fdmla_cache_gather": (_i, [_vp] * 4 + [_i] * 7 + [_vp]),
     "fdmla_moe_route_topk": (_i, [_vp] * 3 + [_i] * 3 + [_vp]),
     "fdmla_moe_pack_workspace_bytes": (_sz, [_i] * 3),
-    "fdmla_moe_pack": (_i, [_vp] * 5 + [_sz] + [_i] * 4 + [_vp]),
+    "fdmla_moe_pack": (_i, [_vp] * 5 + [_sz] + [_i] * 5 + [_vp]),
     "fdmla_moe_gather": (_i, [_vp] * 4 + [_i] * 4 + [_vp]),
     "fdmla_moe_scatter": (_i, [_vp] * 3 + [_i] * 4 + [_vp]),
     "fdmla_moe_combine": (_i, [_vp] * 5 + [_i] * 4 + [_vp]),

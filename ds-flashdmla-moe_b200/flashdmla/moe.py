@@ -40,8 +40,9 @@ def route_topk(logits: torch.Tensor, k: int):
     return idx, w
 
 
-def pack(idx: torch.Tensor, n_experts: int, capacity: int):
-    """idx [T,k] int32 -> pos [T,k], perm [min(T k, E capacity)], offsets [E+1] (all int32, on the device)."""
+def pack(idx: torch.Tensor, n_experts: int, capacity: int, padded: bool = False):
+    """idx [T,k] int32 -> pos [T,k], perm [min(T k, E capacity)], offsets [E+1] (all int32, on the device).
+    padded: every expert owns `capacity` packed rows (offsets[e] = e capacity; perm has E capacity entries)."""
     _need_cuda(idx)
     if idx.dtype != torch.int32 or idx.dim() != 2:
         raise FlashDMLAError("idx must be [T,k] int32")
@@ -49,14 +50,14 @@ def pack(idx: torch.Tensor, n_experts: int, capacity: int):
     T, k = idx.shape
     dev = idx.device
     pos = torch.empty(T, k, dtype=torch.int32, device=dev)
-    perm = torch.empty(max(1, min(T * k, n_experts * capacity)), dtype=torch.int32, device=dev)
+    perm = torch.empty(max(1, n_experts * capacity if padded else min(T * k, n_experts * capacity)), dtype=torch.int32, device=dev)
     offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         L = _lib.lib()
         nbytes = L.fdmla_moe_pack_workspace_bytes(T, k, n_experts)
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
         check(L.fdmla_moe_pack(_ptr(idx), _ptr(pos), _ptr(perm), _ptr(offsets), _ptr(ws), ws.numel(), T, k,
-                               int(n_experts), int(capacity), _stream(idx)), "fdmla_moe_pack")
+                               int(n_experts), int(capacity), int(bool(padded)), _stream(idx)), "fdmla_moe_pack")
     return pos, perm, offsets
 
 
@@ -151,6 +152,22 @@ class MoEFFN:
                 yp[lo:hi] = swiglu_mlp(xp[lo:hi], self.W1[e], self.W3[e], self.W2[e])
         sh = swiglu_mlp(x, *self.shared) if self.shared is not None else None
         return combine(yp, pos, w, sh)
+
+    def forward_batched(self, x: torch.Tensor, capacity: Optional[int] = None) -> torch.Tensor:
+        """The same layer with padded packing: the packed rows are an [E, capacity, d] batch, the expert MLPs
+        three batched GEMMs, and nothing is read back to the host (so the step can be captured in a CUDA graph).
+        Rows past an expert's count are multiplied too - that is the price - and never combined."""
+        cap = self.capacity(x.shape[0]) if capacity is None else int(capacity)
+        idx, w = route_topk(x.float() @ self.Wg, self.k)
+        pos, perm, offsets = pack(idx, self.E, cap, padded=True)
+        xp = torch.zeros(self.E * cap, x.shape[1], dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            check(_lib.lib().fdmla_moe_scatter(_ptr(x.contiguous()), _ptr(pos), _ptr(xp), x.shape[0], self.k, x.shape[1],
+                                               _dtype_code(x), _stream(x)), "fdmla_moe_scatter")
+        xb = xp.view(self.E, cap, x.shape[1])
+        yb = torch.bmm(torch.nn.functional.silu(torch.bmm(xb, self.W1)) * torch.bmm(xb, self.W3), self.W2)
+        sh = swiglu_mlp(x, *self.shared) if self.shared is not None else None
+        return combine(yb.view(self.E * cap, x.shape[1]), pos, w, sh)
 
     def forward_ep(self, x: torch.Tensor, group: Optional[dist.ProcessGroup] = None, capacity: Optional[int] = None,
                    route_fn: Optional[Callable] = None, gather_fn: Optional[Callable] = None,

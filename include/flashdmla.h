@@ -274,11 +274,15 @@ int fdmla_moe_route_topk(const float *logits, int32_t *idx, float *w, int T,
  *   pos     [T, k]:  packed row of every assignment, -1 if dropped
  *   perm    [>= min(T k, E capacity)]: token of every packed row
  * Deterministic (no atomics decide an order).  Workspace: see below.
+ * padded != 0: every expert owns `capacity` rows (offsets[e] = e * capacity),
+ * so that the packed rows form an [E, capacity, d] batch for a batched GEMM;
+ * rows past an expert's count hold nothing and no assignment points at them
+ * (perm then has E * capacity entries, those of unused rows are unwritten).
  */
 size_t fdmla_moe_pack_workspace_bytes(int T, int k, int E);
 int fdmla_moe_pack(const int32_t *idx, int32_t *pos, int32_t *perm,
                    int32_t *offsets, void *workspace, size_t workspace_bytes,
-                   int T, int k, int E, int capacity, void *stream);
+                   int T, int k, int E, int capacity, int padded, void *stream);
 
 /*
  * packed[r, :] = x[perm[r], :] for r < offsets[E] (read on the device);

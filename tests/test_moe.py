@@ -46,7 +46,7 @@ def test_argument_validation_needs_no_gpu():
     assert L.fdmla_moe_route_topk(None, None, None, 4, 8, 2, None) == -1
     assert L.fdmla_moe_route_topk(1, 1, 1, 4, 8, 9, None) == -2          # k > E
     assert L.fdmla_moe_pack_workspace_bytes(1000, 8, 256) == ((1000 * 8 + 255) // 256 * 256 + 8000 + 256) * 4
-    assert L.fdmla_moe_pack(1, 1, 1, 1, None, 0, 4, 2, 8, 3, None) == -4
+    assert L.fdmla_moe_pack(1, 1, 1, 1, None, 0, 4, 2, 8, 3, 0, None) == -4
     assert L.fdmla_moe_gather(16, 16, 16, 16, 4, 8, 7, 1, None) == -2    # 14-byte rows
     assert L.fdmla_moe_combine(1, 1, 1, None, 1, 4, 2, 8, 5, None) == -1
     from flashdmla.moe import expert_ranges, route_topk
@@ -198,3 +198,14 @@ def test_whole_layer_matches_the_oracle(cuda):
                 want[t] += wn[t, j] * morc.swiglu_mlp(xf[t:t + 1], f(layer.W1[e]), f(layer.W3[e]), f(layer.W2[e]))[0]
     err = np.linalg.norm(out - want) / np.linalg.norm(want)
     assert err <= 1.5e-2, err                                # bf16 GEMMs and a bf16 result against fp32
+    # padded packing + batched GEMMs: the same routing, the same kept assignments
+    out_b = layer.forward_batched(x.to(cuda)).float().cpu().numpy()
+    err_b = np.linalg.norm(out_b - want) / np.linalg.norm(want)
+    assert err_b <= 1.5e-2, err_b
+    from flashdmla import moe
+    idx_g, _ = moe.route_topk(x.to(cuda).float() @ layer.Wg, layer.k)
+    pos_p, perm_p, offs_p = moe.pack(idx_g, layer.E, cap, padded=True)
+    assert offs_p.tolist() == [e * cap for e in range(layer.E + 1)]
+    pp = pos_p.cpu().numpy()
+    assert np.array_equal(pp >= 0, pos >= 0)
+    assert np.array_equal(np.where(pp >= 0, pp - idx * cap, -1), np.where(pos >= 0, pos - offs[idx], -1))   # same rank inside the expert
