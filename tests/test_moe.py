@@ -209,3 +209,26 @@ def test_whole_layer_matches_the_oracle(cuda):
     pp = pos_p.cpu().numpy()
     assert np.array_equal(pp >= 0, pos >= 0)
     assert np.array_equal(np.where(pp >= 0, pp - idx * cap, -1), np.where(pos >= 0, pos - offs[idx], -1))   # same rank inside the expert
+
+
+@pytest.mark.gpu
+def test_batched_layer_replays_as_a_cuda_graph(cuda):
+    """forward_batched reads nothing back to the host, so a whole MoE layer captures as one CUDA graph."""
+    from flashdmla.moe import MoEFFN
+    layer = MoEFFN(d_model=128, d_ff=128, n_experts=8, top_k=2, capacity_factor=1.5, device=cuda, seed=6)
+    g = torch.Generator().manual_seed(10)
+    x_in = torch.zeros(96, 128, dtype=torch.bfloat16, device=cuda)
+    side = torch.cuda.Stream(device=cuda)
+    with torch.cuda.stream(side):
+        layer.forward_batched(x_in)                      # warm-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = layer.forward_batched(x_in)
+    for _ in range(2):
+        x = (torch.randn(96, 128, generator=g) * 0.5).to(torch.bfloat16).to(cuda)
+        x_in.copy_(x)
+        graph.replay()
+        torch.cuda.synchronize()
+        want = layer.forward_batched(x)
+        assert torch.equal(out, want)
