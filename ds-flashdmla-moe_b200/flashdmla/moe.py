@@ -169,6 +169,44 @@ class MoEFFN:
         sh = swiglu_mlp(x, *self.shared) if self.shared is not None else None
         return combine(yb.view(self.E * cap, x.shape[1]), pos, w, sh)
 
+    def forward_ep_batched(self, x: torch.Tensor, capacity: int, group: Optional[dist.ProcessGroup] = None,
+                           route_fn: Optional[Callable] = None, scatter_fn: Optional[Callable] = None,
+                           combine_fn: Optional[Callable] = None) -> torch.Tensor:
+        """Expert parallelism without a host read-back: padded packing makes every rank's share of the packed
+        rows the same size ([experts per rank, capacity, d]), so the two all-to-alls have equal, known splits and
+        the experts of a rank run as three batched GEMMs over [experts per rank, world x capacity, d].  Needs
+        n_experts divisible by the number of ranks and THE SAME `capacity` ON EVERY RANK (it fixes the message
+        sizes; ranks may hold different numbers of tokens).  Unused rows travel and are multiplied too."""
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.E % world:
+            raise FlashDMLAError("forward_ep_batched needs n_experts divisible by the number of ranks")
+        n_loc = self.E // world
+        cap = int(capacity)
+        if route_fn is None:
+            idx, w = route_topk(x.float() @ self.Wg, self.k)
+            pos, perm, offsets = pack(idx, self.E, cap, padded=True)
+        else:
+            idx, w, pos = route_fn(x, cap)
+        if scatter_fn is None:
+            xp = torch.zeros(self.E * cap, x.shape[1], dtype=x.dtype, device=x.device)
+            with torch.cuda.device(x.device):
+                check(_lib.lib().fdmla_moe_scatter(_ptr(x.contiguous()), _ptr(pos), _ptr(xp), x.shape[0], self.k, x.shape[1],
+                                                   _dtype_code(x), _stream(x)), "fdmla_moe_scatter")
+        else:
+            xp = scatter_fn(x, pos, self.E * cap)
+        x_in = torch.empty_like(xp)                                   # [world (source), n_loc, cap, d]
+        dist.all_to_all_single(x_in, xp, group=group)
+        d = x.shape[1]
+        xb = x_in.view(world, n_loc, cap, d).permute(1, 0, 2, 3).reshape(n_loc, world * cap, d)
+        lo = rank * n_loc
+        W1, W3, W2 = self.W1[lo:lo + n_loc], self.W3[lo:lo + n_loc], self.W2[lo:lo + n_loc]
+        yb = torch.bmm(torch.nn.functional.silu(torch.bmm(xb, W1)) * torch.bmm(xb, W3), W2)
+        y_out = yb.view(n_loc, world, cap, d).permute(1, 0, 2, 3).contiguous().view(self.E * cap, d)
+        y_back = torch.empty_like(y_out)
+        dist.all_to_all_single(y_back, y_out, group=group)
+        sh = swiglu_mlp(x, *self.shared) if self.shared is not None else None
+        return (combine_fn or combine)(y_back, pos, w, sh)
+
     def forward_ep(self, x: torch.Tensor, group: Optional[dist.ProcessGroup] = None, capacity: Optional[int] = None,
                    route_fn: Optional[Callable] = None, gather_fn: Optional[Callable] = None,
                    combine_fn: Optional[Callable] = None) -> torch.Tensor:

@@ -2,6 +2,7 @@
 torch.distributed.run, one process per GPU).  Every rank builds the same seeded global problem,
 keeps its shard, runs the product path with the real collective and compares its result with
 the CPU oracle on the unsharded problem.  Exits non-zero on any mismatch."""
+import datetime
 import math
 import os
 import sys
@@ -52,20 +53,24 @@ def sequence_parallel_case(dev, world, rank):
 
 def expert_parallel_case(dev, world, rank):
     from flashdmla.moe import MoEFFN
-    layer = MoEFFN(d_model=128, d_ff=256, n_experts=10, top_k=3, capacity_factor=1.0, device=dev, seed=4)    # same weights on every rank
+    layer = MoEFFN(d_model=128, d_ff=256, n_experts=12, top_k=3, capacity_factor=1.0, device=dev, seed=4)    # same weights on every rank
     x = (torch.randn(150 + 7 * rank, 128, generator=torch.Generator().manual_seed(50 + rank)) * 0.5).to(torch.bfloat16).to(dev)
-    cap = layer.capacity(x.shape[0])
-    got = layer.forward_ep(x, capacity=cap)               # experts sharded 10 -> world ranks, rows over NCCL all-to-all
+    cap = layer.capacity(160)                             # one capacity for all ranks (they hold 150, 157, ... tokens)
+    got = layer.forward_ep(x, capacity=cap)               # experts sharded 12 -> world ranks, rows over NCCL all-to-all
     want = layer.forward(x, capacity=cap)                 # all experts here
     err = float((got.float() - want.float()).norm() / want.float().norm())
     assert err < 5e-3, err                                # same arithmetic, other GEMM batch shapes
+    if layer.E % world == 0:
+        got2 = layer.forward_ep_batched(x, cap)  # padded rows, equal splits, no host read-back
+        err2 = float((got2.float() - want.float()).norm() / want.float().norm())
+        assert err2 < 5e-3, err2
 
 
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))   # a mismatch ends in an error, not a hang
     try:
         orc.build()
         context_parallel_case(dev, world, rank)

@@ -104,7 +104,26 @@ def _ep_worker(rank, world, port, q):
             return out + sh
         out = layer.forward_ep(torch.from_numpy(x), capacity=cap, route_fn=route_fn, gather_fn=gather_fn, combine_fn=combine_fn)
         want, _ = morc.moe_ffn(x, W["Wg"], W["W1"], W["W3"], W["W2"], K, cap, W["shared"])
-        q.put((rank, "ok", float(np.abs(out.numpy() - want).max())))
+        err = float(np.abs(out.numpy() - want).max())
+
+        # the padded, read-back-free exchange: same kept assignments, rows at expert * capacity + rank
+        def route_padded(xt, capacity):
+            idx, w = morc.route_topk(xt.numpy() @ W["Wg"], K)
+            pos, perm, offs = morc.pack(idx, E, capacity)
+            ppos = np.where(pos >= 0, pos - offs[idx] + idx * capacity, -1).astype(np.int32)
+            return torch.from_numpy(idx), torch.from_numpy(w), torch.from_numpy(ppos)
+
+        def scatter_fn(xt, pos, n_rows):
+            xp = torch.zeros(n_rows, xt.shape[1])
+            for t in range(pos.shape[0]):
+                for j in range(pos.shape[1]):
+                    if pos[t, j] >= 0:
+                        xp[pos[t, j]] = xt[t]
+            return xp
+        out2 = layer.forward_ep_batched(torch.from_numpy(x), cap, route_fn=route_padded, scatter_fn=scatter_fn,
+                                        combine_fn=combine_fn)
+        err = max(err, float(np.abs(out2.numpy() - want).max()))
+        q.put((rank, "ok", err))
     except Exception as e:
         q.put((rank, "error", type(e).__name__ + ": " + str(e)[:300]))
     finally:
