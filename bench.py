@@ -9,7 +9,10 @@ B=128 sequences per GPU, H=128, Skv=4096, 576-wide latent rows (V = first 512),
 page size 64, page table = seeded random permutation of the pool, scale
 1/sqrt(192), entries 0.1*N(0,1).  Sequences are sharded over GPUs with no
 collective (weak scaling: every GPU decodes its own 128 sequences).  The line
-also carries the causal-prefill figure (B=4, H=128, S=8192, heads sharded).
+also carries the causal-prefill figure (B=4, H=128, S=8192, heads sharded) and, on
+more than one GPU, the long-context decode whose KV sequence is split over the
+GPUs (B=8, Skv in [16384, 131072]: the one exchange step of the path, an NCCL
+all-gather of the partial results) and a context-parallel prefill.
 
 `--impl reference` times the CPU oracle (the restatement of the reference's
 naive attention; the reference ships no CPU code and no DMLA kernels) on the
@@ -153,6 +156,43 @@ def time_steps(fn, steps, warmup, world):
     return ms
 
 
+def median_launch_ms(fn, launches=200, warmup=10):
+    """Median device time of one call of `fn` on the current stream: an event between every two of
+    `launches` back-to-back calls (the stream never runs dry: a call is enqueued in far less time than it
+    runs), independent of --steps."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(launches + 1)]
+    ev[0].record()
+    for i in range(launches):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    return statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(launches))
+
+
+def pin_to_cores(local: int, world: int):
+    """Give every rank its own share of the host cores before it allocates pinned memory (first touch
+    then lands near the cores that drive the copies).  Returns the cores, or None if the platform has no
+    affinity call."""
+    try:
+        avail = sorted(os.sched_getaffinity(0))
+        per = max(1, len(avail) // max(world, 1))
+        mine = avail[local * per:(local + 1) * per] or avail
+        os.sched_setaffinity(0, mine)
+        return mine
+    except (AttributeError, OSError):
+        return None
+
+
+def decode_config(world):
+    """The workload both arms are measured on (the GPU arm's tuning choices are reported under `plan`)."""
+    return {"workload": "paged_mla_decode", "B_per_gpu": B, "H": H, "Skv": SKV, "d_qk": D_QK, "d_v": D_V,
+            "page_size": PAGE, "parallelism": f"batch-sharded x{world}, no collective",
+            "l2": f"working set {B * SKV * D_QK * 2 / 1e6:.0f} MB per step exceeds the 126 MB L2 (no flush needed)"}
+
+
 def cpu_baseline_sample(target_s=12.0):
     """Oracle (port of the reference's naive attention) on the host cores, bounded sample."""
     from flashdmla import synthetic
@@ -202,7 +242,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "paged_mla_decode_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "paged_mla_decode B=128 H=128 Skv=4096 d=576/512 page=64 (bounded sample per step)"},
+        "config": decode_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -240,6 +280,7 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    cores = pin_to_cores(local, world) if world > 1 else sorted(os.sched_getaffinity(0))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -249,7 +290,7 @@ def main():
 
     hbm_peak, tf_burst, tf_sust, peak_src = peaks()
     if args.only_prefill:
-        pf = bench_prefill(dev, rank, world, tf_burst)
+        pf = bench_prefill(dev, rank, world, tf_burst, tf_sust)
         if rank == 0:
             print(json.dumps({"prefill": pf, "device_error_flag": flashdmla.device_error_flag()}), flush=True)
         if world > 1:
@@ -265,7 +306,22 @@ def main():
     Q, pool, table, seqlens = make_decode_inputs(dev, seed=1000 + rank)
     splits = args.splits or flashdmla.suggest_splits(B, H, SKV, D_QK, D_V, PAGE)
     ws = flashdmla.DecodeWorkspace()
-    launches_per_step = 2 if splits > 1 else 1
+    L = _lib.lib()
+    import ctypes
+    qmin, units = ctypes.c_int(0), ctypes.c_int(0)
+    mode = L.fdmla_decode_plan(B, H, D_QK, D_V, PAGE, SKV // PAGE, splits, _lib.BF16, ctypes.byref(qmin), ctypes.byref(units))
+    mode_name = {0: "equal splits" if splits > 1 else "one work item per sequence", 1: "balanced runs + merge kernel",
+                 2: "balanced runs, merged in the attention kernel"}.get(mode, "?")
+    # kernels of this library per step: the attention kernel, plus the merge kernel where one runs (the balanced
+    # in-kernel schedule also enqueues a 1 KB memset node, which is not a kernel of ours)
+    launches_per_step = 1 if (splits == 1 or mode == 2) else 2
+    n_units = units.value or 74
+    tiles_total = B * (SKV // 256)
+    if mode in (1, 2):
+        tiles_per_pair_max = max(-(-tiles_total // n_units), qmin.value)
+    else:
+        tiles_per_pair_max = -(-(B * splits) // n_units) * -(-(SKV // 256) // splits)
+    pairs_idle_frac = 1.0 - tiles_total / float(n_units * tiles_per_pair_max)
 
     def step():
         return flashdmla.flash_dmla_paged_decode(Q, pool, table, seqlens, D_V, SCALE, num_splits=splits,
@@ -282,109 +338,39 @@ def main():
     ms_per_step = total_ms / args.steps
     value = world * B / (ms_per_step * 1e-3)
 
-    # dominant kernel alone (split-KV attention without the merge), CUDA events on its stream
-    Op, mp, lp = ws.get(splits, B, H, D_V, dev)
-    L = _lib.lib()
+    # the dominant kernel alone, through the C ABI, CUDA events on its stream, median of 200 launches: the whole call
+    # where the attention kernel also merges (or nothing is to merge), the partial-only call (O = NULL) where a merge
+    # kernel would follow
+    Op, mp, lp = ws.get(splits, B, H, D_V, dev) if splits > 1 else (None, None, None)
     stream = torch.cuda.current_stream().cuda_stream
+    only_partials = launches_per_step == 2
+    ptr = lambda t: None if t is None else t.data_ptr()
 
-    def kernel_only():
-        _lib.check(L.fdmla_decode_paged(Q.data_ptr(), pool.data_ptr(), table.data_ptr(), seqlens.data_ptr(),
-                                        O.data_ptr(), m.data_ptr(), l.data_ptr(), Op.data_ptr(), mp.data_ptr(),
-                                        lp.data_ptr(), B, H, D_QK, D_V, PAGE, SKV // PAGE, pool.shape[0], splits, 0, -1,
-                                        SCALE, _lib.BF16, stream), "fdmla_decode_paged")
-    _lib.set_decode_merge(False)         # the same call as a step, minus the merge launch
-    k_ms = time_steps(kernel_only, args.steps, 3, world) / args.steps
+    def kernel_call(tab):
+        def f():
+            _lib.check(L.fdmla_decode_paged(Q.data_ptr(), pool.data_ptr(), tab.data_ptr(), seqlens.data_ptr(),
+                                            None if only_partials else O.data_ptr(), m.data_ptr(), l.data_ptr(), ptr(Op),
+                                            ptr(mp), ptr(lp), B, H, D_QK, D_V, PAGE, SKV // PAGE, pool.shape[0], splits, 0,
+                                            -1, SCALE, _lib.BF16, stream), "fdmla_decode_paged")
+        return f
+    k_ms = median_launch_ms(kernel_call(table))
     # control: the same launch with every sequence's page table aliased onto the pages of 8 sequences
     # (38 MB of distinct cache rows, resident in L2), i.e. the kernel with HBM taken out of the picture
     alias_table = table[:8].repeat((B + 7) // 8, 1)[:B].contiguous()
-
-    def kernel_l2_resident():
-        _lib.check(L.fdmla_decode_paged(Q.data_ptr(), pool.data_ptr(), alias_table.data_ptr(), seqlens.data_ptr(),
-                                        O.data_ptr(), m.data_ptr(), l.data_ptr(), Op.data_ptr(), mp.data_ptr(),
-                                        lp.data_ptr(), B, H, D_QK, D_V, PAGE, SKV // PAGE, pool.shape[0], splits, 0, -1,
-                                        SCALE, _lib.BF16, stream), "fdmla_decode_paged")
-    k_l2_ms = time_steps(kernel_l2_resident, args.steps, 3, world) / args.steps
-    _lib.set_decode_merge(True)
+    k_l2_ms = median_launch_ms(kernel_call(alias_table))
     achieved = DECODE_BYTES / (k_ms * 1e-3) / 1e9
 
-    # end to end: host buffers in, host buffers out, through the public operator.  Every step copies its
-    # inputs from pinned host memory and its results back; the copies run on their own streams with two
-    # sets of buffers, so the copy-in of step i+1 and the copy-out of step i-1 overlap the kernel of step i.
-    NB = 2
-    hQ, htab, hlen = Q.cpu().pin_memory(), table.cpu().pin_memory(), seqlens.cpu().pin_memory()
-    dQ = [torch.empty_like(Q) for _ in range(NB)]
-    dtab = [torch.empty_like(table) for _ in range(NB)]
-    dlen = [torch.empty_like(seqlens) for _ in range(NB)]
-    hO = [torch.empty(B, H, D_V, dtype=torch.bfloat16).pin_memory() for _ in range(NB)]
-    hm = [torch.empty(B, H).pin_memory() for _ in range(NB)]
-    hl = [torch.empty(B, H).pin_memory() for _ in range(NB)]
-    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    ev_in = [torch.cuda.Event() for _ in range(NB)]
-    ev_done = [torch.cuda.Event() for _ in range(NB)]
-    ev_out = [torch.cuda.Event() for _ in range(NB)]
-    keep = [None] * NB
-    counter = [0]
-
-    def e2e_step():
-        i = counter[0]
-        counter[0] += 1
-        b = i % NB
-        cur = torch.cuda.current_stream()
-        with torch.cuda.stream(s_in):
-            if i >= NB:
-                s_in.wait_event(ev_done[b])              # the kernel that read this input set is finished
-            dQ[b].copy_(hQ, non_blocking=True); dtab[b].copy_(htab, non_blocking=True); dlen[b].copy_(hlen, non_blocking=True)
-            ev_in[b].record(s_in)
-        cur.wait_event(ev_in[b])
-        o, mm, ll = flashdmla.flash_dmla_paged_decode(dQ[b], pool, dtab[b], dlen[b], D_V, SCALE, num_splits=splits,
-                                                      workspace=ws, max_seqlen=SKV)
-        ev_done[b].record(cur)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(ev_done[b])
-            if i >= NB:
-                s_out.wait_event(ev_out[b])
-            for t in (o, mm, ll):
-                t.record_stream(s_out)
-            hO[b].copy_(o, non_blocking=True); hm[b].copy_(mm, non_blocking=True); hl[b].copy_(ll, non_blocking=True)
-            ev_out[b].record(s_out)
-        keep[b] = (o, mm, ll)
-
-    def e2e_time(steps, warmup):
-        for _ in range(warmup):
-            e2e_step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        cur = torch.cuda.current_stream()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(cur)
-        s_in.wait_event(e0)
-        s_out.wait_event(e0)
-        for _ in range(steps):
-            e2e_step()
-        cur.wait_stream(s_in)
-        cur.wait_stream(s_out)
-        e1.record(cur)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-    e2e_ms = e2e_time(args.steps, 3) / args.steps
+    e2e = bench_e2e(dev, world, Q, pool, table, seqlens, splits, ws, args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    h2d = hQ.numel() * 2 + htab.numel() * 4 + hlen.numel() * 4
-    d2h = hO[0].numel() * 2 + hm[0].numel() * 4 + hl[0].numel() * 4
 
-    prefill = None
-    on_the_fly = None
-    moe_plumbing = None
+    prefill = on_the_fly = moe_plumbing = long_context = context_prefill = None
     if not args.no_prefill:
-        prefill = bench_prefill(dev, rank, world, tf_burst)
+        prefill = bench_prefill(dev, rank, world, tf_burst, tf_sust)
+        if world > 1:
+            del pool
+            torch.cuda.empty_cache()
+            long_context = bench_long_context(dev, rank, world)
+            context_prefill = bench_context_prefill(dev, rank, world)
         if rank == 0:
             on_the_fly = bench_on_the_fly(dev, tf_burst)
             moe_plumbing = bench_moe_plumbing(dev, hbm_peak)
@@ -396,15 +382,11 @@ def main():
             "metric": "paged_mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "paged_mla_decode", "B_per_gpu": B, "H": H, "Skv": SKV, "d_qk": D_QK, "d_v": D_V,
-                       "page_size": PAGE, "num_splits": splits, "parallelism": f"batch-sharded x{world}, no collective",
-                       "l2": "working set 604 MB per step exceeds the 126 MB L2 (no flush needed)",
-                       "kernel_family": kernel_family},
+            "config": decode_config(world),
+            "plan": {"num_splits": splits, "schedule": mode_name, "kernel_family": kernel_family,
+                     "host_cores_of_rank0": len(cores) if cores else None},
             "clocks": clocks,
-            "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "note": "paged KV pool stays resident in HBM (it is the cache); every step copies Q, page table, seqlens in "
-                            "and O, m, l out; the copies run on their own streams, double-buffered, overlapping the kernel"},
+            "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps * world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "traffic": NCU_DRAM_BYTES_PER_SEQ * B,
@@ -412,11 +394,15 @@ def main():
                                            "scaled by the number of sequences",
                          "peak_source": peak_src,
                          "kernel": "fwd_tc2_kernel (2-CTA tcgen05 split-KV decode)", "kernel_ms": k_ms,
+                         "kernel_ms_method": "median of 200 back-to-back C-ABI calls, one CUDA event between calls",
                          "algorithmic_bytes": DECODE_BYTES, "tensor_tflops": DECODE_FLOP / (k_ms * 1e-3) / 1e12,
                          "kernel_ms_l2_resident_control": k_l2_ms,
+                         "tiles_per_pair_max": tiles_per_pair_max, "pairs": n_units, "pairs_idle_frac": pairs_idle_frac,
                          "frac_of_8TBs_spec": achieved / 8000.0},
             "decode_hbm_gbs_per_gpu": DECODE_BYTES / (ms_per_step * 1e-3) / 1e9,
             "prefill": prefill,
+            "long_context": long_context,
+            "context_parallel_prefill": context_prefill,
             "on_the_fly": on_the_fly,
             "moe_plumbing": moe_plumbing,
             "device_error_flag": err,
@@ -428,8 +414,228 @@ def main():
         dist.destroy_process_group()
 
 
-def bench_prefill(dev, rank, world, tf_peak, iters=3):
-    """Causal prefill, B=4,H=128,S=8192, d=576/512, heads sharded over ranks (K_lat replicated)."""
+def bench_e2e(dev, world, Q, pool, table, seqlens, splits, ws, steps):
+    """End to end through the public operator with HOST buffers: every step copies its inputs (Q, page table,
+    lengths) from pinned host memory and its results (O, m, l) back.  One staging buffer per direction - the three
+    tensors packed at 256-byte offsets - so that a step is ONE copy in and ONE copy out; the device side works on
+    views of the staging buffers.  The copies run on their own streams with two sets of buffers, so the copy-in of
+    step i+1 and the copy-out of step i-1 overlap the kernel of step i.  The same schedule without the kernel gives
+    the ceiling the host link sets (`copy_only_ms`)."""
+    import flashdmla
+    al = lambda n: (n + 255) & ~255
+    nQ, ntab, nlen = Q.numel() * 2, table.numel() * 4, seqlens.numel() * 4
+    o_tab, o_len, n_in = al(nQ), al(nQ) + al(ntab), al(nQ) + al(ntab) + al(nlen)
+    nO, nm = B * H * D_V * 2, B * H * 4
+    o_m, o_l, n_out = al(nO), al(nO) + al(nm), al(nO) + 2 * al(nm)
+    NB = 2
+    h_in = torch.empty(n_in, dtype=torch.uint8).pin_memory()
+    h_in[:nQ].copy_(Q.cpu().view(torch.uint8).reshape(-1))
+    h_in[o_tab:o_tab + ntab].copy_(table.cpu().view(torch.uint8).reshape(-1))
+    h_in[o_len:o_len + nlen].copy_(seqlens.cpu().view(torch.uint8).reshape(-1))
+    h_out = [torch.empty(n_out, dtype=torch.uint8).pin_memory() for _ in range(NB)]
+    d_in = [torch.empty(n_in, dtype=torch.uint8, device=dev) for _ in range(NB)]
+    d_out = [torch.empty(n_out, dtype=torch.uint8, device=dev) for _ in range(NB)]
+    vQ = [d[:nQ].view(torch.bfloat16).view(B, H, D_QK) for d in d_in]
+    vtab = [d[o_tab:o_tab + ntab].view(torch.int32).view(B, -1) for d in d_in]
+    vlen = [d[o_len:o_len + nlen].view(torch.int32) for d in d_in]
+    vout = [(d[:nO].view(torch.bfloat16).view(B, H, D_V), d[o_m:o_m + nm].view(torch.float32).view(B, H),
+             d[o_l:o_l + nm].view(torch.float32).view(B, H)) for d in d_out]
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    ev_in = [torch.cuda.Event() for _ in range(NB)]
+    ev_done = [torch.cuda.Event() for _ in range(NB)]
+    ev_out = [torch.cuda.Event() for _ in range(NB)]
+    counter = [0]
+
+    def e2e_step(with_kernel):
+        i = counter[0]
+        counter[0] += 1
+        b = i % NB
+        cur = torch.cuda.current_stream()
+        with torch.cuda.stream(s_in):
+            if i >= NB:
+                s_in.wait_event(ev_done[b])              # the kernel that read this input set is finished
+            d_in[b].copy_(h_in, non_blocking=True)
+            ev_in[b].record(s_in)
+        cur.wait_event(ev_in[b])
+        if i >= NB:
+            cur.wait_event(ev_out[b])                    # the copy that read this output set is finished
+        if with_kernel:
+            flashdmla.flash_dmla_paged_decode(vQ[b], pool, vtab[b], vlen[b], D_V, SCALE, num_splits=splits,
+                                              workspace=ws, max_seqlen=SKV, out=vout[b])
+        ev_done[b].record(cur)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[b])
+            h_out[b].copy_(d_out[b], non_blocking=True)
+            ev_out[b].record(s_out)
+
+    def e2e_time(n, warmup, with_kernel):
+        counter[0] = 0
+        for _ in range(warmup):
+            e2e_step(with_kernel)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        cur = torch.cuda.current_stream()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(cur)
+        s_in.wait_event(e0)
+        s_out.wait_event(e0)
+        for _ in range(n):
+            e2e_step(with_kernel)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+        e1.record(cur)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / n
+    e2e_ms = e2e_time(steps, 4, True)
+    got = vout[(counter[0] - 1) % NB]
+    torch.cuda.synchronize()
+    O_ref, m_ref, l_ref = flashdmla.flash_dmla_paged_decode(Q, pool, table, seqlens, D_V, SCALE, num_splits=splits, workspace=ws)
+    same = bool(torch.equal(got[0], O_ref) and torch.equal(got[1], m_ref))
+    copy_ms = e2e_time(steps, 4, False)
+    return {"value": world * B / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": n_in,
+            "d2h_bytes_per_step": n_out, "ms_per_step": e2e_ms, "copy_only_ms": copy_ms,
+            "frac_of_copy_ceiling": copy_ms / e2e_ms,
+            "h2d_gbs_per_gpu": n_in / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_gpu": n_out / (e2e_ms * 1e-3) / 1e9,
+            "host_link_gbs_all_gpus": world * (n_in + n_out) / (e2e_ms * 1e-3) / 1e9,
+            "result_matches_resident_run": same,
+            "note": "paged KV pool stays resident in HBM (it is the cache); every step moves Q, page table, seqlens in "
+                    "and O, m, l out, one copy per direction from/to one pinned staging buffer, on their own streams, "
+                    "double-buffered; copy_only_ms is the same schedule without the kernel"}
+
+
+def _median_over_ranks(ms, world):
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return ms
+
+
+def bench_long_context(dev, rank, world, steps=50, warmup=10):
+    """Long-context decode (B=8, H=128, Skv ~ U{16384..131072}, page 64): the KV sequence of every request is cut
+    into `world` contiguous page-aligned slices (remainder to the first ranks, the rule of the reference's
+    csrc/attention/fa2_fwd_mpi.cu:47-53), every rank attends its slice, the partial (O, m, l) travel in one
+    NCCL all-gather and every rank merges them.  Timed per phase with CUDA events (median over the steps, max over
+    ranks) and as a whole like the headline (K steps between barriers, max over ranks)."""
+    import flashdmla
+    from flashdmla import parallel
+    B8 = 8
+    lens = torch.randint(16384, 131073, (B8,), generator=torch.Generator().manual_seed(4100)).tolist()
+    pages = [(x + PAGE - 1) // PAGE for x in lens]
+    n_pages = sum(pages)
+    g = torch.Generator(device=dev).manual_seed(4101)          # the same cache on every rank
+    pool = torch.empty(n_pages, PAGE, D_QK, dtype=torch.bfloat16, device=dev)
+    for p0 in range(0, n_pages, 1024):
+        p1 = min(n_pages, p0 + 1024)
+        pool[p0:p1] = (torch.randn(p1 - p0, PAGE, D_QK, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    Q = (torch.randn(B8, H, D_QK, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(4102)).to(torch.int32)
+    table = torch.zeros(B8, max(pages), dtype=torch.int32)
+    cur = 0
+    for b in range(B8):
+        table[b, :pages[b]] = perm[cur:cur + pages[b]]
+        cur += pages[b]
+    seqlens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    table_d = table.to(dev)
+    # the unsplit problem on one GPU: reference result and 1-GPU time
+    ws1 = flashdmla.DecodeWorkspace()
+    one = lambda: flashdmla.flash_dmla_paged_decode(Q, pool, table_d, seqlens, D_V, SCALE, workspace=ws1, max_seqlen=max(lens))
+    O1, m1, l1 = one()
+    one_ms = _median_over_ranks(median_launch_ms(one, launches=steps, warmup=warmup), world)
+    # this rank's slice: its own pool holding only its pages
+    parts = parallel.split_sequence_pages(lens, PAGE, world, rank)
+    ids = torch.cat([table[b, first:first + n] for b, (first, n, _) in enumerate(parts)]).long()
+    lpool = pool[ids.to(dev)].contiguous()
+    ltab = torch.zeros(B8, max(max(n for _, n, _ in parts), 1), dtype=torch.int32)
+    llen = torch.zeros(B8, dtype=torch.int32)
+    cur = 0
+    for b, (first, n, ntok) in enumerate(parts):
+        ltab[b, :n] = torch.arange(cur, cur + n, dtype=torch.int32)
+        cur += n
+        llen[b] = ntok
+    ltab, llen = ltab.to(dev), llen.to(dev)
+    del pool
+    torch.cuda.empty_cache()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+    res = [None]
+
+    def make_step(ev):
+        def f():
+            res[0] = parallel.sequence_parallel_decode(Q, lpool, ltab, llen, D_V, SCALE, timing_events=ev)
+        return f
+    plain = make_step(None)
+    for _ in range(warmup):
+        plain()
+    torch.cuda.synchronize()
+    dist.barrier()
+    for i in range(steps):
+        make_step(evs[i])()
+    torch.cuda.synchronize()
+    med = lambda a, b: statistics.median(e[a].elapsed_time(e[b]) for e in evs)
+    local_ms, ag_ms, merge_ms = (_median_over_ranks(med(0, 1), world), _median_over_ranks(med(1, 2), world),
+                                 _median_over_ranks(med(2, 3), world))
+    total_ms = time_steps(plain, steps, 3, world) / steps
+    O, m, l = res[0]
+    err = float((O.float() - O1.float()).abs().max())
+    msg_bytes = B8 * H * (D_V + 2) * 4
+    local_tokens = int(llen.sum().item())
+    return {"workload": f"long-context decode B={B8} H={H} Skv~U[16384,131072] page={PAGE}, KV split over {world} GPUs "
+                        f"(sequence lengths {lens})",
+            "tokens_per_s": B8 / (total_ms * 1e-3), "ms_per_step": total_ms,
+            "local_ms": local_ms, "allgather_ms": ag_ms, "merge_ms": merge_ms,
+            "bytes_out": msg_bytes, "bytes_in": (world - 1) * msg_bytes,
+            "allgather_busbw_gbs": (world - 1) * msg_bytes / (ag_ms * 1e-3) / 1e9,
+            "vs_1gpu_ms": one_ms, "speedup_over_1gpu": one_ms / total_ms,
+            "local_hbm_gbs_rank0": local_tokens * D_QK * 2 / (local_ms * 1e-3) / 1e9,
+            "max_abs_vs_unsplit": err, "collective": "torch.distributed.all_gather_into_tensor (NCCL), one message per rank",
+            "limiter": max((("local attention", local_ms), ("all-gather", ag_ms), ("merge", merge_ms)), key=lambda kv: kv[1])[0]}
+
+
+def bench_context_prefill(dev, rank, world, iters=10):
+    """Context-parallel causal prefill, B=1, H=128, S=1024 per GPU: zigzag chunks, one NCCL all-gather of the bf16
+    latent rows, then the tensor-core forward on this rank's two query chunks."""
+    import flashdmla
+    from flashdmla import parallel
+    S = 1024 * world
+    g = torch.Generator(device=dev).manual_seed(4200)          # the same tensors on every rank, then sharded
+    K = (torch.randn(1, S, D_QK, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    Kl = parallel.shard_context(K, world, rank, dim=1)
+    Ql = (torch.randn(1, PF_H, S // world, D_QK, generator=torch.Generator(device=dev).manual_seed(4300 + rank), device=dev)
+          * 0.1).to(torch.bfloat16)
+    del K
+    step = lambda: parallel.context_parallel_prefill(Ql, Kl, D_V, SCALE)
+    flat = torch.empty((world,) + tuple(Kl.shape), dtype=Kl.dtype, device=dev)
+    gather = lambda: dist.all_gather_into_tensor(flat.view(world * Kl.shape[0], *Kl.shape[1:]), Kl)
+    for _ in range(3):
+        step(); gather()
+    tot, ag = [], []
+    for _ in range(iters):
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record(); step(); e[1].record(); gather(); e[2].record()
+        torch.cuda.synchronize()
+        tot.append(e[0].elapsed_time(e[1])); ag.append(e[1].elapsed_time(e[2]))
+    total_ms = _median_over_ranks(statistics.median(tot), world)
+    ag_ms = _median_over_ranks(statistics.median(ag), world)
+    flop = 2.0 * PF_H * (S * (S + 1) / 2) * (D_QK + D_V)
+    return {"workload": f"context-parallel causal prefill B=1 H={PF_H} S={S} over {world} GPUs (zigzag chunks)",
+            "ms": total_ms, "allgather_ms_alone": ag_ms, "allgather_share": ag_ms / total_ms,
+            "allgather_bytes_in": (world - 1) * Kl.numel() * 2, "tflops_total": flop / (total_ms * 1e-3) / 1e12,
+            "tokens_per_s": S / (total_ms * 1e-3)}
+
+
+def bench_prefill(dev, rank, world, tf_burst, tf_sust, iters=10, warmup=3):
+    """Causal prefill, B=4,H=128,S=8192, d=576/512, heads sharded over ranks (K_lat replicated); median of `iters`
+    launches after `warmup`, max over ranks."""
     import flashdmla
     Hl = PF_H // world
     g = torch.Generator(device=dev).manual_seed(77)
@@ -440,46 +646,57 @@ def bench_prefill(dev, rank, world, tf_peak, iters=3):
 
     def step():
         return flashdmla.flash_dmla_cache_latent(Q, K, D_V, SCALE, True)
-    ms = time_steps(step, iters, 1, world) / iters
+    if world > 1:
+        dist.barrier()
+    ms = _median_over_ranks(median_launch_ms(step, launches=iters, warmup=warmup), world)
     tflops = PREFILL_FLOP_CAUSAL / (ms * 1e-3) / 1e12
     return {"workload": f"causal prefill B={PF_B} H={PF_H} S={PF_S} d=576/512, heads sharded", "ms": ms, "tflops_total": tflops,
-            "tflops_per_gpu": tflops / world, "frac_of_measured_bf16_peak": tflops / world / tf_peak,
+            "tflops_per_gpu": tflops / world, "frac_of_measured_bf16_peak": tflops / world / tf_burst,
+            "frac_of_measured_bf16_sustained": tflops / world / tf_sust,
             "frac_of_2250_spec": tflops / world / 2250.0, "kernel_family": flashdmla.last_kernel(),
+            "timing": f"median of {iters} launches after {warmup} warm-ups, CUDA events",
             "tokens_per_s": PF_B * PF_S / (ms * 1e-3)}
 
 
-def bench_on_the_fly(dev, tf_peak, iters=3):
-    """On-the-fly mode (per-head K, V projected to 64-wide latents), B=8,H=16,S=4096, causal: forward and
-    backward through the autograd operator.  FLOP: attention 4 S(S+1)/2 64 per head forward (two GEMMs), five
-    GEMMs backward, plus the latent projections (2 forward, 2 recomputed + 2 gradient + 2 weight-gradient backward)."""
+def bench_on_the_fly(dev, tf_peak, iters=5):
+    """On-the-fly mode (per-head K, V projected to 64-wide latents), causal, forward and backward through the
+    autograd operator, at B=8,H=16,S=4096 (the training-backward configuration) and at B=4,H=16,S=2048 (the
+    single-GPU forward configuration).  FLOP: attention 4 S(S+1)/2 64 per head forward (two GEMMs), five GEMMs
+    backward, plus the latent projections (2 forward, 2 recomputed + 2 gradient + 2 weight-gradient backward)."""
     import flashdmla
-    B4, H4, S4, dm, dl = 8, 16, 4096, 128, 64
-    g = torch.Generator(device=dev).manual_seed(99)
-    mk = lambda *sh, s=1.0: (torch.randn(*sh, generator=g, device=dev) * s).to(torch.bfloat16)
-    Q, K, V = mk(B4, H4, S4, dl), mk(B4, H4, S4, dm), mk(B4, H4, S4, dm)
-    WK, WV = mk(dm, dl, s=0.1), mk(dm, dl, s=0.1)
-    dO = mk(B4, H4, S4, dl)
-    ts = [t.requires_grad_(True) for t in (Q, K, V, WK, WV)]
-    attn = 2.0 * B4 * H4 * (S4 * (S4 + 1) / 2) * dl            # one causal GEMM
-    proj = 2.0 * B4 * H4 * S4 * dm * dl                        # one projection-sized GEMM
-    fwd_flop, bwd_flop = 2 * attn + 2 * proj, 5 * attn + 6 * proj
-    fwd_ms, bwd_ms = [], []
-    for _ in range(iters + 1):
-        for t in ts:
-            t.grad = None
-        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        e[0].record()
-        O, m, l = flashdmla.flash_dmla_on_the_fly(*ts, 0.125, True)
-        e[1].record()
-        O.backward(dO)
-        e[2].record()
-        torch.cuda.synchronize()
-        fwd_ms.append(e[0].elapsed_time(e[1]))
-        bwd_ms.append(e[1].elapsed_time(e[2]))
-    f, b = sorted(fwd_ms[1:])[len(fwd_ms[1:]) // 2], sorted(bwd_ms[1:])[len(bwd_ms[1:]) // 2]
-    return {"workload": f"on-the-fly B={B4} H={H4} S={S4} d_model={dm} d_lat={dl} causal (autograd operator)",
-            "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fwd_flop / (f * 1e-3) / 1e12, "bwd_tflops": bwd_flop / (b * 1e-3) / 1e12,
-            "bwd_frac_of_measured_bf16_peak": bwd_flop / (b * 1e-3) / 1e12 / tf_peak, "kernel_family": flashdmla.last_kernel()}
+
+    def one(B4, H4, S4, dm=128, dl=64):
+        g = torch.Generator(device=dev).manual_seed(99)
+        mk = lambda *sh, s=1.0: (torch.randn(*sh, generator=g, device=dev) * s).to(torch.bfloat16)
+        Q, K, V = mk(B4, H4, S4, dl), mk(B4, H4, S4, dm), mk(B4, H4, S4, dm)
+        WK, WV = mk(dm, dl, s=0.1), mk(dm, dl, s=0.1)
+        dO = mk(B4, H4, S4, dl)
+        ts = [t.requires_grad_(True) for t in (Q, K, V, WK, WV)]
+        attn = 2.0 * B4 * H4 * (S4 * (S4 + 1) / 2) * dl            # one causal GEMM
+        proj = 2.0 * B4 * H4 * S4 * dm * dl                        # one projection-sized GEMM
+        fwd_flop, bwd_flop = 2 * attn + 2 * proj, 5 * attn + 6 * proj
+        fwd_ms, bwd_ms = [], []
+        for _ in range(iters + 2):
+            for t in ts:
+                t.grad = None
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            O, m, l = flashdmla.flash_dmla_on_the_fly(*ts, 0.125, True)
+            e[1].record()
+            O.backward(dO)
+            e[2].record()
+            torch.cuda.synchronize()
+            fwd_ms.append(e[0].elapsed_time(e[1]))
+            bwd_ms.append(e[1].elapsed_time(e[2]))
+        f, b = statistics.median(fwd_ms[2:]), statistics.median(bwd_ms[2:])
+        return {"workload": f"on-the-fly B={B4} H={H4} S={S4} d_model={dm} d_lat={dl} causal (autograd operator)",
+                "fwd_ms": f, "bwd_ms": b, "fwd_tflops": fwd_flop / (f * 1e-3) / 1e12, "bwd_tflops": bwd_flop / (b * 1e-3) / 1e12,
+                "fwd_frac_of_measured_bf16_peak": fwd_flop / (f * 1e-3) / 1e12 / tf_peak,
+                "bwd_frac_of_measured_bf16_peak": bwd_flop / (b * 1e-3) / 1e12 / tf_peak,
+                "tokens_per_s_fwd": B4 * S4 / (f * 1e-3), "kernel_family": flashdmla.last_kernel()}
+    out = one(8, 16, 4096)
+    out["config1"] = one(4, 16, 2048)
+    return out
 
 
 def bench_moe_plumbing(dev, hbm_peak, iters=5):

@@ -1,12 +1,18 @@
 """Build libflashdmla.so (sm_100a only) in-tree with nvcc.
 
-    python ds-flashdmla-moe_b200/build.py [--force] [--verbose]
+    python ds-flashdmla-moe_b200/build.py [--force] [--verbose] [--timeline]
 
 Every .cu under csrc/ is compiled with
 `-gencode arch=compute_100a,code=sm_100a -lineinfo` and linked into
 flashdmla/libflashdmla.so.  The CUDA runtime is linked statically and the
 driver API is reached through cudaGetDriverEntryPoint, so the library loads on
 a machine without a GPU driver (symbol checks, CPU-only test runs).
+
+--timeline builds a second library, flashdmla/libflashdmla_timeline.so, with
+-DFDMLA_TIMELINE: the 2-CTA forward kernel then stamps what every CTA pair does
+with the global timer and the launcher appends the stamps of every launch to
+the file named by FDMLA_TIMELINE_FILE (select the library with FLASHDMLA_LIB).
+A development aid; the ordinary library contains none of it.
 """
 from __future__ import annotations
 
@@ -37,15 +43,18 @@ def _newest_header() -> float:
     return max(os.path.getmtime(h) for h in hs)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, timeline: bool = False) -> str:
+    obj_dir = OBJ + "_timeline" if timeline else OBJ
+    out = OUT.replace(".so", "_timeline.so") if timeline else OUT
+    extra = ["-DFDMLA_TIMELINE"] if timeline else []
+    os.makedirs(obj_dir, exist_ok=True)
     hdr = _newest_header()
     jobs = []
     for src in _sources():
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJ, src[:-3] + ".o")
+        o = os.path.join(obj_dir, src[:-3] + ".o")
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
-            cmd = ["nvcc", *NVCC_FLAGS, "-c", s, "-o", o]
+            cmd = ["nvcc", *NVCC_FLAGS, *extra, "-c", s, "-o", o]
             if verbose:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -59,11 +68,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=4) as ex:
         list(ex.map(run, jobs))
-    objs = [os.path.join(OBJ, s[:-3] + ".o") for s in _sources()]
-    if jobs or not os.path.exists(OUT):
-        run(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT, *objs])
-    return OUT
+    objs = [os.path.join(obj_dir, s[:-3] + ".o") for s in _sources()]
+    if jobs or not os.path.exists(out):
+        run(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, *objs])
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, timeline="--timeline" in sys.argv))

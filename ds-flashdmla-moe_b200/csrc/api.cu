@@ -64,6 +64,48 @@ cache_gather_kernel(const T *__restrict__ pool, const int32_t *__restrict__ page
     for (int k = threadIdx.x; k < d; k += blockDim.x) dst[k] = src[k];
 }
 
+// CTA pairs the 2-CTA tensor kernel keeps resident on the current device (74 on a B200); the constant when there
+// is no device to ask.
+static int pair_units() {
+    const int n = fwd_tensor2_resident_clusters();
+    return n > 0 ? n : kNumSMs / 2;
+}
+
+static double equal_split_cost(long long items, int tiles, int s, int units) {
+    const long long waves = (items * s + units - 1) / units;
+    double cost = (double)waves * ((double)tiles / s + 1.5);
+    if (s > 1) cost += 0.75 + 0.02 * s * (double)waves;   // merge launch + partial traffic
+    return cost;
+}
+
+// How a decode call with `slabs` partial slabs runs on the 2-CTA tensor kernel when a final result is wanted.
+// Costs are in tile times (a 256-key tile of one CTA pair), for sequences of the maximum length.
+//   EQUAL               every sequence in `slabs` equal pieces, merge kernel
+//   BALANCED_MERGE      the tiles of all sequences in equal contiguous runs, a sequence cut into at most `slabs`
+//                       pieces, merge kernel over the cut rows (launch + partial traffic: about 7 tile times)
+//   BALANCED_IN_KERNEL  the same runs with at most min(slabs - 1, kMaxInKernelPieces) pieces per sequence, merged by
+//                       the CTA pair that finishes a sequence's last piece; the last slab holds the arrival counters
+constexpr int kMaxInKernelPieces = 4;
+struct DecodePlan { enum Mode { EQUAL, BALANCED_MERGE, BALANCED_IN_KERNEL } mode; int quota_min; double cost; };
+
+static DecodePlan plan_decode(int B, int nt_max, int slabs, int units) {
+    DecodePlan best{DecodePlan::EQUAL, 0, equal_split_cost(B, nt_max, slabs, units)};
+    if (slabs < 2 || nt_max < 1) return best;
+    const long long run = ((long long)B * nt_max + units - 1) / units;
+    {   // pieces <= floor((nt - 1) / q) + 2 <= slabs  <=  q >= ceil(nt / (slabs - 1))
+        const int qmin = (nt_max + slabs - 2) / (slabs - 1);
+        const double cost = (double)(run > qmin ? run : qmin) + 1.5 + 7.0;
+        if (cost < best.cost) best = DecodePlan{DecodePlan::BALANCED_MERGE, qmin, cost};
+    }
+    if (slabs >= 3) {
+        const int pieces = slabs - 1 < kMaxInKernelPieces ? slabs - 1 : kMaxInKernelPieces;
+        const int qmin = (nt_max + pieces - 2) / (pieces - 1);
+        const double cost = (double)(run > qmin ? run : qmin) + 1.5 + 1.0;
+        if (cost < best.cost) best = DecodePlan{DecodePlan::BALANCED_IN_KERNEL, qmin, cost};
+    }
+    return best;
+}
+
 }  // namespace fdmla
 
 using namespace fdmla;
@@ -158,39 +200,51 @@ int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,
     // adds partial results that have to be written, read back and merged.
     const bool mla = (dtype == FDMLA_BF16 && d_qk == 576 && d_v == 512 && page_size % 64 == 0);
     const int tile = mla ? 256 : 32;
-    const int units = mla ? kNumSMs / 2 : kNumSMs;
+    const int units = mla ? pair_units() : kNumSMs;
     const long long items = (long long)B * ((H + 127) / 128) * ((mla || d_v <= 256) ? 1 : 2);
-    const double tiles = (double)((max_seqlen + tile - 1) / tile);
+    const int tiles = (max_seqlen + tile - 1) / tile;
     const int pages = (max_seqlen + page_size - 1) / page_size;
     int best = 1;
     double best_cost = 1e30;
-    const int s_max = (int)tiles < pages ? (int)tiles : pages;      // never less than one tile per split
+    const int s_max = tiles < pages ? tiles : pages;      // never less than one tile per split
     for (int s = 1; s <= 64 && s <= s_max; ++s) {
-        const long long waves = (items * s + units - 1) / units;
-        double cost = (double)waves * (tiles / s + 1.5);
-        if (s > 1) cost += 0.75 + 0.02 * s * (double)waves;   // merge launch + partial traffic
+        const double cost = equal_split_cost(items, tiles, s, units);
         if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
-    if (mla && H <= 128 && (int)tiles >= 1) {
-        // Balanced schedule of the 2-CTA kernel: the tiles of all sequences are dealt out in equal
-        // contiguous runs, so the cost is the run length plus one pipeline fill, the merge launch and
-        // the partials of the sequences that get cut (at most one per CTA pair; together about seven
-        // tile times on a B200).  The slabs only bound how often one sequence may be cut.
+    if (mla && H <= 128 && H >= 2 && tiles >= 1) {
+        // Balanced schedule of the 2-CTA kernel (see DecodePlan): first with the merge inside the attention kernel,
+        // which wants one slab more than the pieces a sequence may be cut into ...
+        for (int pieces = 2; pieces <= kMaxInKernelPieces; ++pieces) {
+            const DecodePlan pl = plan_decode(B, tiles, pieces + 1, units);
+            if (pl.mode == DecodePlan::BALANCED_IN_KERNEL && pl.cost < best_cost - 1e-9) { best_cost = pl.cost; best = pieces + 1; }
+        }
+        // ... then with the merge kernel, for few long sequences that have to be cut many times: twice the pieces a
+        // full-length sequence needs, since ragged batches have shorter runs than B x max and cut more often
         const double run = std::ceil((double)B * tiles / units);
-        // twice the pieces a full-length sequence needs: ragged batches have fewer tiles than B x max, so their
-        // runs are shorter than `run` and a long sequence is cut more often
         int slabs = 2 * (int)std::ceil(tiles / run) + 1;
-        if (slabs < 2) slabs = 2;
-        if (slabs > 64) slabs = 64;
-        const double run_eff = std::fmax(run, std::ceil(tiles / (slabs - 1)));
-        const double cost = run_eff + 1.5 + 7.0;     // + merge launch and partial traffic, measured ~25 us
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = slabs; }
+        slabs = slabs < kMaxInKernelPieces + 2 ? kMaxInKernelPieces + 2 : (slabs > 64 ? 64 : slabs);
+        const DecodePlan pl = plan_decode(B, tiles, slabs, units);
+        if (pl.mode != DecodePlan::EQUAL && pl.cost < best_cost - 1e-9) { best_cost = pl.cost; best = slabs; }
     }
     return best;
 }
 
-static int g_decode_merge = 1;
-void fdmla_set_decode_merge(int on) { g_decode_merge = on ? 1 : 0; }
+int fdmla_decode_plan(int B, int H, int d_qk, int d_v, int page_size, int max_pages, int num_splits, int dtype,
+                      int *quota_min, int *units) {
+    if (quota_min) *quota_min = 0;
+    if (units) *units = 0;
+    if (B <= 0 || H <= 0 || page_size <= 0 || max_pages <= 0 || num_splits < 1) return FDMLA_ERR_INVALID;
+    const bool mla = dtype == FDMLA_BF16 && d_qk == 576 && d_v == 512 && page_size % 64 == 0;
+    if (!mla || num_splits < 2 || H > 128 || H < 2 || g_backend.load() == FDMLA_BACKEND_PORTABLE ||
+        tensor_single_cta_preferred())
+        return 0;
+    const int nt_max = (int)(((long long)max_pages * page_size + 255) / 256);
+    const int u = pair_units();
+    const DecodePlan pl = plan_decode(B, nt_max, num_splits, u);
+    if (units) *units = u;
+    if (quota_min) *quota_min = pl.quota_min;
+    return (int)pl.mode;
+}
 
 int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_table,
                        const int32_t *seqlens, void *O, float *m, float *l, float *O_part,
@@ -207,6 +261,7 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_t
     if (!partial_only && (!m || !l)) return FDMLA_ERR_INVALID;
     if ((num_splits > 1 || partial_only) && (!O_part || !m_part || !l_part)) return FDMLA_ERR_WORKSPACE;
     if (B > 65535) return FDMLA_ERR_UNSUPPORTED;
+    if ((long long)max_pages * page_size > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     FwdProblem p{};
     p.Q = Q; p.K = kv_pool; p.V = nullptr; p.page_table = page_table; p.seqlens = seqlens;
@@ -215,28 +270,30 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_t
     p.G = B; p.R = H; p.Sq = 1; p.Skv = max_pages * page_size; p.d_qk = d_qk; p.d_v = d_v;
     p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages;
     p.num_splits = num_splits; p.kv_begin = kv_begin; p.kv_end = kv_end; p.causal = 0; p.scale = scale;
-    if (!partial_only && num_splits >= 2 && kv_begin <= 0 && kv_end < 0 && H <= 128) {
+    bool merge_launch = num_splits > 1 && !partial_only;
+    if (!partial_only && num_splits >= 2 && kv_begin <= 0 && kv_end < 0 && H <= 128 && H >= 2 &&
+        g_backend.load() != FDMLA_BACKEND_PORTABLE && !tensor_single_cta_preferred() && fwd_tensor2_supported(p, dtype)) {
         // A final result is wanted and there are spare slabs: the 2-CTA tensor kernel may hand out the
-        // keys as balanced runs of tiles instead of num_splits equal pieces of every sequence (other
-        // kernels ignore the hint).  It writes uncut sequences straight to O, so it needs O.
-        // It does so when that is predicted to be faster than the equal pieces: the longest run of tiles a CTA
-        // pair gets, with sequences of the maximum length, against whole waves of equal pieces.
-        const int nt_max = (max_pages * page_size + 255) / 256;
-        const int units = kNumSMs / 2;
-        const int quota_min = (nt_max + num_splits - 2) / (num_splits - 1);
-        const long long run = ((long long)B * nt_max + units - 1) / units;
-        const double bal = (double)(run > quota_min ? run : quota_min) + 1.5;
-        const long long waves = ((long long)B * num_splits + units - 1) / units;
-        const double eq = (double)waves * ((double)nt_max / num_splits + 1.5);
-        if (bal < eq) {
+        // keys as balanced runs of tiles instead of num_splits equal pieces of every sequence.  It writes
+        // uncut sequences straight to O, so it needs O.
+        const int nt_max = (int)(((long long)max_pages * page_size + 255) / 256);
+        const DecodePlan pl = plan_decode(B, nt_max, num_splits, pair_units());
+        if (pl.mode != DecodePlan::EQUAL) {
             p.balanced = 1;
-            p.quota_min = quota_min;
+            p.quota_min = pl.quota_min;
             p.O = O;
+        }
+        if (pl.mode == DecodePlan::BALANCED_IN_KERNEL) {
+            // the arrival counters live in the last slab of l_part (no piece is ever written there: a sequence is cut
+            // into num_splits - 1 pieces at most) and have to start at zero
+            p.tickets = reinterpret_cast<unsigned int *>(l_part + (size_t)(num_splits - 1) * B * H);
+            if (cudaMemsetAsync(p.tickets, 0, sizeof(unsigned int) * 2 * (size_t)B, st) != cudaSuccess) return FDMLA_ERR_CUDA;
+            merge_launch = false;
         }
     }
     int rc = run_forward(p, dtype, st);
     if (rc) return rc;
-    if (num_splits > 1 && !partial_only && g_decode_merge)
+    if (merge_launch)
         rc = launch_merge(O_part, m_part, l_part, O, m, l, (long long)B * H, d_v, num_splits, dtype, st);
     return rc;
 }
@@ -249,6 +306,17 @@ int fdmla_merge_lse(const float *O_part, const float *m_part, const float *l_par
     if (!O_part || !m_part || !l_part || !O || !m || !l) return FDMLA_ERR_INVALID;
     return launch_merge(O_part, m_part, l_part, O, m, l, rows, d_v, num_parts, out_dtype,
                         static_cast<cudaStream_t>(stream));
+}
+
+int fdmla_merge_lse_strided(const float *O_part, const float *m_part, const float *l_part, void *O,
+                            float *m, float *l, long long rows, int d_v, int num_parts,
+                            long long part_stride_o, long long part_stride_ml, int out_dtype, void *stream) {
+    if (!dtype_ok(out_dtype) || rows < 0 || d_v <= 0 || num_parts < 1) return FDMLA_ERR_INVALID;
+    if (part_stride_o < rows * d_v || part_stride_ml < rows) return FDMLA_ERR_INVALID;
+    if (rows == 0) return FDMLA_OK;
+    if (!O_part || !m_part || !l_part || !O || !m || !l) return FDMLA_ERR_INVALID;
+    return launch_merge_strided(O_part, m_part, l_part, O, m, l, rows, d_v, num_parts, (size_t)part_stride_o,
+                                (size_t)part_stride_ml, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 // workspace of the on-the-fly backward:

@@ -61,6 +61,9 @@ struct FwdProblem {
     // Balanced decode schedule of the 2-CTA tensor kernel (0 = off): keys are handed out as contiguous
     // runs of 256-key tiles, at least quota_min per CTA pair; num_splits then counts the partial slabs.
     int balanced, quota_min;
+    // Balanced schedule only: arrival counters [2 G], zero at launch.  When given, the CTA that finishes the last
+    // piece of a cut sequence merges the pieces itself and no merge kernel is needed; nullptr = merge kernel.
+    unsigned int *tickets;
 };
 
 // Token range [lo, hi) of split `s` for a group whose attended window is
@@ -86,11 +89,18 @@ __host__ __device__ __forceinline__ void split_window(int w_lo, int w_hi, int gr
 int launch_fwd_portable(const FwdProblem &p, int dtype, cudaStream_t stream);
 int launch_fwd_tensor(const FwdProblem &p, int dtype, cudaStream_t stream);   // tcgen05
 bool fwd_tensor_supported(const FwdProblem &p, int dtype);
-int tensor_error_flag(int reset);
-void tensor_prefer_single_cta(int on);   // keep MLA shapes on the 1-CTA kernel (A/B tests)   // device-side time-out / bad-page flag of the tcgen05 kernels
+int tensor_error_flag(int reset);        // device-side time-out / bad-page flag of the tcgen05 kernels
+void tensor_prefer_single_cta(int on);   // keep MLA shapes on the 1-CTA kernel (A/B tests)
+bool tensor_single_cta_preferred();
 int launch_merge(const float *O_part, const float *m_part, const float *l_part, void *O,
                  float *m, float *l, long long rows, int d_v, int num_parts, int out_dtype,
                  cudaStream_t stream);
+int launch_merge_strided(const float *O_part, const float *m_part, const float *l_part, void *O,
+                         float *m, float *l, long long rows, int d_v, int num_parts, size_t part_stride_o,
+                         size_t part_stride_ml, int out_dtype, cudaStream_t stream);
+// 2-CTA tensor kernel: does it take this problem, and how many of its CTA pairs run at once on this device
+bool fwd_tensor2_supported(const FwdProblem &p, int dtype);
+int fwd_tensor2_resident_clusters();
 int launch_project(const void *X, const void *W, void *Y, long long rows, int d_in, int d_out,
                    int w_transposed, int x_f32, int dtype, cudaStream_t stream);
 

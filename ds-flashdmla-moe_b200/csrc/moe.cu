@@ -156,7 +156,8 @@ __global__ void gather_rows_kernel(const uint4 *__restrict__ x, const int *__res
     const long long total = (long long)n_rows * vec_per_row;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / vec_per_row), v = (int)(i - (long long)r * vec_per_row);
-        packed[i] = x[(size_t)perm[r] * vec_per_row + v];
+        const int t = perm[r];          // -1: a row of padded packing that holds no assignment
+        packed[i] = t >= 0 ? x[(size_t)t * vec_per_row + v] : make_uint4(0, 0, 0, 0);
     }
 }
 
@@ -281,6 +282,9 @@ extern "C" int fdmla_moe_pack(const int *idx, int *pos, int *perm, int *offsets,
     cudaStream_t s = (cudaStream_t)stream;
     const int A = T * k, nb = (A + PACK_BLOCK - 1) / PACK_BLOCK;
     int *blk = static_cast<int *>(workspace), *lrank = blk + (size_t)(nb > 0 ? nb : 1) * E, *totals = lrank + (A > 0 ? A : 1);
+    // padded packing: rows past an expert's count keep no token; mark them so that a gather skips them
+    if (padded && (size_t)E * capacity > 0 &&
+        cudaMemsetAsync(perm, 0xff, (size_t)E * capacity * sizeof(int), s) != cudaSuccess) return FDMLA_ERR_CUDA;
     if (nb > 0) pack_count_kernel<<<nb, PACK_BLOCK, E * sizeof(int), s>>>(idx, blk, lrank, A, E);
     pack_scan_blocks_kernel<<<(E + 7) / 8, 256, 0, s>>>(blk, totals, nb, E, capacity);
     pack_scan_experts_kernel<<<1, 256, 0, s>>>(totals, offsets, E, capacity, padded);

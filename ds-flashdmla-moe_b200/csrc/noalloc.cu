@@ -5,6 +5,8 @@
 // hosts that forbid allocation calls inside an operator, and callers on a path where an
 // allocation would synchronise the device.  For them the split-KV partial results live in
 // a fixed array that is part of the library image instead of in a caller buffer.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace fdmla {
@@ -16,17 +18,18 @@ static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratch
 // The array's name is only a host-side stand-in for the symbol; the device address has to
 // be asked for, once per device, with that device current.
 constexpr int kMaxDevices = 64;
-static void *g_scratch_ptr[kMaxDevices] = {};
+static std::atomic<void *> g_scratch_ptr[kMaxDevices];
 
 static int builtin_scratch(void **ptr) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FDMLA_ERR_CUDA;
-    if (g_scratch_ptr[dev] == nullptr) {
-        void *p = nullptr;
+    void *p = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        // two host threads may both get here; both obtain the same address
         if (cudaGetSymbolAddress(&p, g_builtin_scratch) != cudaSuccess || p == nullptr) return FDMLA_ERR_CUDA;
-        g_scratch_ptr[dev] = p;
+        g_scratch_ptr[dev].store(p, std::memory_order_release);
     }
-    *ptr = g_scratch_ptr[dev];
+    *ptr = p;
     return FDMLA_OK;
 }
 
@@ -63,8 +66,10 @@ int fdmla_decode_paged_noalloc(const void *Q, const void *kv_pool, const int32_t
         p += align256(rows * sizeof(float));
         l_part = reinterpret_cast<float *>(p);
     }
-    // Nothing in the array has to start at zero: every partial slot the merge reads is
-    // written by the attention kernel of the same call first (empty splits write l = 0).
+    // The caller clears nothing: every partial slot a merge reads is written by the attention
+    // kernel of the same call first (empty splits write l = 0), and the arrival counters of the
+    // balanced schedule, which do have to start at zero, are cleared by fdmla_decode_paged with a
+    // memset on the stream before its launch.
     return fdmla_decode_paged(Q, kv_pool, page_table, seqlens, O, m, l, O_part, m_part, l_part, B, H, d_qk,
                               d_v, page_size, max_pages, num_pages, num_splits, 0, -1, scale, dtype, stream);
 }

@@ -242,20 +242,20 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 merge_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
              const float *__restrict__ l_part, TO *__restrict__ O, float *__restrict__ m,
-             float *__restrict__ l, long long rows, int d_v, int P) {
+             float *__restrict__ l, long long rows, int d_v, int P, size_t so, size_t sml) {
     const int lane = threadIdx.x & 31;
     const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
         if (l_part[r] < 0.f) continue;
         float mx = -CUDART_INF_F;
         for (int q = lane; q < P; q += 32)
-            if (l_part[q * rows + r] > 0.f) mx = fmaxf(mx, m_part[q * rows + r]);
+            if (l_part[q * sml + r] > 0.f) mx = fmaxf(mx, m_part[q * sml + r]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float ls = 0.f;
         for (int q = lane; q < P; q += 32) {
-            const float lp = l_part[q * rows + r];
-            if (lp > 0.f) ls += lp * __expf(m_part[q * rows + r] - mx);
+            const float lp = l_part[q * sml + r];
+            if (lp > 0.f) ls += lp * __expf(m_part[q * sml + r] - mx);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
@@ -264,10 +264,10 @@ merge_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
             const int c = c0 + lane * 4;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             for (int q = 0; q < P; ++q) {
-                const float lp = l_part[q * rows + r];         // same address in every lane
+                const float lp = l_part[q * sml + r];         // same address in every lane
                 if (lp > 0.f) {
-                    const float w = lp * __expf(m_part[q * rows + r] - mx) * inv;
-                    const float *src = O_part + ((size_t)q * rows + r) * d_v;
+                    const float w = lp * __expf(m_part[q * sml + r] - mx) * inv;
+                    const float *src = O_part + (size_t)q * so + (size_t)r * d_v;
                     if (c + 3 < d_v && (d_v & 3) == 0) {
                         const float4 v = *reinterpret_cast<const float4 *>(src + c);
                         acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
@@ -290,26 +290,26 @@ template <typename TO>
 __global__ void __launch_bounds__(128)
 merge_row_block_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
                        const float *__restrict__ l_part, TO *__restrict__ O, float *__restrict__ m,
-                       float *__restrict__ l, long long rows, int d_v, int P) {
+                       float *__restrict__ l, long long rows, int d_v, int P, size_t so, size_t sml) {
     const long long r = blockIdx.x;
     if (l_part[r] < 0.f) return;
     float mx = -CUDART_INF_F;
     for (int q = 0; q < P; ++q)
-        if (l_part[q * rows + r] > 0.f) mx = fmaxf(mx, m_part[q * rows + r]);
+        if (l_part[q * sml + r] > 0.f) mx = fmaxf(mx, m_part[q * sml + r]);
     float ls = 0.f;
     for (int q = 0; q < P; ++q) {
-        const float lp = l_part[q * rows + r];
-        if (lp > 0.f) ls += lp * __expf(m_part[q * rows + r] - mx);
+        const float lp = l_part[q * sml + r];
+        if (lp > 0.f) ls += lp * __expf(m_part[q * sml + r] - mx);
     }
     const float inv = ls > 0.f ? 1.f / ls : 0.f;
     for (int c = threadIdx.x * 4; c < d_v; c += 512) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
         for (int q = 0; q < P; ++q) {
-            const float lp = l_part[q * rows + r];
+            const float lp = l_part[q * sml + r];
             if (lp > 0.f) {
-                const float w = lp * __expf(m_part[q * rows + r] - mx) * inv;
-                const float *src = O_part + ((size_t)q * rows + r) * d_v;
+                const float w = lp * __expf(m_part[q * sml + r] - mx) * inv;
+                const float *src = O_part + (size_t)q * so + (size_t)r * d_v;
                 if (c + 3 < d_v && (d_v & 3) == 0) {
                     const float4 v = *reinterpret_cast<const float4 *>(src + c);
                     acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
@@ -326,17 +326,19 @@ merge_row_block_kernel(const float *__restrict__ O_part, const float *__restrict
     if (threadIdx.x == 0) { m[r] = mx; l[r] = ls; }
 }
 
-int launch_merge(const float *O_part, const float *m_part, const float *l_part, void *O,
-                 float *m, float *l, long long rows, int d_v, int num_parts, int out_dtype,
-                 cudaStream_t stream) {
+// part_stride_o / part_stride_ml: elements between consecutive parts of O_part and of m_part / l_part
+// (rows * d_v and rows for the dense [num_parts, rows, ...] layout).
+int launch_merge_strided(const float *O_part, const float *m_part, const float *l_part, void *O,
+                         float *m, float *l, long long rows, int d_v, int num_parts, size_t part_stride_o,
+                         size_t part_stride_ml, int out_dtype, cudaStream_t stream) {
     if (rows <= 0) return FDMLA_OK;
     if (rows <= 4096) {      // a block per row keeps more of the GPU busy than a warp per row would
         if (out_dtype == FDMLA_F32)
             merge_row_block_kernel<float><<<(unsigned)rows, 128, 0, stream>>>(O_part, m_part, l_part, static_cast<float *>(O), m, l,
-                                                                               rows, d_v, num_parts);
+                                                                               rows, d_v, num_parts, part_stride_o, part_stride_ml);
         else if (out_dtype == FDMLA_BF16)
             merge_row_block_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(
-                O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O), m, l, rows, d_v, num_parts);
+                O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O), m, l, rows, d_v, num_parts, part_stride_o, part_stride_ml);
         else
             return FDMLA_ERR_INVALID;
         return check_launch();
@@ -345,13 +347,20 @@ int launch_merge(const float *O_part, const float *m_part, const float *l_part, 
     const unsigned grid = (unsigned)(want < 8LL * kNumSMs ? want : 8LL * kNumSMs);
     if (out_dtype == FDMLA_F32)
         merge_kernel<float><<<grid, 256, 0, stream>>>(O_part, m_part, l_part, static_cast<float *>(O), m, l, rows,
-                                                      d_v, num_parts);
+                                                      d_v, num_parts, part_stride_o, part_stride_ml);
     else if (out_dtype == FDMLA_BF16)
         merge_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O),
-                                                             m, l, rows, d_v, num_parts);
+                                                             m, l, rows, d_v, num_parts, part_stride_o, part_stride_ml);
     else
         return FDMLA_ERR_INVALID;
     return check_launch();
+}
+
+int launch_merge(const float *O_part, const float *m_part, const float *l_part, void *O,
+                 float *m, float *l, long long rows, int d_v, int num_parts, int out_dtype,
+                 cudaStream_t stream) {
+    return launch_merge_strided(O_part, m_part, l_part, O, m, l, rows, d_v, num_parts, (size_t)rows * d_v, (size_t)rows,
+                                out_dtype, stream);
 }
 
 // ---------------------------------------------------------------------------

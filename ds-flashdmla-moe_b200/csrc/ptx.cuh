@@ -276,6 +276,13 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity)
         if (mbar_try_wait_cluster(bar, parity)) return true;
     return false;
 }
+// 32-bit load from the shared memory of a CTA of this cluster (address from map_to_cta); the CTA must be known to
+// have started, i.e. only after a cluster barrier
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -152,6 +152,25 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 tma_load_2d(smem_u32(sA1), mapA1, 0, own_rows_base + own0, BAR(B_OWNER));
                 tma_load_2d(smem_u32(sA2), mapA2, 0, own_rows_base + own0, BAR(B_OWNER));
             }
+            // A streamed tile that runs past the end of its group holds rows of the next group (or the fill value).
+            // Their columns of E1 / E2 are zero, but 0 x Inf or 0 x NaN in the accumulating GEMMs is NaN, so those
+            // rows are zeroed in shared memory once the copy has landed (whole 128-byte rows: the swizzle does not
+            // matter), as the forward kernels do for keys past the end of a sequence.
+            auto fix_tail = [&](int i) {
+                const int str0 = (s_first + i) * TILE;
+                const int limit = MODE == MODE_DKV ? p.R : p.Skv;
+                if (str0 + TILE > limit) {
+                    const int first_bad = limit > str0 ? limit - str0 : 0;
+                    const int n16 = (TILE - first_bad) * 8;
+                    uint8_t *b = sB + (i & 1) * 2 * OP_BYTES;
+                    for (int idx = lane; idx < 2 * n16; idx += 32) {
+                        const int t = idx / n16, rem = idx - t * n16;
+                        *reinterpret_cast<uint4 *>(b + t * OP_BYTES + (first_bad + rem / 8) * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                }
+            };
             load_stream(0);
             if (n_stream > 1) load_stream(1);
             ok = mbar_wait(BAR(B_OWNER), 0);
@@ -189,6 +208,7 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 }
             };
             ok = ok && mbar_wait(BAR(B_FULL), 0);
+            fix_tail(0);
             tc_fence_after_sync();
             issue_t(0, 0);
             issue_t(0, 1);
@@ -203,6 +223,7 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                         // ... and T[h] is free for the next tile's half, which overlaps the other half's elementwise work
                         if (h == 0) {
                             ok = ok && mbar_wait(BAR(B_FULL + ((i + 1) & 1)), ((i + 1) >> 1) & 1);
+                            fix_tail(i + 1);
                             tc_fence_after_sync();
                         }
                         issue_t(i + 1, h);

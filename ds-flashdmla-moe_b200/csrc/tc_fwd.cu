@@ -19,6 +19,10 @@
 // 2^8 (the row statistics written out are exact: m is the true maximum).
 #include <cuda.h>
 
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -466,8 +470,9 @@ bool make_tensor_map_bf16_chunked(CUtensorMap *m, const void *base, long long ro
 
 namespace fdmla {
 
-static int g_prefer_single_cta = 0;                            // debugging / A-B switch
-void tensor_prefer_single_cta(int on) { g_prefer_single_cta = on; }
+static std::atomic<int> g_prefer_single_cta{0};                // debugging / A-B switch
+void tensor_prefer_single_cta(int on) { g_prefer_single_cta.store(on); }
+bool tensor_single_cta_preferred() { return g_prefer_single_cta.load() != 0; }
 
 template <class C>
 static bool cfg_matches(const FwdProblem &p) {
@@ -509,7 +514,7 @@ static int launch_cfg(const FwdProblem &p, cudaStream_t stream) {
 
 int launch_fwd_tensor(const FwdProblem &p, int dtype, cudaStream_t stream) {
     if (!fwd_tensor_supported(p, dtype)) return FDMLA_ERR_UNSUPPORTED;
-    if (!g_prefer_single_cta && fwd_tensor2_supported(p, dtype)) return launch_fwd_tensor2(p, stream);
+    if (!g_prefer_single_cta.load() && fwd_tensor2_supported(p, dtype)) return launch_fwd_tensor2(p, stream);
     if (cfg_matches<MlaCfg>(p)) return launch_cfg<MlaCfg>(p, stream);
     if (cfg_matches<OtfCfg>(p)) return launch_cfg<OtfCfg>(p, stream);
     return launch_cfg<Cl64Cfg>(p, stream);

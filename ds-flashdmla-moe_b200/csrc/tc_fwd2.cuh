@@ -51,24 +51,8 @@ constexpr int Q_CHUNK = 64 * 128;     // 64 rows x 128 B
 constexpr int Q_BYTES = NQC * Q_CHUNK;            // 73 728
 constexpr int SLOT = 16384;           // ring slot: 2 boxes of [64 keys x 128 B]
 constexpr int BOX = 8192;
-#ifndef FDMLA_NSLOT
-#define FDMLA_NSLOT 7
-#endif
-constexpr int NSLOT = FDMLA_NSLOT;
-#ifndef FDMLA_TMA_EPI
-#define FDMLA_TMA_EPI 1
-#endif
-#ifndef FDMLA_PEMPTY
-#define FDMLA_PEMPTY 1
-#endif
-constexpr bool USE_PEMPTY = FDMLA_PEMPTY != 0;   // per-quarter hand-back of P (else: whole tile via OREADY)
-#ifndef FDMLA_PF_DIST
-#define FDMLA_PF_DIST 1
-#endif
-#ifndef FDMLA_PF_STEP
-#define FDMLA_PF_STEP 1
-#endif
-constexpr int PF_DIST = FDMLA_PF_DIST;  // decode: tiles of distance of the softmax threads' L2 prefetch (0 = off)
+constexpr int NSLOT = 7;              // ring slots (with Q and P resident this fills the 227 KB)
+constexpr int PF_DIST = 1;            // decode: how many tiles ahead the softmax threads prefetch cache rows into L2
 constexpr int P_Q = 64 * SUB * 2;     // one P quarter: 64 rows x 64 keys bf16 = 8 192
 constexpr int P_BYTES = 4 * P_Q;
 constexpr int P_SBO = (SUB / 8) * 128;            // 1 024
@@ -91,27 +75,25 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// Optional event trace of the first cluster (development builds only, -DFDMLA_TRACE):
-// g_trace[rank][stream][index] = SM clock at the event.
-#ifdef FDMLA_TRACE
-constexpr int TR_N = 256;
-__device__ long long g_trace[2][6][TR_N];
-__device__ int g_trace_cluster = 0;
-__device__ int g_dbg[160][8];      // per CTA: last wait each role entered (development builds only)
-#define DBG(slot, val) do { if (lane == 0) g_dbg[blockIdx.x][slot] = (val); } while (0)
-__device__ unsigned long long g_trace_span[256][4];     // per CTA: globaltimer at entry, after set-up, before teardown, at exit
+// Development builds only (-DFDMLA_TIMELINE): wall-clock stamps (globaltimer, ns) of what every CTA pair
+// does, written by the leader CTA and dumped by the launcher to the file named by the environment variable
+// FDMLA_TIMELINE_FILE after each launch.  Slot 0 kernel entry, 1 set-up done, 2 + 3 i scores of item i's first tile
+// ready, 3 + 3 i item i's last P V accumulated, 4 + 3 i item i's result written, 30 roles finished, 31 exit.
+// Nothing of this is compiled into the library otherwise.
+#ifdef FDMLA_TIMELINE
+constexpr int TL_CLUSTERS = 128, TL_SLOTS = 32, TL_ITEMS = 9;
+__device__ unsigned long long g_timeline[TL_CLUSTERS][TL_SLOTS];
+__device__ int g_timeline_tiles[TL_CLUSTERS][TL_ITEMS];
 __device__ __forceinline__ unsigned long long gtimer() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-#define TRACE(stream, idx)                                                                        \
-    do {                                                                                           \
-        if (trace_on && (idx) < TR_N) g_trace[rank][stream][idx] = clock64();                      \
-    } while (0)
+#define TL(slot) do { if (leader && cid < TL_CLUSTERS && (slot) < TL_SLOTS) g_timeline[cid][slot] = gtimer(); } while (0)
+#define TL_ITEM(i, nt) do { if (leader && cid < TL_CLUSTERS && (i) < TL_ITEMS) g_timeline_tiles[cid][i] = (nt); } while (0)
 #else
-#define TRACE(stream, idx) do { } while (0)
-#define DBG(slot, val) do { } while (0)
+#define TL(slot) do { } while (0)
+#define TL_ITEM(i, nt) do { } while (0)
 #endif
 
 // Four consecutive K=16 steps of one 2-CTA MMA: descriptors advance by a_step / b_step (in
@@ -166,6 +148,15 @@ __device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
     return true;
 }
 
+// Keys of KV group g.  A length outside [0, Skv] (Skv = max_pages * page_size for a paged cache) is clamped:
+// the page table has no entries for more, and an unclamped length would cut a sequence into more pieces
+// than the caller's scratch has slabs for.  The producer reports the clamp through the error flag.
+__device__ __forceinline__ int group_seq(const FwdProblem &p, int g) {
+    if (!p.seqlens) return p.Skv;
+    const int s = p.seqlens[g];
+    return s < 0 ? 0 : (s > p.Skv ? p.Skv : s);
+}
+
 // One unit of work of the persistent kernel: a 128-row tile of one KV group and one KV split.
 struct Item {
     int row0, g, split;       // first row of the tile, KV group, split index
@@ -188,7 +179,7 @@ __device__ __forceinline__ Item make_item(const FwdProblem &p, int idx, int n_ro
     it.split = rem - it.g * p.num_splits;
     const int tile_idx = p.causal ? n_row_tiles - 1 - rt : rt;     // causal: the longest rows first
     it.row0 = tile_idx * 128;
-    it.seq = p.seqlens ? p.seqlens[it.g] : p.Skv;
+    it.seq = group_seq(p, it.g);
     const int w_lo = p.kv_begin > 0 ? p.kv_begin : 0;
     const int w_hi = (p.kv_end >= 0 && p.kv_end < it.seq) ? p.kv_end : it.seq;
     // splits are cut on tile boundaries where the page size allows it
@@ -219,19 +210,50 @@ __device__ __forceinline__ Item make_item(const FwdProblem &p, int idx, int n_ro
 //    are laid end to end (an empty sequence counts as one) and cluster c takes tiles [c q, (c+1) q) of that
 //    line, q = max(ceil(total / n), quota_min).  A sequence that lies inside one cluster's run is
 //    written as the final result; one that is cut is written as partials (piece k into slab k) and merged
-//    by a second kernel.  quota_min bounds the pieces per sequence by the number of slabs.
+//    either by the pair that finishes the sequence's last piece (p.tickets != nullptr) or by a second
+//    kernel.  quota_min bounds the pieces per sequence by the number of slabs.
+//    A run is walked last sequence first, then the others in order: the sequences a run shares with its
+//    neighbours come first, so that both halves of a cut sequence are finished early in their runs and
+//    the merge of the pair that arrives second is not what the kernel ends with.
 struct Cursor {
     bool balanced;
     // items
     int round, n_rounds, cid, n_clusters, n_items, n_row_tiles;
     // balanced
-    int g, tile0, left, quota, first_of_g;     // first_of_g: position of sequence g's first tile on the line
+    int quota, run_lo, run_hi;                 // this cluster's tiles [run_lo, run_hi) on the line
+    int g_last, first_of_last;                 // sequence holding tile run_hi - 1 and the position of its first tile
+    int g, first_of_g;                         // walking state: next sequence in order and its first tile
+    int g_end;                                 // the in-order walk stops before this sequence
+    int phase;                                 // 0: the last sequence is due, 1: the others in order, 2: done
 };
 
 __device__ __forceinline__ int sched_tiles(const FwdProblem &p, int g) {
-    const int seq = p.seqlens ? p.seqlens[g] : p.Skv;
-    const int nt = (seq + T - 1) / T;
+    const int nt = (group_seq(p, g) + T - 1) / T;
     return nt > 0 ? nt : 1;
+}
+
+// Sequence holding tile `pos` of the line and the position of that sequence's first tile.  Called by all 32
+// lanes of a warp together; pos must be below the line's length.
+__device__ __forceinline__ void line_locate(const FwdProblem &p, int pos, int lane, int &g, int &first) {
+    int base = 0;
+    g = p.G - 1; first = 0;
+    for (int g0 = 0; g0 < p.G; g0 += 32) {
+        const int v = (g0 + lane < p.G) ? sched_tiles(p, g0 + lane) : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, (g0 + lane < p.G) && base + incl > pos);
+        if (hit) {
+            const int src = __ffs(hit) - 1;
+            first = __shfl_sync(0xffffffffu, base + incl - v, src);
+            g = g0 + src;
+            return;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+    }
 }
 
 // Called by all 32 lanes of a warp together.
@@ -244,7 +266,7 @@ __device__ __forceinline__ void cursor_init(Cursor &c, const FwdProblem &p, int 
     c.n_row_tiles = (p.R + 127) / 128;
     c.n_items = c.n_row_tiles * p.G * p.num_splits;
     c.n_rounds = (c.n_items + n_clusters - 1) / n_clusters;
-    c.g = 0; c.tile0 = 0; c.left = 0; c.quota = 1; c.first_of_g = 0;
+    c.quota = 1; c.run_lo = c.run_hi = 0; c.g_last = c.first_of_last = c.g = c.first_of_g = c.g_end = 0; c.phase = 2;
     if (!c.balanced) return;
     int total = 0;
     for (int g0 = 0; g0 < p.G; g0 += 32) total += (g0 + lane < p.G) ? sched_tiles(p, g0 + lane) : 0;
@@ -256,29 +278,12 @@ __device__ __forceinline__ void cursor_init(Cursor &c, const FwdProblem &p, int 
     c.quota = q;
     const long long start_ll = (long long)cid * q;
     if (start_ll >= total) return;                    // nothing left for this cluster
-    const int start = (int)start_ll;
-    c.left = (total - start) < q ? (total - start) : q;
-    int base = 0;
-    for (int g0 = 0; g0 < p.G; g0 += 32) {
-        const int v = (g0 + lane < p.G) ? sched_tiles(p, g0 + lane) : 0;
-        int incl = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int n = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += n;
-        }
-        const unsigned hit = __ballot_sync(0xffffffffu, base + incl > start);
-        if (hit) {
-            const int src = __ffs(hit) - 1;
-            const int first = __shfl_sync(0xffffffffu, base + incl - v, src);
-            c.g = g0 + src;
-            c.first_of_g = first;
-            c.tile0 = start - first;
-            return;
-        }
-        base += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    c.left = 0;
+    c.run_lo = (int)start_ll;
+    c.run_hi = (total - c.run_lo) < q ? total : c.run_lo + q;
+    line_locate(p, c.run_lo, lane, c.g, c.first_of_g);
+    line_locate(p, c.run_hi - 1, lane, c.g_last, c.first_of_last);
+    c.phase = (c.g_last != c.g) ? 0 : 1;
+    c.g_end = (c.g_last != c.g) ? c.g_last : c.g_last + 1;
 }
 
 // Next item of this cluster (the same in every thread that asks); false when the cluster is done.
@@ -291,12 +296,21 @@ __device__ __forceinline__ bool cursor_next(Cursor &c, const FwdProblem &p, bool
         }
         return false;
     }
-    if (c.left <= 0 || c.g >= p.G) return false;
-    const int seq = p.seqlens ? p.seqlens[c.g] : p.Skv;
-    const int nt = sched_tiles(p, c.g);
-    const int take = c.left < nt - c.tile0 ? c.left : nt - c.tile0;
-    const int ta = c.tile0, tb = c.tile0 + take;
-    it.row0 = 0; it.g = c.g; it.seq = seq;
+    if (c.phase >= 2) return false;
+    int g, first;
+    if (c.phase == 0) {
+        g = c.g_last; first = c.first_of_last; c.phase = 1;
+    } else {
+        if (c.g >= c.g_end) { c.phase = 2; return false; }
+        g = c.g; first = c.first_of_g;
+    }
+    const int seq = group_seq(p, g);
+    const int nt = sched_tiles(p, g);
+    if (g == c.g) { c.first_of_g += nt; ++c.g; }        // the in-order walk moves on
+    // tiles of this sequence inside the run
+    const int a = first > c.run_lo ? first : c.run_lo, b = (first + nt) < c.run_hi ? (first + nt) : c.run_hi;
+    const int ta = a - first, tb = b - first;
+    it.row0 = 0; it.g = g; it.seq = seq;
     it.lo = ta * T;
     it.hi = tb * T < seq ? tb * T : seq;
     if (it.hi < it.lo) it.hi = it.lo;
@@ -307,11 +321,8 @@ __device__ __forceinline__ bool cursor_next(Cursor &c, const FwdProblem &p, bool
     it.n_tiles = (it.n_sub + 3) / 4;
     it.fix = it.n_sub > 0 && it.t_begin + it.n_sub * SUB > seq;
     it.final_out = ta == 0 && tb == nt;
-    it.split = c.cid - c.first_of_g / c.quota;                 // piece index within the sequence
-    it.n_parts = (c.first_of_g + nt - 1) / c.quota - c.first_of_g / c.quota + 1;
-    c.left -= take;
-    if (tb == nt) { c.first_of_g += nt; ++c.g; c.tile0 = 0; }
-    else c.tile0 = tb;
+    it.split = c.cid - first / c.quota;                         // piece index within the sequence
+    it.n_parts = (first + nt - 1) / c.quota - first / c.quota + 1;
     return true;
 }
 
@@ -334,24 +345,21 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     int *s_rows = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(red) + RED_BYTES);   // [ROWS_CACHE]
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_rows + ROWS_CACHE);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
+    int *err_slot = reinterpret_cast<int *>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const bool leader = rank == 0;
-#ifdef FDMLA_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][0] = gtimer();
-    const bool trace_on = (int)(blockIdx.x >> 1) == g_trace_cluster;
-#endif
 
     // ---- the work list (identical in both CTAs of the pair and in every role) -----------
     const int cid = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-    const int err_now = *reinterpret_cast<volatile int *>(&g_tc_error);
-    const bool poisoned = err_now != 0 && err_now != ERR_PAGE;
+    if (threadIdx.x == 0) TL(0);
 
     // ---- set-up ------------------------------------------------------------------------
     if (threadIdx.x == 0) {
+        *err_slot = *reinterpret_cast<volatile int *>(&g_tc_error);
         mbar_init(BAR(B_QFULL), 1);
         mbar_init(BAR(B_PEER_QFULL), 1);
         mbar_init(BAR(B_QEMPTY), 1);
@@ -383,9 +391,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     cluster_sync_all();                      // the peer's barriers exist before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-#ifdef FDMLA_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][1] = gtimer();
-#endif
+    // Once any CTA has reported a failed wait the rest of the grid does no work.  The leader's thread 0 has read the
+    // flag once (before the barriers above); every thread of the pair takes that one value from the leader's shared
+    // memory, so that all roles of both CTAs walk the same item list even if the flag changes meanwhile.
+    const int err_now = (int)ld_shared_cluster_u32(map_to_cta(smem_u32(err_slot), 0));
+    const bool poisoned = err_now != 0 && err_now != ERR_PAGE;
+    if (threadIdx.x == 0) TL(1);
 
     // global row of the first key of sub-block s of an item (pool row for paged caches)
     auto sub_row = [&](const Item &it, int s, bool *bad_page) -> int {
@@ -413,13 +424,11 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             prefetch_tmap(&tmK);
             prefetch_tmap(&tmV);
         }
-#ifdef FDMLA_TRACE
-        int ptr_n = 0;
-#endif
         Cursor cur;
         cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
         Item it;
         for (int round = 0; ok && cursor_next(cur, p, poisoned, it); ++round) {
+            if (p.seqlens && p.seqlens[it.g] != it.seq) bad = true;      // a length outside [0, max_pages * page_size] was clamped
             if (it.n_tiles == 0) continue;
             // Q of the previous item is free once its last Q K^T has completed
             if (q_loads > 0) ok = ok && mbar_wait(BAR(B_QEMPTY), (q_loads - 1) & 1);
@@ -454,10 +463,6 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     else
                         ok = ok && mbar_wait(BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
                 }
-#ifdef FDMLA_TRACE
-                if (lane == 0 && round == 0) TRACE(0, ptr_n);
-                ++ptr_n;
-#endif
                 const int s0 = 4 * t + 2 * (int)rank;
                 const int present = (s0 + 1 < it.n_sub) ? 2 : (s0 < it.n_sub ? 1 : 0);
                 const int r0 = present > 0 ? row_of(s0) : 0, r1 = present > 1 ? row_of(s0 + 1) : 0;
@@ -480,10 +485,6 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     ok = ok && mbar_wait2(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
                 else if (us[1] >= 1)
                     ok = ok && mbar_wait(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
-#ifdef FDMLA_TRACE
-                if (lane == 0 && round == 0) TRACE(0, ptr_n);
-                ++ptr_n;
-#endif
                 const int s = 4 * t + q;
                 const int row = row_of(s);
                 if (elected) {
@@ -541,9 +542,6 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             uint32_t ph = 0;
             int tg0 = 0;                // tiles of the items before the current one
             int q_loads = 0, items_done = 0, fix_uses = 0;     // items_done: items that used the accumulator
-#ifdef FDMLA_TRACE
-            int ntr = 0;
-#endif
             Cursor cur;
             cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
             Item it;
@@ -574,20 +572,10 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     for (int i = 0; i < 3; ++i) take(sl[i], phs[i]);
                     if (g3 == 0) {
                         // S[b] was last read by the softmax of the tile two before
-                        DBG(0, tg * 100 + 10 + g3);
                         if (tg >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tg / 2) - 1) & 1);
                         tc_fence_after_sync();
                     }
-#ifdef FDMLA_TRACE
-                    if (lane == 0 && round == 0) TRACE(1, ntr);
-#endif
-                    DBG(0, tg * 100 + 20 + g3);
                     ok = ok && mbar_wait3(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1], BAR(B_FULL + sl[2]), phs[2]);
-                    DBG(0, tg * 100 + 30 + g3);
-#ifdef FDMLA_TRACE
-                    if (lane == 0 && round == 0) TRACE(2, ntr);
-                    ++ntr;
-#endif
                     if (elected) {
 #pragma unroll
                         for (int i = 0; i < 3; ++i) {
@@ -608,22 +596,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     int sl[2];
                     uint32_t phs[2];
                     for (int j = 0; j < 2; ++j) take(sl[j], phs[j]);
-#ifdef FDMLA_TRACE
-                    if (lane == 0 && round == 0) TRACE(1, ntr);
-#endif
-                    DBG(0, tg * 100 + 40 + q);
                     ok = ok && mbar_wait(BAR(B_PFULL + q), tg & 1);
-                    DBG(0, tg * 100 + 50 + q);
                     tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
-#ifdef FDMLA_TRACE
-                    if (lane == 0 && round == 0) TRACE(4, ntr);
-#endif
                     ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1]);
-                    DBG(0, tg * 100 + 60 + q);
-#ifdef FDMLA_TRACE
-                    if (lane == 0 && round == 0) TRACE(2, ntr);
-                    ++ntr;
-#endif
                     if (it.t_begin + (4 * t + q) * SUB + SUB > it.seq)
                         ok = ok && mbar_wait2(BAR(B_FIX), fix_uses & 1, BAR(B_FIX + 1), fix_uses & 1);
                     if (elected) {
@@ -633,7 +608,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                                       16, 128, idesc_pv, (t | q) != 0);
                             mma_commit_2cta(BAR(B_EMPTY + sl[j]), 3);
                         }
-                        if (USE_PEMPTY) mma_commit_2cta(BAR(B_PEMPTY + q), 3);    // this P quarter may be overwritten
+                        mma_commit_2cta(BAR(B_PEMPTY + q), 3);    // this P quarter may be overwritten
                         if (last) mma_commit_2cta(BAR(B_OREADY + (tg & 1)), 3);   // tile t folded into O
                     }
                 };
@@ -711,7 +686,6 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             const int rr = it.row0 + 64 * (int)rank + row;
             const bool row_ok = rr < p.R;
             const int lo = it.lo, hi = it.hi, seq = it.seq, n_tiles = it.n_tiles;
-            if (L == 0) TRACE(5, round * 4 + 0);
             int upper = lo;
             if (row_ok) {
                 long long vis = seq;
@@ -723,17 +697,37 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 if (upper < lo) upper = lo;
             }
             float m_true = -CUDART_INF_F, m_ref = -CUDART_INF_F, l_run = 0.f;   // l_run: this thread's key half only
+            // decode: the cache row this thread pulls into L2 for the first tile of the pair's NEXT item while it works
+            // on the last tile of this one (an item's first tile has no tile before it to do that)
+            const char *next_first_row = nullptr;
+            if (do_prefetch && PF_DIST > 0 && n_tiles > 0) {
+                Cursor peek = cur;
+                Item nxt;
+                while (cursor_next(peek, p, poisoned, nxt))
+                    if (nxt.n_tiles > 0) {
+                        const int s = 2 * (int)rank + half;
+                        bool bad_page = false;
+                        if (s < nxt.n_sub && nxt.t_begin + s * SUB + row < nxt.blk_hi) {
+                            const size_t r0 = (size_t)sub_row(nxt, s, &bad_page) + row;
+                            if (!bad_page) next_first_row = static_cast<const char *>(p.K) + r0 * (NQC * 128);
+                        }
+                        break;
+                    }
+            }
             for (int t = 0; t < n_tiles; ++t) {
                 const int tg = tg0 + t, b = tg & 1, tok0 = it.t_begin + t * T + 128 * half;
                 const uint32_t s_addr = tmem + lane_base + S_COL0 + b * S_COLS;
                 // after a failed wait the loop keeps running without further waits so that the
                 // named barriers below stay matched across the softmax threads
-                if (L == 0 && round == 0) TRACE(3, t * 8 + 0);
                 if (PF_DIST > 0 && do_prefetch) {
                     // While this thread would only wait for S: pull one cache row of a later tile into L2.
                     // The 128 softmax threads of the CTA cover the CTA's own 128 keys of that tile (the
                     // pair covers the tile), so the TMA copies issued PF_DIST tiles from now hit L2 and
                     // the ring only has to hide the L2 latency, not the HBM latency.
+                    if (t == n_tiles - 1 && next_first_row != nullptr) {
+#pragma unroll
+                        for (int c = 0; c < NQC; ++c) prefetch_l2(next_first_row + c * 128);
+                    }
                     for (int tp = (t == 0 ? 1 : t + PF_DIST); tp <= t + PF_DIST; ++tp) {
                         const int s = 4 * tp + 2 * (int)rank + half;
                         if (s < it.n_sub && it.t_begin + s * SUB + row < it.blk_hi) {
@@ -741,13 +735,13 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                             const char *src = static_cast<const char *>(p.K) + ((size_t)sub_row(it, s, &bad_page) + row) * (NQC * 128);
                             if (!bad_page) {
 #pragma unroll
-                                for (int c = 0; c < NQC; c += FDMLA_PF_STEP) prefetch_l2(src + c * 128);
+                                for (int c = 0; c < NQC; ++c) prefetch_l2(src + c * 128);
                             }
                         }
                     }
                 }
                 if (ok && !(ok = mbar_wait(BAR(B_SFULL + b), (tg / 2) & 1))) fail = ERR_SOFTMAX;
-                if (L == 0 && round == 0) TRACE(3, t * 8 + 1);
+                if (L == 0 && t == 0) TL(2 + 3 * round);
                 tc_fence_after_sync();
                 // pass 1: maximum of this thread's 128 keys (no per-key masking when all are visible)
                 const bool all_visible = tok0 >= lo && tok0 + 128 <= upper && sl2 > 0.f;
@@ -775,18 +769,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 // the row's other key half lives in the thread 64 lanes away
                 red[(tg & 1) * 128 + L] = tmax;
                 named_bar_sync(1, 128);
-                if (L == 0 && round == 0) TRACE(3, t * 8 + 2);
                 tmax = fmaxf(tmax, red[(tg & 1) * 128 + (L ^ 64)]);
                 const float m_new = fmaxf(m_true, tmax);
                 const bool need = m_new > m_ref + 8.f;
-                if (!USE_PEMPTY && t > 0) {
-                    // P*V of tile t-1 must be complete before its P is overwritten or O rescaled
-                    if (ok && !(ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1))) fail = ERR_SOFTMAX_RESCALE;
-                    tc_fence_after_sync();
-                }
                 if (__any_sync(0xffffffffu, need)) {
                     // O is rescaled: every P*V of tile t-1 must have been accumulated
-                    if (USE_PEMPTY && t > 0) {
+                    if (t > 0) {
                         if (ok && !(ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1))) fail = ERR_SOFTMAX_RESCALE;
                         tc_fence_after_sync();
                     }
@@ -810,7 +798,6 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     }
                 }
                 m_true = m_new;
-                if (L == 0 && round == 0) TRACE(3, t * 8 + 3);
                 // pass 2: P = 2^(s - m_ref), quarter by quarter (this half owns quarters 2*half, 2*half+1)
                 float lsum = 0.f;
 #pragma unroll 1
@@ -840,12 +827,9 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     }
                     const int quarter = 2 * half + (cc >> 1);
                     // the last P*V that read this quarter's previous contents is done
-                    if (USE_PEMPTY && !(cc & 1) && p_reads[cc >> 1] > 0 && ok &&
+                    if (!(cc & 1) && p_reads[cc >> 1] > 0 && ok &&
                         !(ok = mbar_wait(BAR(B_PEMPTY + quarter), (p_reads[cc >> 1] - 1) & 1))) {
                         fail = ERR_SOFTMAX_P;
-#ifdef FDMLA_TRACE
-                        if (row == 0) { g_dbg[blockIdx.x][2 + half] = tg * 100 + quarter; g_dbg[blockIdx.x][4 + half] = n_tiles; }
-#endif
                     }
                     uint8_t *prow = sP + quarter * P_Q + (row >> 3) * P_SBO + (row & 7) * 16 + (cc & 1) * 4 * 128;
 #pragma unroll
@@ -860,7 +844,6 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         // column of O, so no thread of either key half may still be rescaling its part of O.
                         if (cc == 1) named_bar_sync(1, 128);
                         else named_bar_sync(2 + half, 64);
-                        if (L == 0 && round == 0) TRACE(3, t * 8 + 4 + (cc >> 1));
                         if (row == 0) {
                             // (relaxed: the 64 writers have fenced their stores towards the async proxy and
                             // met at the named barrier; the arrival itself carries no data)
@@ -880,13 +863,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 tc_fence_after_sync();
             }
             tg0 += n_tiles;
-            if (L == 0) TRACE(5, round * 4 + 1);
+            if (L == 0) { TL(3 + 3 * round); TL_ITEM(round, n_tiles); }
             // row sum = both key halves
             named_bar_sync(1, 128);
             red[L] = l_run;
             named_bar_sync(1, 128);
             const float l_tot = l_run + red[L ^ 64];
-            if (L == 0 && round == 0) TRACE(5, 16);
             // ---- epilogue: thread L writes row `row`, d_v columns [256*half, 256*half + 256) ----
             const bool have = ok && n_tiles > 0 && l_tot > 0.f;
             const float inv = have ? 1.f / l_tot : 0.f;
@@ -894,7 +876,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             const size_t grow = (size_t)it.g * p.R + (row_ok ? rr : 0);
             const size_t prow_idx = (size_t)it.split * p.G * p.R + grow;
             const int col0 = 256 * half;
-            if (FDMLA_TMA_EPI && DECODE && final_out && it.rows_here == 128) {
+            if (DECODE && final_out && it.rows_here == 128) {
                 // bf16 result of a full decode tile (prefill measured 2 % faster with the plain row stores
                 // below): staged in the (now idle) P buffer as 64-row x 64-column boxes in
                 // the 128-byte swizzle and written by TMA tensor stores.  Each key-half group of 64 threads
@@ -935,10 +917,8 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         tma_store_2d(&tmO, col0 + 64 * bx, y, smem_u32(box));
                         bulk_commit();
                     }
-                    if (L == 0 && round == 0) TRACE(5, 17 + bx);
                 }
                 if (row == 0) bulk_wait_read<0>();       // before the next item's P is written (barrier below)
-                if (L == 0 && round == 0) TRACE(5, 21);
             } else {
 #pragma unroll 1
                 for (int cc = 0; cc < O_COLS / 32; ++cc) {
@@ -980,8 +960,8 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 const float l_out = have ? l_tot * fast_exp2(m_ref - m_true) : 0.f;
                 if (final_out) { p.m[grow] = m_out; p.l[grow] = l_out; }
                 else { p.m_part[prow_idx] = m_out; p.l_part[prow_idx] = l_out; }
-                if (it.n_parts > 0) {
-                    // balanced schedule: tell the merge which slabs of this row hold something
+                if (it.n_parts > 0 && p.tickets == nullptr) {
+                    // balanced schedule with the merge kernel: tell it which slabs of this row hold something
                     const size_t slab = (size_t)p.G * p.R;
                     if (final_out) p.l_part[grow] = -1.f;                  // "O, m, l already final"
                     else if (it.split == 0)
@@ -991,12 +971,65 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         }
                 }
             }
+            if (DECODE && it.n_parts > 1 && p.tickets != nullptr) {
+                // Balanced schedule, merge in this kernel: this CTA has written its 64 rows of one piece of a cut
+                // sequence.  It then draws a ticket for (sequence, CTA rank); the CTA that draws the last one finds
+                // every piece of these rows in memory and merges them into O, m, l (the log-sum-exp rule of the merge
+                // kernel, csrc/attention/fa2_fwd.cu:93-111 of the reference across partial results).  Nobody waits for
+                // anybody.  The tickets start at zero: the launcher clears them before every launch.
+                __threadfence();                                   // this thread's partial rows are visible device-wide
+                named_bar_sync(1, 128);
+                if (L == 0) reinterpret_cast<unsigned int *>(red)[0] = atomicAdd(&p.tickets[2 * it.g + (int)rank], 1u);
+                named_bar_sync(1, 128);
+                const bool last_piece = reinterpret_cast<volatile unsigned int *>(red)[0] == (unsigned)(it.n_parts - 1);
+                if (last_piece && row_ok) {
+                    __threadfence();
+                    const size_t slab = (size_t)p.G * p.R;
+                    float mx = -CUDART_INF_F;
+                    for (int k = 0; k < it.n_parts; ++k)
+                        if (__ldcg(p.l_part + k * slab + grow) > 0.f) mx = fmaxf(mx, __ldcg(p.m_part + k * slab + grow));
+                    float ls = 0.f;
+                    for (int k = 0; k < it.n_parts; ++k) {
+                        const float lk = __ldcg(p.l_part + k * slab + grow);
+                        if (lk > 0.f) ls += lk * __expf(__ldcg(p.m_part + k * slab + grow) - mx);
+                    }
+                    const float inv_l = ls > 0.f ? 1.f / ls : 0.f;
+                    __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + grow * p.d_v + col0;
+#pragma unroll 1
+                    for (int cc = 0; cc < O_COLS / 16; ++cc) {
+                        float acc[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                        for (int k = 0; k < it.n_parts; ++k) {
+                            const float lk = __ldcg(p.l_part + k * slab + grow);
+                            if (lk > 0.f) {
+                                const float w = lk * __expf(__ldcg(p.m_part + k * slab + grow) - mx) * inv_l;
+                                const float4 *src = reinterpret_cast<const float4 *>(p.O_part + (k * slab + grow) * p.d_v + col0 + cc * 16);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float4 v = __ldcg(src + j);
+                                    acc[4 * j] = fmaf(w, v.x, acc[4 * j]); acc[4 * j + 1] = fmaf(w, v.y, acc[4 * j + 1]);
+                                    acc[4 * j + 2] = fmaf(w, v.z, acc[4 * j + 2]); acc[4 * j + 3] = fmaf(w, v.w, acc[4 * j + 3]);
+                                }
+                            }
+                        }
+                        uint32_t w8[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+                            w8[e] = *reinterpret_cast<uint32_t *>(&h);
+                        }
+                        st_global_v8(dst + cc * 16, w8);
+                    }
+                    if (half == 0) { p.m[grow] = mx; p.l[grow] = ls; }
+                }
+            }
             // this CTA's softmax warps have read O out of tensor memory: the next item may overwrite it
             // (an empty item never touched the accumulator and signals nothing)
             tc_fence_before_sync();
             named_bar_sync(1, 128);
             if (L == 0 && n_tiles > 0) mbar_arrive_cluster_relaxed(ofree_leader);
-            if (L == 0) TRACE(5, round * 4 + 2);
+            if (L == 0) TL(4 + 3 * round);
         }
         if (!ok) atomicCAS(&g_tc_error, 0, fail ? fail : ERR_SOFTMAX);
     }
@@ -1004,18 +1037,14 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     // ---- teardown: neither CTA may leave while the pair can still touch its memory --------
     tc_fence_before_sync();
     __syncthreads();
-#ifdef FDMLA_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][2] = gtimer();
-#endif
+    if (threadIdx.x == 0) TL(30);
     __syncwarp();
     cluster_sync_all();
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc_2cta(tmem, TMEM_COLS);
     }
-#ifdef FDMLA_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_span[blockIdx.x][3] = gtimer();
-#endif
+    if (threadIdx.x == 0) TL(31);
 }
 
 }  // namespace tc2
@@ -1023,30 +1052,15 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
 // --------------------------------------------------------------------------------------
 // Host side
 // --------------------------------------------------------------------------------------
-#ifdef FDMLA_TRACE
-extern "C" int fdmla_trace_spans(unsigned long long *dst) {
-    return cudaMemcpyFromSymbol(dst, tc2::g_trace_span, sizeof(unsigned long long) * 256 * 4) == cudaSuccess ? 0 : -1;
-}
-extern "C" int fdmla_trace_dbg(int *dst) {
-    return cudaMemcpyFromSymbol(dst, tc2::g_dbg, sizeof(int) * 160 * 8) == cudaSuccess ? 0 : -1;
-}
-extern "C" int fdmla_trace_select(int cluster) {
-    return cudaMemcpyToSymbol(tc2::g_trace_cluster, &cluster, sizeof(int)) == cudaSuccess ? 0 : -1;
-}
-extern "C" int fdmla_trace_fetch(long long *dst, int max_elems) {
-    const int n = 2 * 6 * tc2::TR_N;
-    if (max_elems < n) return -n;
-    return cudaMemcpyFromSymbol(dst, tc2::g_trace, sizeof(long long) * n) == cudaSuccess ? n : -1;
-}
-#endif
 
 namespace tc2 {
 // CTA pairs of fwd_tc2_kernel that are resident at the same time on the current device (cached per device).
 static int resident_clusters() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
-    if (cached[dev] > 0) return cached[dev];
+    const int have = cached[dev].load(std::memory_order_relaxed);
+    if (have > 0) return have;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148);
     cfg.blockDim = dim3(THREADS);
@@ -1057,16 +1071,19 @@ static int resident_clusters() {
     cfg.attrs = &at;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, fwd_tc2_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaFuncSetAttribute(fwd_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, fwd_tc2_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
         cudaGetLastError();
         int sms = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) return -1;
         n = sms / 2;
     }
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
     return n;
 }
 }  // namespace tc2
+
+int fwd_tensor2_resident_clusters() { return tc2::resident_clusters(); }
 
 bool fwd_tensor2_supported(const FwdProblem &p, int dtype) {
     if (dtype != FDMLA_BF16) return false;
@@ -1088,6 +1105,7 @@ int launch_fwd_tensor2(const FwdProblem &p_in, cudaStream_t stream) {
                        p.kv_end >= 0))
         p.balanced = 0;
     if (!p.balanced && p.num_splits > 1) p.O = nullptr;      // equal splits: partials only
+    if (!p.balanced || p.Sq != 1) p.tickets = nullptr;
     CUtensorMap tmQ, tmK, tmV, tmO;
     const long long kv_rows = p.page_table ? (long long)p.num_pages * p.page_size : (long long)p.G * p.Skv;
     if (!make_tensor_map_bf16_chunked(&tmQ, p.Q, (long long)p.G * p.R, p.d_qk, 64, 9)) return FDMLA_ERR_CUDA;
@@ -1107,6 +1125,26 @@ int launch_fwd_tensor2(const FwdProblem &p_in, cudaStream_t stream) {
     if (resident <= 0) return FDMLA_ERR_CUDA;
     const int n_clusters = (p.balanced || n_items >= resident) ? resident : (int)n_items;
     kern<<<dim3(2 * n_clusters), tc2::THREADS, tc2::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmO);
+#ifdef FDMLA_TIMELINE
+    if (const char *path = getenv("FDMLA_TIMELINE_FILE")) {
+        // one record per launch: n_clusters, decode flag, then the stamps and the tiles per item of every pair
+        static unsigned long long stamps[tc2::TL_CLUSTERS][tc2::TL_SLOTS];
+        static int tiles[tc2::TL_CLUSTERS][tc2::TL_ITEMS];
+        if (cudaStreamSynchronize(stream) == cudaSuccess &&
+            cudaMemcpyFromSymbol(stamps, tc2::g_timeline, sizeof(stamps)) == cudaSuccess &&
+            cudaMemcpyFromSymbol(tiles, tc2::g_timeline_tiles, sizeof(tiles)) == cudaSuccess) {
+            if (FILE *f = fopen(path, "ab")) {
+                const int head[4] = {n_clusters, decode ? 1 : 0, tc2::TL_SLOTS, tc2::TL_ITEMS};
+                fwrite(head, sizeof(head), 1, f);
+                fwrite(stamps, sizeof(stamps), 1, f);
+                fwrite(tiles, sizeof(tiles), 1, f);
+                fclose(f);
+            }
+            static const unsigned long long zero[tc2::TL_CLUSTERS][tc2::TL_SLOTS] = {};
+            cudaMemcpyToSymbol(tc2::g_timeline, zero, sizeof(zero));
+        }
+    }
+#endif
     return check_launch();
 }
 

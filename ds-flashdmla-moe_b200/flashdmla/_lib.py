@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libflashdmla.so")
+# FLASHDMLA_LIB names another build of the library (a development build with timeline stamps, say)
+LIB_PATH = os.environ.get("FLASHDMLA_LIB") or os.path.join(_HERE, "libflashdmla.so")
 
 F32, BF16 = 0, 1
 BACKEND_AUTO, BACKEND_PORTABLE, BACKEND_TENSOR = 0, 1, 2
@@ -31,10 +32,11 @@ SIGNATURES = {
     "fdmla_fwd_on_the_fly": (_i, [_vp] * 9 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),
     "fdmla_decode_paged": (_i, [_vp] * 10 + [_i] * 10 + [_f, _i, _vp]),
     "fdmla_decode_suggest_splits": (_i, [_i] * 7),
-    "fdmla_set_decode_merge": (None, [_i]),
+    "fdmla_decode_plan": (_i, [_i] * 8 + [_vp, _vp]),
     "fdmla_decode_paged_noalloc_max_rows": (_sz, [_i]),
     "fdmla_decode_paged_noalloc": (_i, [_vp] * 7 + [_i] * 8 + [_f, _i, _vp]),
     "fdmla_merge_lse": (_i, [_vp] * 6 + [_ll, _i, _i, _i, _vp]),
+    "fdmla_merge_lse_strided": (_i, [_vp] * 6 + [_ll, _i, _i, _ll, _ll, _i, _vp]),
     "fdmla_bwd_on_the_fly_workspace_bytes": (_sz, [_i] * 7),
     "fdmla_bwd_on_the_fly": (_i, [_vp] * 15 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),
     "fdmla_bwd_cache_latent_workspace_bytes": (_sz, [_i] * 7),
@@ -85,11 +87,6 @@ def set_backend(backend: int) -> None:
 def set_single_cta(on: bool) -> None:
     """Keep 576/512 shapes on the single-CTA tcgen05 kernel (A/B measurements, tests)."""
     check(lib().fdmla_set_single_cta(int(bool(on))), "fdmla_set_single_cta")
-
-
-def set_decode_merge(on: bool) -> None:
-    """Measurement switch: leave the decode partials unmerged so the attention kernel can be timed alone."""
-    lib().fdmla_set_decode_merge(int(bool(on)))
 
 
 def last_kernel() -> str:

@@ -204,7 +204,7 @@ def suggest_splits(B: int, H: int, max_seqlen: int, d_qk: int, d_v: int, page_si
 
 def flash_dmla_paged_decode(Q, kv_pool, page_table, seqlens, d_v, scale=None, num_splits=None,
                             kv_begin=0, kv_end=-1, workspace: Optional[DecodeWorkspace] = None,
-                            max_seqlen: Optional[int] = None, partial_only=False):
+                            max_seqlen: Optional[int] = None, partial_only=False, out=None):
     """One decode step over a paged latent KV cache.
 
     Q [B,H,d_qk] or [B,H,1,d_qk]; kv_pool [num_pages,page_size,d_qk];
@@ -212,6 +212,9 @@ def flash_dmla_paged_decode(Q, kv_pool, page_table, seqlens, d_v, scale=None, nu
     Returns O [B,H,(1,)d_v] (Q's dtype), m, l [B,H,(1)] fp32.  With
     partial_only=True returns the fp32 partials (O_part [S,B,H,d_v], m_part,
     l_part [S,B,H]) of the attended window [kv_begin, kv_end) instead.
+    out = (O, m, l) or, with partial_only, (O_part, m_part, l_part): contiguous
+    tensors of those shapes to write into instead of fresh ones (a caller that
+    keeps its results in one staging or message buffer passes views of it).
     """
     _need_cuda(Q, kv_pool, page_table, seqlens)
     _same_dtype(Q, kv_pool)
@@ -241,7 +244,18 @@ def flash_dmla_paged_decode(Q, kv_pool, page_table, seqlens, d_v, scale=None, nu
     num_splits = max(1, int(num_splits))
     dev = Q.device
     O_part = m_part = l_part = None
-    if num_splits > 1 or partial_only:
+    if out is not None:
+        want = ([(num_splits, B, H, d_v), (num_splits, B, H), (num_splits, B, H)] if partial_only
+                else [(B, H, d_v), (B, H), (B, H)])
+        dts = [torch.float32 if partial_only else Q.dtype, torch.float32, torch.float32]
+        if len(out) != 3:
+            raise FlashDMLAError("out must be a triple of tensors")
+        for t, shp, dt in zip(out, want, dts):
+            if tuple(t.shape) != shp or t.dtype != dt or not t.is_contiguous() or t.device != dev:
+                raise FlashDMLAError(f"out tensor must be contiguous {shp} {dt} on {dev}")
+    if partial_only and out is not None:
+        O_part, m_part, l_part = out
+    elif num_splits > 1 or partial_only:
         if workspace is not None and not partial_only:
             O_part, m_part, l_part = workspace.get(num_splits, B, H, d_v, dev)
         else:
@@ -249,7 +263,9 @@ def flash_dmla_paged_decode(Q, kv_pool, page_table, seqlens, d_v, scale=None, nu
             m_part = torch.empty(num_splits * B * H, dtype=torch.float32, device=dev)
             l_part = torch.empty(num_splits * B * H, dtype=torch.float32, device=dev)
     O = m = l = None
-    if not partial_only:
+    if not partial_only and out is not None:
+        O, m, l = out
+    elif not partial_only:
         O = torch.empty(B, H, d_v, dtype=Q.dtype, device=dev)
         m = torch.empty(B, H, dtype=torch.float32, device=dev)
         l = torch.empty(B, H, dtype=torch.float32, device=dev)
@@ -260,32 +276,55 @@ def flash_dmla_paged_decode(Q, kv_pool, page_table, seqlens, d_v, scale=None, nu
             num_pages, num_splits, int(kv_begin), int(kv_end), float(scale), code, _stream(Q)),
             "fdmla_decode_paged")
     if partial_only:
-        return (O_part[: num_splits * B * H * d_v].view(num_splits, B, H, d_v),
-                m_part[: num_splits * B * H].view(num_splits, B, H),
-                l_part[: num_splits * B * H].view(num_splits, B, H))
+        return (O_part.reshape(-1)[: num_splits * B * H * d_v].view(num_splits, B, H, d_v),
+                m_part.reshape(-1)[: num_splits * B * H].view(num_splits, B, H),
+                l_part.reshape(-1)[: num_splits * B * H].view(num_splits, B, H))
     if squeeze:
         return O[:, :, None, :], m[:, :, None], l[:, :, None]
     return O, m, l
 
 
-def merge_partials(O_p, m_p, l_p, out_dtype: Optional[torch.dtype] = None):
-    """LSE merge over the leading dim: O_p [P,...,d_v] fp32, m_p,l_p [P,...] fp32."""
+def _part_stride(t: torch.Tensor, inner: int) -> Optional[int]:
+    """Stride between parts if everything behind the leading dim is dense (inner elements), else None."""
+    if t.shape[0] == 1:
+        return inner
+    return t.stride(0) if t[0].is_contiguous() and t.stride(0) >= inner else None
+
+
+def merge_partials(O_p, m_p, l_p, out_dtype: Optional[torch.dtype] = None, out=None):
+    """LSE merge over the leading dim: O_p [P,...,d_v] fp32, m_p,l_p [P,...] fp32.
+
+    The parts need not sit back to back: any layout in which every part is dense
+    in itself and the parts are a fixed number of elements apart is merged in
+    place (views into an all-gathered buffer of per-rank messages, say).
+    out = (O, m, l) writes into given contiguous tensors.
+    """
     _need_cuda(O_p, m_p, l_p)
     if O_p.dtype != torch.float32 or m_p.dtype != torch.float32 or l_p.dtype != torch.float32:
         raise FlashDMLAError("partials must be float32")
-    O_p, m_p, l_p = O_p.contiguous(), m_p.contiguous(), l_p.contiguous()
     P, d_v = O_p.shape[0], O_p.shape[-1]
     rows = m_p[0].numel()
-    out_dtype = out_dtype or torch.float32
-    O = torch.empty(O_p.shape[1:], dtype=out_dtype, device=O_p.device)
-    m = torch.empty(m_p.shape[1:], dtype=torch.float32, device=O_p.device)
-    l = torch.empty(m_p.shape[1:], dtype=torch.float32, device=O_p.device)
-    code = _lib.F32 if out_dtype == torch.float32 else _lib.BF16
+    so, sm, sl = _part_stride(O_p, rows * d_v), _part_stride(m_p, rows), _part_stride(l_p, rows)
+    if so is None or sm is None or sl is None or sm != sl:
+        O_p, m_p, l_p = O_p.contiguous(), m_p.contiguous(), l_p.contiguous()
+        so, sm = rows * d_v, rows
+    out_dtype = out_dtype or (out[0].dtype if out is not None else torch.float32)
     if out_dtype not in (torch.float32, torch.bfloat16):
         raise FlashDMLAError("out_dtype must be float32 or bfloat16")
+    if out is not None:
+        O, m, l = out
+        if (tuple(O.shape) != tuple(O_p.shape[1:]) or O.dtype != out_dtype or not O.is_contiguous()
+                or m.numel() != rows or l.numel() != rows or not m.is_contiguous() or not l.is_contiguous()
+                or m.dtype != torch.float32 or l.dtype != torch.float32):
+            raise FlashDMLAError("out tensors do not match the merged result")
+    else:
+        O = torch.empty(O_p.shape[1:], dtype=out_dtype, device=O_p.device)
+        m = torch.empty(m_p.shape[1:], dtype=torch.float32, device=O_p.device)
+        l = torch.empty(m_p.shape[1:], dtype=torch.float32, device=O_p.device)
+    code = _lib.F32 if out_dtype == torch.float32 else _lib.BF16
     with torch.cuda.device(O_p.device):
-        check(_lib.lib().fdmla_merge_lse(_ptr(O_p), _ptr(m_p), _ptr(l_p), _ptr(O), _ptr(m), _ptr(l),
-                                         rows, d_v, P, code, _stream(O_p)), "fdmla_merge_lse")
+        check(_lib.lib().fdmla_merge_lse_strided(_ptr(O_p), _ptr(m_p), _ptr(l_p), _ptr(O), _ptr(m), _ptr(l),
+                                                 rows, d_v, P, so, sm, code, _stream(O_p)), "fdmla_merge_lse_strided")
     return O, m, l
 
 

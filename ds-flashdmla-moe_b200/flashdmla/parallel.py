@@ -47,14 +47,37 @@ def split_sequence_pages(seqlens: List[int], page_size: int, world: int, rank: i
     return out
 
 
+# One rank's partial result travels as ONE fp32 message laid out in blocks,
+#   [ O (rows x d_v) | m (rows) | l (rows) ],
+# so that the decode (or the local merge) writes its three outputs straight into the message and the
+# receiver merges the gathered messages where they lie, as strided parts: nothing is packed or unpacked.
+def message_views(buf: torch.Tensor, lead: Tuple[int, ...], d_v: int):
+    """Views (O [*lead, d_v], m [*lead], l [*lead]) of one message, or of a [W, n] stack of messages
+    ([W, *lead, d_v], [W, *lead], [W, *lead]; the parts are then n elements apart)."""
+    rows = 1
+    for x in lead:
+        rows *= int(x)
+    n = rows * (d_v + 2)
+    if buf.dim() == 1:
+        if buf.numel() != n:
+            raise ValueError("message size does not match its shape")
+        return (buf[: rows * d_v].view(*lead, d_v), buf[rows * d_v: rows * d_v + rows].view(*lead),
+                buf[rows * d_v + rows:].view(*lead))
+    W = buf.shape[0]
+    if buf.dim() != 2 or buf.shape[1] != n:
+        raise ValueError("expected a [world, message] stack")
+    return (buf[:, : rows * d_v].unflatten(1, (*lead, d_v)), buf[:, rows * d_v: rows * d_v + rows].unflatten(1, lead),
+            buf[:, rows * d_v + rows:].unflatten(1, lead))
+
+
 def pack_partial(O: torch.Tensor, m: torch.Tensor, l: torch.Tensor) -> torch.Tensor:
-    """[..., d_v] + [...] + [...] -> one [..., d_v + 2] fp32 message."""
-    return torch.cat([O.float(), m.float()[..., None], l.float()[..., None]], dim=-1).contiguous()
+    """(O [..., d_v], m [...], l [...]) -> one message (a copy; the CUDA path writes into message_views instead)."""
+    return torch.cat([O.float().reshape(-1), m.float().reshape(-1), l.float().reshape(-1)])
 
 
-def unpack_partials(buf: torch.Tensor):
-    """[W, ..., d_v + 2] -> O_p [W, ..., d_v], m_p, l_p [W, ...] (contiguous)."""
-    return buf[..., :-2].contiguous(), buf[..., -2].contiguous(), buf[..., -1].contiguous()
+def unpack_partials(buf: torch.Tensor, lead: Tuple[int, ...], d_v: int):
+    """[W, n] stack of messages -> O_p [W, *lead, d_v], m_p, l_p [W, *lead] (views)."""
+    return message_views(buf, tuple(lead), d_v)
 
 
 class PartialCheckError(RuntimeError):
@@ -77,35 +100,54 @@ def sequence_parallel_decode(Q, local_pool, local_page_table, local_seqlens, d_v
                              group: Optional[dist.ProcessGroup] = None, out_dtype=None,
                              num_splits: Optional[int] = None,
                              decode_fn: Optional[Callable] = None,
-                             merge_fn: Optional[Callable] = None, validate: bool = False):
+                             merge_fn: Optional[Callable] = None, validate: bool = False,
+                             workspace=None, timing_events=None):
     """Decode when every rank holds one slice of each sequence's paged cache.
 
     Q [B,H,d_qk] is replicated; local_* describe this rank's slice only.
     Returns the merged O [B,H,d_v], m, l [B,H] on every rank.
     decode_fn / merge_fn default to the CUDA operators; tests of the host-side
-    protocol may inject CPU stand-ins.
+    protocol may inject CPU stand-ins.  workspace: a flashdmla.DecodeWorkspace to
+    reuse across steps.  timing_events: four CUDA events recorded on the current
+    stream at the start, after the local partial, after the all-gather and after
+    the merge (measurement only).
     """
-    if decode_fn is None or merge_fn is None:
-        from . import ops
-        if decode_fn is None:
-            def decode_fn(Q, pool, table, lens, d_v, scale):
-                Op, mp, lp = ops.flash_dmla_paged_decode(Q, pool, table, lens, d_v, scale,
-                                                         num_splits=num_splits, partial_only=True)
-                if Op.shape[0] == 1:
-                    return Op[0], mp[0], lp[0]
-                return ops.merge_partials(Op, mp, lp, torch.float32)
-        if merge_fn is None:
-            merge_fn = ops.merge_partials
-    O_loc, m_loc, l_loc = decode_fn(Q, local_pool, local_page_table, local_seqlens, d_v, scale)
-    msg = pack_partial(O_loc, m_loc, l_loc)
+    B, H = Q.shape[0], Q.shape[1]
     world = dist.get_world_size(group)
-    flat = torch.empty((world * msg.shape[0],) + tuple(msg.shape[1:]), dtype=msg.dtype, device=msg.device)
-    dist.all_gather_into_tensor(flat, msg, group=group)      # concatenated along dim 0, rank-major
-    gathered = flat.view((world,) + tuple(msg.shape))
-    O_p, m_p, l_p = unpack_partials(gathered)
+    n = B * H * (d_v + 2)
+    rec = (lambda i: timing_events[i].record()) if timing_events is not None else (lambda i: None)
+    rec(0)
+    msg = torch.empty(n, dtype=torch.float32, device=Q.device)
+    mO, mm, ml = message_views(msg, (B, H), d_v)
+    if decode_fn is None:
+        from . import ops
+        splits = num_splits
+        if splits is None:
+            span = max(int(local_page_table.shape[1]) * int(local_pool.shape[1]), 1)
+            splits = ops.suggest_splits(B, H, span, Q.shape[-1], d_v, int(local_pool.shape[1]), Q.dtype)
+        if splits == 1:      # the attention kernel writes the message itself
+            ops.flash_dmla_paged_decode(Q, local_pool, local_page_table, local_seqlens, d_v, scale, num_splits=1,
+                                        partial_only=True, out=(mO[None], mm[None], ml[None]))
+        else:                # split-KV partials, merged (in fp32) into the message
+            Op, mp, lp = ops.flash_dmla_paged_decode(Q, local_pool, local_page_table, local_seqlens, d_v, scale,
+                                                     num_splits=splits, partial_only=True)
+            ops.merge_partials(Op, mp, lp, torch.float32, out=(mO, mm, ml))
+    else:
+        O_loc, m_loc, l_loc = decode_fn(Q, local_pool, local_page_table, local_seqlens, d_v, scale)
+        mO.copy_(O_loc); mm.copy_(m_loc); ml.copy_(l_loc)
+    if merge_fn is None:
+        from . import ops
+        merge_fn = ops.merge_partials
+    rec(1)
+    flat = torch.empty(world * n, dtype=torch.float32, device=Q.device)
+    dist.all_gather_into_tensor(flat, msg, group=group)      # rank-major
+    rec(2)
+    O_p, m_p, l_p = message_views(flat.view(world, n), (B, H), d_v)
     if validate:          # synchronises; meant for debugging and for the failure-detection tests
         check_partials(O_p, m_p, l_p)
-    return merge_fn(O_p, m_p, l_p, out_dtype or Q.dtype)
+    res = merge_fn(O_p, m_p, l_p, out_dtype or Q.dtype)
+    rec(3)
+    return res
 
 
 # --------------------------------------------------------------------------- #

@@ -70,10 +70,17 @@ int fdmla_set_single_cta(int on);
 const char *fdmla_last_kernel(void);
 
 /* Device-side error flag of the tensor-core kernels on the current device:
- * 0 = none, 1..3 = a bounded wait inside a kernel gave up (producer, MMA,
- * softmax role), 4 = a page id outside [0, num_pages) was read from a page
- * table.  Synchronises the device; reset != 0 clears the flag.  Returns -1 if
- * the flag cannot be read.  No reference counterpart. */
+ * 0 = none; 1..3 and 11..17 = a bounded wait inside a kernel gave up (which role
+ * and which wait); 4 = a page id outside [0, num_pages) was read from a page
+ * table, or a sequence length outside [0, max_pages * page_size] was clamped.
+ * Synchronises the device; reset != 0 clears the flag.  Returns -1 if the flag
+ * cannot be read.
+ * The flag is sticky.  After a time-out code every later tensor-core launch on
+ * that device does no work at all (it writes O = 0, l = 0, m = -inf) while the
+ * C call still returns FDMLA_OK, until the flag is cleared with reset != 0: a
+ * caller that cannot afford silent empty results polls the flag, e.g. once per
+ * step, and resets it after handling the failure.  Code 4 does not stop later
+ * launches.  No reference counterpart. */
 int fdmla_device_error_flag(int reset);
 
 /*
@@ -125,11 +132,17 @@ int fdmla_fwd_on_the_fly(const void *Q, const void *K, const void *V,
  *   If O is NULL only the partials are produced, exactly as described (piece s
  *   of every sequence in slab s).  When O is given, the scratch contents after
  *   the call are unspecified: with num_splits >= 2, the whole key range and
- *   H <= 128 the tcgen05 kernel treats the slabs as room to cut sequences and
- *   deals the 256-key tiles of all sequences out to the SMs in equal contiguous
- *   runs; a sequence is cut at most num_splits - 1 times, uncut sequences are
- *   written to O directly and the merge touches only the cut ones.
- *   Every page id read from page_table must be in [0, num_pages).
+ *   2 <= H <= 128 the tcgen05 kernel may treat the slabs as room to cut sequences
+ *   and deal the 256-key tiles of all sequences out to the SMs in equal
+ *   contiguous runs; uncut sequences are written to O directly.  A cut sequence
+ *   is merged either by a merge kernel (at most num_splits pieces) or, when few
+ *   pieces suffice, inside the attention kernel by the thread blocks that finish
+ *   its last piece (at most min(num_splits - 1, 4) pieces; the first 2 B words of
+ *   the last slab of l_part then serve as arrival counters, which the call clears
+ *   with a memset on `stream` before the launch).
+ *   Every page id read from page_table must be in [0, num_pages) and every
+ *   seqlens[b] in [0, max_pages * page_size]; a length outside is clamped and
+ *   reported through fdmla_device_error_flag (code 4).
  * The paged cache is the "KV-cache" of README.md:15; per (b, h) the math is
  * that of vanilla_attn_forward (vanallia_attn.cu:85-99) on the gathered rows.
  */
@@ -146,10 +159,18 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool,
 int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,
                                 int page_size, int dtype);
 
-/* Measurement switch: with on == 0, fdmla_decode_paged leaves the partials
- * unmerged (O, m, l are then incomplete), so that the attention kernel can be
- * timed alone.  Default 1.  No reference counterpart. */
-void fdmla_set_decode_merge(int on);
+/* How fdmla_decode_paged would run a problem for which a final result is wanted
+ * over the whole key range: 0 = every sequence in num_splits equal pieces (or a
+ * kernel other than the 2-CTA tensor kernel), 1 = balanced runs of 256-key tiles
+ * with the merge kernel, 2 = balanced runs merged inside the attention kernel.
+ * For 1 and 2, *quota_min receives the least number of tiles a run holds (it
+ * bounds the pieces a sequence is cut into) and *units the number of runs (CTA
+ * pairs resident on the current device).  A run holds
+ * max(ceil(total tiles / units), quota_min) tiles.  Negative: invalid argument.
+ * No reference counterpart. */
+int fdmla_decode_plan(int B, int H, int d_qk, int d_v, int page_size,
+                      int max_pages, int num_splits, int dtype, int *quota_min,
+                      int *units);
 
 /*
  * fdmla_decode_paged for callers that cannot allocate device memory.  It has no counterpart
@@ -167,7 +188,8 @@ void fdmla_set_decode_merge(int on);
  *   - The first call on a device looks up the array's device address; make that first call
  *     outside any stream capture.
  *   - Every call on a device shares the one array and it keeps the previous call's contents.
- *     Nothing in it has to be cleared (each call overwrites every slot it later reads), but
+ *     The caller clears nothing (each call overwrites every slot it later reads and zeroes the
+ *     few counters that must start at zero with a memset on `stream`), but
  *     two calls that overlap on the GPU (different streams, or different host threads) race
  *     on it: serialise them, or use fdmla_decode_paged with separate buffers.
  *   - Each GPU that loads the library holds the 32 MiB until the process exits.
@@ -191,6 +213,18 @@ int fdmla_merge_lse(const float *O_part, const float *m_part,
                     const float *l_part, void *O, float *m, float *l,
                     long long rows, int d_v, int num_parts, int out_dtype,
                     void *stream);
+
+/* The same merge over partials that are not stored back to back: part p of
+ * O_part starts part_stride_o floats after part p - 1 (>= rows * d_v), part p of
+ * m_part / l_part part_stride_ml floats after part p - 1 (>= rows).  This is the
+ * layout of all-gathered messages that each hold one rank's O, m and l one after
+ * the other (the exchange step that replaces the host all-gather of
+ * csrc/attention/fa2_fwd_mpi.cu:65-74). */
+int fdmla_merge_lse_strided(const float *O_part, const float *m_part,
+                            const float *l_part, void *O, float *m, float *l,
+                            long long rows, int d_v, int num_parts,
+                            long long part_stride_o, long long part_stride_ml,
+                            int out_dtype, void *stream);
 
 /*
  * On-the-fly DMLA backward.  Inputs of the forward plus its outputs O, m, l
@@ -277,7 +311,8 @@ int fdmla_moe_route_topk(const float *logits, int32_t *idx, float *w, int T,
  * padded != 0: every expert owns `capacity` rows (offsets[e] = e * capacity),
  * so that the packed rows form an [E, capacity, d] batch for a batched GEMM;
  * rows past an expert's count hold nothing and no assignment points at them
- * (perm then has E * capacity entries, those of unused rows are unwritten).
+ * (perm then has E * capacity entries, those of unused rows are -1 and
+ * fdmla_moe_gather writes zeros for them).
  */
 size_t fdmla_moe_pack_workspace_bytes(int T, int k, int E);
 int fdmla_moe_pack(const int32_t *idx, int32_t *pos, int32_t *perm,

@@ -33,9 +33,16 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
-def build_ref(reference: str = "/root/reference") -> str | None:
+def reference_dir() -> str:
+    """Checkout of the reference project: $FDMLA_REFERENCE_DIR, else a directory `reference` beside this
+    repository."""
+    return os.environ.get("FDMLA_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def build_ref(reference: str | None = None) -> str | None:
     """Compile the reference's own forward kernels where the checkout exists."""
-    if not os.path.isdir(reference):
+    reference = reference or reference_dir()
+    if not os.path.isdir(os.path.join(reference, "csrc", "attention")):
         return _REF_PATH if os.path.exists(_REF_PATH) else None
     subprocess.check_call(["make", "-C", _HERE, "-s", "ref", f"REFERENCE={reference}"],
                           stdout=subprocess.DEVNULL)

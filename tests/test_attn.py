@@ -242,6 +242,37 @@ def test_on_the_fly_backward(shape, dtype, backend, cuda):
         assert rel_fro(t.grad, w) <= tol, f"{name}: rel-Fro {rel_fro(t.grad, w):.3e}"
 
 
+def test_on_the_fly_backward_ignores_the_neighbouring_head(cuda):
+    """Sq is no multiple of the 128-row tile, so the last tile the tensor-core backward streams for head 0 also
+    holds the first rows of head 1.  Those rows carry NaN here (host-made inputs); they are masked, and a masked
+    row must not reach head 0's gradients as 0 x NaN either."""
+    import flashdmla
+    B, H, S, dm, dl = 1, 2, 192, 128, 64
+    dtype = torch.bfloat16
+    Q = _rand((B, H, S, dl), 1.0, 141, dtype)
+    K = _rand((B, H, S, dm), 1.0, 142, dtype)
+    V = _rand((B, H, S, dm), 1.0, 143, dtype)
+    WK = _rand((dm, dl), math.sqrt(2.0 / (dm + dl)), 144, dtype)
+    WV = _rand((dm, dl), math.sqrt(2.0 / (dm + dl)), 145, dtype)
+    dO = _rand((B, H, S, dl), 1.0, 146, dtype)
+    sc = 1 / math.sqrt(dl)
+    bad = [t.clone() for t in (Q, K, V, dO)]
+    for t in bad:
+        t[:, 1] = float("nan")
+    ts = [t.to(cuda).requires_grad_(True) for t in (bad[0], bad[1], bad[2], WK, WV)]
+    O, m, l = flashdmla.flash_dmla_on_the_fly(*ts, sc, True)
+    assert flashdmla.last_kernel() == "tcgen05"
+    O.backward(bad[3].to(cuda))
+    f = [t[:, :1].float() for t in (Q, K, V)] + [WK.float(), WV.float()]
+    Or, mr, lr = orc.fwd_on_the_fly(*f, sc, True)
+    want = orc.bwd_on_the_fly(*f, Or, mr, lr, dO[:, :1].float(), sc, True)
+    assert torch.isfinite(O[:, 0].float()).all()
+    for t, w, name in zip(ts[:3], want[:3], ("dQ", "dK", "dV")):
+        got = t.grad[:, :1]
+        assert torch.isfinite(got.float()).all(), f"{name} of head 0 picked up the neighbouring head's NaN"
+        assert rel_fro(got, w) <= 2e-2, f"{name}: rel-Fro {rel_fro(got, w):.3e}"
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_cache_latent_backward(dtype, backend, cuda):
     import flashdmla
@@ -364,3 +395,27 @@ def test_paged_decode_balanced_schedule(heads, slabs, cuda):
     assert_stats(m[:, hs], l[:, hs], mr, lr)
     for b in (3, 39):     # empty sequences: zeros, -inf, 0
         assert (O[b] == 0).all() and (l[b] == 0).all() and torch.isinf(m[b]).all()
+
+
+def test_sequence_length_beyond_the_page_table_is_clamped_and_reported(cuda):
+    """seqlens[b] > max_pages * page_size cannot be served by the page table: the kernels attend the
+    max_pages * page_size keys the table describes and report it (error flag 4, which does not stop
+    later launches).  Without the clamp the balanced schedule would cut such a sequence into more
+    pieces than there are partial slabs."""
+    import flashdmla
+    lens = [700, 300, 1000]
+    Q, pool, table, sl = _paged(len(lens), 128, lens, 576, 64, torch.bfloat16, seed=15, std=0.1)
+    sc = 1 / math.sqrt(192)
+    cap = table.shape[1] * 64
+    bad, clamped = sl.clone(), sl.clone()
+    bad[1], clamped[1] = 10 ** 6, cap
+    Qd, pd, td = Q.to(cuda), pool.to(cuda), table.to(cuda)
+    assert flashdmla.device_error_flag(reset=True) in (0, 4)
+    for splits in (1, 3, 5):
+        want = flashdmla.flash_dmla_paged_decode(Qd, pd, td, clamped.to(cuda), 512, sc, num_splits=splits)
+        assert flashdmla.device_error_flag() == 0
+        got = flashdmla.flash_dmla_paged_decode(Qd, pd, td, bad.to(cuda), 512, sc, num_splits=splits)
+        assert flashdmla.device_error_flag(reset=True) == 4
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+    assert flashdmla.device_error_flag() == 0

@@ -90,6 +90,14 @@ def test_config3_causal_prefill_full_size(cuda):
         Or, mr, lr = orc.attn_plain(Q[b, h, i:i + 1].float().cpu(), Kb, Kb[:, :512], SC_MLA)
         assert_O(O[b, h, i:i + 1], Or, what=f"O[{b},{h},{i}]")
         assert_stats(m[b, h, i:i + 1], l[b, h, i:i + 1], mr, lr)
+    # whole 128-row tiles (both CTAs of a pair, both key halves, the diagonal tile): the last tile of the
+    # sequence and one in the middle.  Rows [r0, r0 + 128) against keys [0, r0 + 128) with the bottom-right
+    # causal mask are exactly those rows of the full problem.
+    for b, h, r0 in ((3, 127, S - 128), (1, 40, 4096)):
+        Or, mr, lr = orc.fwd_cache_latent(Q[b:b + 1, h:h + 1, r0:r0 + 128].float().cpu(), K[b:b + 1, : r0 + 128].float().cpu(),
+                                          512, SC_MLA, True)
+        assert_O(O[b:b + 1, h:h + 1, r0:r0 + 128], Or, what=f"O[{b},{h},{r0}:{r0 + 128}]")
+        assert_stats(m[b:b + 1, h:h + 1, r0:r0 + 128], l[b:b + 1, h:h + 1, r0:r0 + 128], mr, lr)
     assert torch.isfinite(O.float()).all() and torch.isfinite(m).all() and (l > 0).all()
     del Q, O
 
@@ -126,7 +134,7 @@ def test_config4a_long_context_sequence_split(cuda):
         Op, mp, lp = flashdmla.flash_dmla_paged_decode(Q, pool, ltab.to(cuda), llen.to(cuda), 512, SC_MLA,
                                                        num_splits=1, partial_only=True)
         msgs.append(pack_partial(Op[0], mp[0], lp[0]))
-    Om, mm, lm = flashdmla.merge_partials(*unpack_partials(torch.stack(msgs)), out_dtype=torch.bfloat16)
+    Om, mm, lm = flashdmla.merge_partials(*unpack_partials(torch.stack(msgs), (B, H), 512), out_dtype=torch.bfloat16)
     assert_O(Om, O.float())
     assert_stats(mm, lm, m, l)
     rows = flashdmla.cache_gather(pool, table.to(cuda), seqlens.to(cuda), max(lens))

@@ -228,6 +228,14 @@ def test_whole_layer_matches_the_oracle(cuda):
     pp = pos_p.cpu().numpy()
     assert np.array_equal(pp >= 0, pos >= 0)
     assert np.array_equal(np.where(pp >= 0, pp - idx * cap, -1), np.where(pos >= 0, pos - offs[idx], -1))   # same rank inside the expert
+    # rows of the padded layout that hold no assignment are marked -1 and gathered as zeros
+    used = np.zeros(layer.E * cap, dtype=bool)
+    used[pp[pp >= 0]] = True
+    perm_np = perm_p.cpu().numpy()
+    assert (perm_np[~used] == -1).all() and (perm_np[used] >= 0).all()
+    xg = moe.gather(x.to(cuda), perm_p, offs_p).float().cpu().numpy()
+    assert (xg[~used] == 0).all()
+    assert np.array_equal(xg[used], f(x)[perm_np[used]])
 
 
 @pytest.mark.gpu

@@ -128,6 +128,8 @@ def test_pack_unpack_roundtrip():
     from flashdmla.parallel import pack_partial, unpack_partials
     O, m, l = torch.randn(3, 4, 8), torch.randn(3, 4), torch.rand(3, 4)
     buf = torch.stack([pack_partial(O, m, l), pack_partial(2 * O, m + 1, l)])
-    O2, m2, l2 = unpack_partials(buf)
-    assert torch.equal(O2[0], O) and torch.equal(m2[1], m + 1) and torch.equal(l2[0], l)
-    assert O2.is_contiguous() and m2.is_contiguous()
+    O2, m2, l2 = unpack_partials(buf, (3, 4), 8)
+    assert torch.equal(O2[0], O) and torch.equal(O2[1], 2 * O) and torch.equal(m2[1], m + 1) and torch.equal(l2[0], l)
+    # the parts are views of the gathered buffer, one message apart: nothing is copied on the receiving side
+    assert O2.data_ptr() == buf.data_ptr() and O2.stride(0) == buf.shape[1] and O2[0].is_contiguous()
+    assert m2.stride(0) == l2.stride(0) == buf.shape[1]

@@ -4,9 +4,10 @@ Some callers cannot allocate device memory when they need a decode step: all of 
 already belong to a pool they do not own, the host they are plugged into may not let an
 operator call the allocator, or an allocation would synchronise a latency-critical path.
 For them the split-KV partials live in a fixed array inside the library.  This test calls
-that entry point through the C ABI, twice in a row with different problems (the array is
-shared and keeps what the previous call left in it), and checks each result against the
-ordinary entry point given caller-provided scratch.  It is collected last on purpose.
+that entry point through the C ABI, several times in a row with different problems (the array
+is shared and keeps what the previous call left in it), and checks each result against the
+ordinary entry point given caller-provided scratch and against the CPU oracle.  It is collected
+last on purpose.
 """
 import ctypes
 import math
@@ -37,14 +38,22 @@ def _call_noalloc(L, Q, pool, table, sl, splits, scale):
 
 
 def test_noalloc_decode_matches_the_ordinary_entry_point_twice(cuda):
+    import ctypes as ct
     import flashdmla
     from flashdmla import _lib
+    from oracle import dmla_oracle as orc
     L = _lib.lib()
     scale = 1 / math.sqrt(192)
+    ragged = torch.randint(500, 1025, (80,), generator=torch.Generator().manual_seed(9)).tolist()
     # first call: 3 splits, long ragged sequences; second call: a smaller problem with another
-    # split count, so stale partials of the first call sit right where the second one works
-    for lens, H, splits, seed in (([1500, 64, 2100, 700, 129], 128, 3, 5), ([300, 1000], 64, 2, 6)):
+    # split count, so stale partials of the first call sit right where the second one works; third
+    # call: many short sequences, which the library hands out as balanced runs of tiles merged inside
+    # the attention kernel - the schedule whose arrival counters have to start at zero although the
+    # array still holds whatever the first two calls left there
+    plans = []
+    for lens, H, splits, seed in (([1500, 64, 2100, 700, 129], 128, 3, 5), ([300, 1000], 64, 2, 6), (ragged, 64, 3, 7)):
         Q, pool, table, sl = _problem(lens, H, seed, cuda)
+        plans.append(L.fdmla_decode_plan(len(lens), H, 576, 512, 64, table.shape[1], splits, 1, None, None))
         rc, O, m, l = _call_noalloc(L, Q, pool, table, sl, splits, scale)
         assert rc == 0, L.fdmla_status_string(rc)
         Or, mr, lr = flashdmla.flash_dmla_paged_decode(Q, pool, table, sl, 512, scale, num_splits=splits)
@@ -52,6 +61,12 @@ def test_noalloc_decode_matches_the_ordinary_entry_point_twice(cuda):
         assert_O(O, Or.float())
         assert_stats(m, l, mr, lr)
         assert torch.equal(O, Or) and torch.equal(m, mr) and torch.equal(l, lr)   # same kernels, same split plan
+        # and against the CPU oracle, on the first sequences and heads
+        nb, nh = min(3, len(lens)), 8
+        Oo, mo, lo = orc.decode_paged(Q[:nb, :nh].float().cpu(), pool.float().cpu(), table[:nb].cpu(), sl[:nb].cpu(), 512, scale)
+        assert_O(O[:nb, :nh], Oo)
+        assert_stats(m[:nb, :nh], l[:nb, :nh], mo, lo)
+    assert plans[2] == 2, f"the third problem was meant to take the in-kernel balanced schedule (plans {plans})"
     assert flashdmla.device_error_flag() == 0
 
 
