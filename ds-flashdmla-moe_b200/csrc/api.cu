@@ -85,6 +85,7 @@ static double equal_split_cost(long long items, int tiles, int s, int units) {
 //                       pieces, merge kernel over the cut rows (launch + partial traffic: about 7 tile times)
 //   BALANCED_IN_KERNEL  the same runs with at most min(slabs - 1, kMaxInKernelPieces) pieces per sequence, merged by
 //                       the CTA pair that finishes a sequence's last piece; the last slab holds the arrival counters
+//                       (about 6 tile times for the partial rows, the counters and that merge)
 constexpr int kMaxInKernelPieces = 4;
 struct DecodePlan { enum Mode { EQUAL, BALANCED_MERGE, BALANCED_IN_KERNEL } mode; int quota_min; double cost; };
 
@@ -100,7 +101,9 @@ static DecodePlan plan_decode(int B, int nt_max, int slabs, int units) {
     if (slabs >= 3) {
         const int pieces = slabs - 1 < kMaxInKernelPieces ? slabs - 1 : kMaxInKernelPieces;
         const int qmin = (nt_max + pieces - 2) / (pieces - 1);
-        const double cost = (double)(run > qmin ? run : qmin) + 1.5 + 1.0;
+        // measured at B = 128 x 4096 keys: a pair that handles two cut sequences pays about six tile times for the
+        // fp32 partial rows it writes, the arrival counters and the merge of the sequence it finishes last
+        const double cost = (double)(run > qmin ? run : qmin) + 1.5 + 6.0;
         if (cost < best.cost) best = DecodePlan{DecodePlan::BALANCED_IN_KERNEL, qmin, cost};
     }
     return best;

@@ -25,12 +25,13 @@
 // by TMA (no multicast anywhere) in exactly the order the MMAs consume it: Q*K^T
 // of tile t+1 is issued before P*V of tile t, so the tensor pipe works on the next
 // tile's scores while the softmax warps turn the current ones into P.  Only the leader CTA (rank 0) issues MMAs; completion is
-// broadcast to both CTAs' mbarriers with tcgen05.commit.  CTA 1 forwards "my
-// slot has landed" and both CTAs forward "my P quarter is written" to the leader
-// with remote mbarrier arrivals.
+// broadcast to both CTAs' mbarriers with tcgen05.commit.  The copies of both CTAs
+// credit their bytes to the leader's "slot full" barriers (cta_group::2 copies may
+// name a barrier of the pair's other CTA), and both CTAs tell the leader "my P
+// quarter is written" with remote mbarrier arrivals.
 //
-// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (leader) / load relay
-// (peer) and TMEM owner, warps 2-5 softmax (thread L owns TMEM lane L: row
+// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (leader only) and TMEM
+// owner, warps 2-5 softmax (thread L owns TMEM lane L: row
 // L % 64, key half L / 64 of every tile) and epilogue.
 //
 // The recurrence is the online softmax of the reference's
@@ -60,8 +61,8 @@ constexpr int RED_BYTES = 2 * 128 * 4;
 constexpr int ROWS_CACHE = 1920;      // sub-block rows resolved through the page table up front
 constexpr int O_COLS = 256, S_COL0 = 256, S_COLS = 128, TMEM_COLS = 512;
 // barriers (same offsets in both CTAs)
-constexpr int B_QFULL = 0, B_PEER_QFULL = 1, B_QEMPTY = 2, B_OFREE = 3, B_FULL = 4, B_EMPTY = B_FULL + NSLOT,
-              B_FIX = B_EMPTY + NSLOT, B_SFULL = B_FIX + 2, B_SEMPTY = B_SFULL + 2, B_PFULL = B_SEMPTY + 2,
+constexpr int B_QFULL = 0, B_FIXLOAD = 1, B_QEMPTY = 2, B_OFREE = 3, B_FULL = 4, B_EMPTY = B_FULL + NSLOT,
+              B_FIX = B_EMPTY + NSLOT, B_SFULL = B_FIX + 1, B_SEMPTY = B_SFULL + 2, B_PFULL = B_SEMPTY + 2,
               B_OREADY = B_PFULL + 4, B_PEMPTY = B_OREADY + 2, NBARS = B_PEMPTY + 4;
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + NSLOT * SLOT + P_BYTES + RED_BYTES + ROWS_CACHE * 4 + NBARS * 8 + 16;
 static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
@@ -81,6 +82,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // ready, 3 + 3 i item i's last P V accumulated, 4 + 3 i item i's result written, 30 roles finished, 31 exit.
 // Nothing of this is compiled into the library otherwise.
 #ifdef FDMLA_TIMELINE
+// -DFDMLA_ABLATE=bits (with -DFDMLA_TIMELINE): time the pipeline with one stage taken out (the results are garbage).
+// 1: K/V copies skipped, 2: softmax arithmetic skipped, 4: MMAs skipped.
+#ifndef FDMLA_ABLATE
+#define FDMLA_ABLATE 0
+#endif
+constexpr int ABL = FDMLA_ABLATE;
 constexpr int TL_CLUSTERS = 128, TL_SLOTS = 32, TL_ITEMS = 9;
 __device__ unsigned long long g_timeline[TL_CLUSTERS][TL_SLOTS];
 __device__ int g_timeline_tiles[TL_CLUSTERS][TL_ITEMS];
@@ -91,9 +98,31 @@ __device__ __forceinline__ unsigned long long gtimer() {
 }
 #define TL(slot) do { if (leader && cid < TL_CLUSTERS && (slot) < TL_SLOTS) g_timeline[cid][slot] = gtimer(); } while (0)
 #define TL_ITEM(i, nt) do { if (leader && cid < TL_CLUSTERS && (i) < TL_ITEMS) g_timeline_tiles[cid][i] = (nt); } while (0)
+// Cycles each role spends inside its waits, by kind of wait: [pair][CTA rank][role 0 producer, 1 MMA issuer / relay,
+// 2 softmax thread 0][kind]; kind 7 is the role's whole loop.
+constexpr int TW_KINDS = 8;
+__device__ long long g_waits[TL_CLUSTERS][2][3][TW_KINDS];
+constexpr int TL_TILES = 40;                                  // global-timer stamp of "scores of the pair's n-th tile are ready"
+__device__ unsigned long long g_tile_ts[TL_CLUSTERS][TL_TILES];
+__device__ long long g_tile_clk[TL_CLUSTERS][TL_TILES];      // SM clock at the same moments
+#define TL_TILE(n) do { if (leader && cid < TL_CLUSTERS && (n) < TL_TILES) { g_tile_ts[cid][n] = gtimer(); g_tile_clk[cid][n] = clock64(); } } while (0)
+#define TW_DECL long long tw[TW_KINDS] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long tw_start = clock64()
+#define TW(kind, expr) ([&]() -> bool { const long long t0_ = clock64(); const bool r_ = (expr); tw[kind] += clock64() - t0_; return r_; }())
+#define TW_SYNC() __syncwarp()
+#define TW_BEGIN(var) const long long var = clock64()
+#define TW_END(kind, var) tw[kind] += clock64() - (var)
+#define TW_FLUSH(role) do { tw[7] = clock64() - tw_start; if (cid < TL_CLUSTERS) for (int k_ = 0; k_ < TW_KINDS; ++k_) g_waits[cid][rank][role][k_] = tw[k_]; } while (0)
 #else
+constexpr int ABL = 0;
 #define TL(slot) do { } while (0)
 #define TL_ITEM(i, nt) do { } while (0)
+#define TL_TILE(n) do { } while (0)
+#define TW_DECL do { } while (0)
+#define TW(kind, expr) (expr)
+#define TW_SYNC() do { } while (0)
+#define TW_BEGIN(var) do { } while (0)
+#define TW_END(kind, var) do { } while (0)
+#define TW_FLUSH(role) do { } while (0)
 #endif
 
 // Four consecutive K=16 steps of one 2-CTA MMA: descriptors advance by a_step / b_step (in
@@ -123,30 +152,9 @@ __device__ __forceinline__ void mma4_2cta(uint32_t d_tmem, uint64_t a_desc, uint
 // before the second pair of quarters is even written.
 __device__ __forceinline__ int quarter_at(int i) { return ((i & 1) << 1) | (i >> 1); }      // 0, 2, 1, 3
 
-// The one order in which ring slots are filled and consumed.  `f(is_v, t, a, b)` is
-// called for a K slot as (false, tile, chunk, 0) and for a V slot as (true, tile, quarter,
-// half j); it returns false to stop.  n_sub = number of 64-key sub-blocks to attend.
-template <class F>
-__device__ __forceinline__ bool walk_slots(int n_tiles, int n_sub, F &&f) {
-    // K tile 0, then for every tile t: the whole K tile t+1 (its Q K^T runs while the softmax
-    // of tile t works), then the V quarters of tile t (their P V runs while the softmax of tile
-    // t+1 takes its row maxima).
-    for (int c = 0; c < NQC; ++c)
-        if (!f(false, 0, c, 0)) return false;
-    for (int t = 0; t < n_tiles; ++t) {
-        if (t + 1 < n_tiles)
-            for (int c = 0; c < NQC; ++c)
-                if (!f(false, t + 1, c, 0)) return false;
-        const int nq = (n_sub - 4 * t) < 4 ? (n_sub - 4 * t) : 4;     // quarters of tile t that exist
-        for (int i = 0; i < 4; ++i) {
-            const int q = quarter_at(i);
-            if (q >= nq) continue;
-            if (!f(true, t, q, 0)) return false;
-            if (!f(true, t, q, 1)) return false;
-        }
-    }
-    return true;
-}
+// Ring slots are filled and consumed in one order: the nine K slots of tile 0, then for every tile t the whole K tile
+// t + 1 (its Q K^T runs while the softmax of tile t works) followed by the V slot pairs of tile t's quarters in the
+// order of quarter_at (their P V runs while the softmax of tile t + 1 takes its row maxima).
 
 // Keys of KV group g.  A length outside [0, Skv] (Skv = max_pages * page_size for a paged cache) is clamped:
 // the page table has no entries for more, and an unclamped length would cut a sequence into more pieces
@@ -360,16 +368,15 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
     // ---- set-up ------------------------------------------------------------------------
     if (threadIdx.x == 0) {
         *err_slot = *reinterpret_cast<volatile int *>(&g_tc_error);
-        mbar_init(BAR(B_QFULL), 1);
-        mbar_init(BAR(B_PEER_QFULL), 1);
+        mbar_init(BAR(B_QFULL), 1);          // leader: its producer's arrival, the bytes of both CTAs' copies
+        mbar_init(BAR(B_FIXLOAD), 1);        // own copies of a V slot pair whose tail has to be zeroed
         mbar_init(BAR(B_QEMPTY), 1);
         mbar_init(BAR(B_OFREE), 2);                      // one arrival per CTA of the pair
         for (int s = 0; s < NSLOT; ++s) {
-            mbar_init(BAR(B_FULL + s), leader ? 2 : 1);   // leader: own copy + the peer's "landed" arrival
+            mbar_init(BAR(B_FULL + s), 1);    // used in the leader only: both CTAs' copies credit their bytes to it
             mbar_init(BAR(B_EMPTY + s), 1);
         }
-        mbar_init(BAR(B_FIX), 1);          // zero-filled tail of the j = 0 V slot
-        mbar_init(BAR(B_FIX + 1), 1);      // ... and of the j = 1 V slot (each used once per item at most)
+        mbar_init(BAR(B_FIX), 2);          // leader: both CTAs have zero-filled the tail of a V slot pair (once per item at most)
         for (int b = 0; b < 2; ++b) {
             mbar_init(BAR(B_SFULL + b), 1);
             mbar_init(BAR(B_SEMPTY + b), 4);     // two key halves in each CTA of the pair
@@ -418,7 +425,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         bool bad = false, ok = true;
         const bool elected = elect_one();
         int next_slot = 0, next_use = 0;      // ring position and how many times the ring has wrapped
-        int q_loads = 0;
+        int q_loads = 0, fix_uses = 0;
+        // Every copy of the pair credits its bytes to a barrier of the LEADER CTA (cta_group::2 copies may name a
+        // barrier of the other CTA of the pair): the MMA issuer then waits on one barrier per slot for both halves,
+        // and the leader's producer announces the bytes of both CTAs.
+        const uint32_t lead_bars = map_to_cta(bar0, 0);
+        TW_DECL;
         if (lane == 0) {
             prefetch_tmap(&tmQ);
             prefetch_tmap(&tmK);
@@ -431,11 +443,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             if (p.seqlens && p.seqlens[it.g] != it.seq) bad = true;      // a length outside [0, max_pages * page_size] was clamped
             if (it.n_tiles == 0) continue;
             // Q of the previous item is free once its last Q K^T has completed
-            if (q_loads > 0) ok = ok && mbar_wait(BAR(B_QEMPTY), (q_loads - 1) & 1);
+            if (q_loads > 0) ok = ok && TW(0, mbar_wait(BAR(B_QEMPTY), (q_loads - 1) & 1));
+            TW_BEGIN(tw_set);
             if (elected) {
-                mbar_arrive_expect_tx(BAR(B_QFULL), Q_BYTES);
+                if (leader) mbar_arrive_expect_tx(BAR(B_QFULL), 2 * Q_BYTES);       // this CTA's rows and the peer's
                 const int qrow = it.g * p.R + it.row0 + 64 * (int)rank;
-                tma_load_3d(smem_u32(sQ), &tmQ, 0, qrow, 0, BAR(B_QFULL));          // all 9 chunks in one copy
+                tma_load_3d_pair(smem_u32(sQ), &tmQ, 0, qrow, 0, lead_bars + 8u * B_QFULL);   // all 9 chunks in one copy
             }
             ++q_loads;
             // resolve the page table for the whole key range once, with every lane of the warp
@@ -444,6 +457,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             for (int s = lane; s < n_cached; s += 32) s_rows[s] = sub_row(it, s, &bad);
             __syncwarp();
             auto row_of = [&](int s) -> int { return s < ROWS_CACHE ? s_rows[s] : sub_row(it, s, &bad); };
+            TW_END(6, tw_set);
             // The whole warp walks the ring converged and one elected lane issues the copies (the
             // uniform datapath makes the issue several times cheaper than from a lone diverged lane).
             auto take = [&](int &slot, int &use) {
@@ -456,50 +470,72 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 for (int i = 0; i < 3; ++i) take(sl[i], us[i]);
                 if (us[2] >= 1) {     // slots handed out before: wait until the MMAs that read them are done
                     if (us[0] >= 1)
-                        ok = ok && mbar_wait3(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1,
-                                              BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
+                        ok = ok && TW(1, mbar_wait3(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1,
+                                              BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1));
                     else if (us[1] >= 1)
-                        ok = ok && mbar_wait2(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1, BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
+                        ok = ok && TW(1, mbar_wait2(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1, BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1));
                     else
-                        ok = ok && mbar_wait(BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1);
+                        ok = ok && TW(1, mbar_wait(BAR(B_EMPTY + sl[2]), (us[2] - 1) & 1));
                 }
+                auto present_of = [&](int s_first) { return (s_first + 1 < it.n_sub) ? 2 : (s_first < it.n_sub ? 1 : 0); };
                 const int s0 = 4 * t + 2 * (int)rank;
-                const int present = (s0 + 1 < it.n_sub) ? 2 : (s0 < it.n_sub ? 1 : 0);
+                const int present = present_of(s0);
+                const int present_pair = present_of(4 * t) + present_of(4 * t + 2);
                 const int r0 = present > 0 ? row_of(s0) : 0, r1 = present > 1 ? row_of(s0 + 1) : 0;
+                TW_BEGIN(tw_ki);
                 if (elected) {
 #pragma unroll
                     for (int i = 0; i < 3; ++i) {
-                        const uint32_t full = BAR(B_FULL + sl[i]);
+                        const uint32_t full = lead_bars + 8u * (B_FULL + sl[i]);
                         const uint32_t dst = smem_u32(sRing + sl[i] * SLOT);
-                        mbar_arrive_expect_tx(full, present * BOX);
-                        if (present > 0) tma_load_2d(dst, &tmK, (3 * g3 + i) * 64, r0, full);
-                        if (present > 1) tma_load_2d(dst + BOX, &tmK, (3 * g3 + i) * 64, r1, full);
+                        if (ABL & 1) { if (leader) mbar_arrive(BAR(B_FULL + sl[i])); continue; }
+                        if (leader) mbar_arrive_expect_tx(BAR(B_FULL + sl[i]), present_pair * BOX);
+                        if (present > 0) tma_load_2d_pair(dst, &tmK, (3 * g3 + i) * 64, r0, full);
+                        if (present > 1) tma_load_2d_pair(dst + BOX, &tmK, (3 * g3 + i) * 64, r1, full);
                     }
                 }
+                TW_SYNC();
+                TW_END(4, tw_ki);
             };
             // two V slots: the 64 keys of quarter q of tile t, own d_v columns [256 r + 128 j, +128), j = 0, 1
             auto fill_v2 = [&](int t, int q) {
                 int sl[2], us[2];
                 for (int j = 0; j < 2; ++j) take(sl[j], us[j]);
                 if (us[0] >= 1)
-                    ok = ok && mbar_wait2(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
+                    ok = ok && TW(2, mbar_wait2(BAR(B_EMPTY + sl[0]), (us[0] - 1) & 1, BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1));
                 else if (us[1] >= 1)
-                    ok = ok && mbar_wait(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1);
+                    ok = ok && TW(2, mbar_wait(BAR(B_EMPTY + sl[1]), (us[1] - 1) & 1));
                 const int s = 4 * t + q;
                 const int row = row_of(s);
+                const int t0 = it.t_begin + s * SUB;
+                const bool tail = t0 + SUB > it.seq;      // keys past the end of the sequence in this sub-block
+                TW_BEGIN(tw_vi);
                 if (elected) {
+                    if (!tail) {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const uint32_t full = BAR(B_FULL + sl[j]);
-                        mbar_arrive_expect_tx(full, SLOT);
-                        tma_load_3d(smem_u32(sRing + sl[j] * SLOT), &tmV, 0, row, 4 * (int)rank + 2 * j, full);   // two chunks, one copy
+                        for (int j = 0; j < 2; ++j) {
+                            if (ABL & 1) { if (leader) mbar_arrive(BAR(B_FULL + sl[j])); continue; }
+                            if (leader) mbar_arrive_expect_tx(BAR(B_FULL + sl[j]), 2 * SLOT);
+                            tma_load_3d_pair(smem_u32(sRing + sl[j] * SLOT), &tmV, 0, row, 4 * (int)rank + 2 * j,
+                                             lead_bars + 8u * (B_FULL + sl[j]));   // two chunks, one copy
+                        }
+                    } else {
+                        // the copies of this pair of slots report to a barrier of this CTA, which has to touch the data
+                        // before the MMAs may; the slots' own barriers complete their phase without bytes
+                        mbar_arrive_expect_tx(BAR(B_FIXLOAD), 2 * SLOT);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            if (leader) mbar_arrive(BAR(B_FULL + sl[j]));
+                            tma_load_3d(smem_u32(sRing + sl[j] * SLOT), &tmV, 0, row, 4 * (int)rank + 2 * j, BAR(B_FIXLOAD));
+                        }
                     }
                 }
-                const int t0 = it.t_begin + s * SUB;
-                if (t0 + SUB > it.seq) {
-                    // keys past the end of the sequence: zero their V rows once the copies have
-                    // landed (whole 128-byte rows, so the swizzle does not matter)
-                    ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), us[0] & 1, BAR(B_FULL + sl[1]), us[1] & 1);
+                TW_SYNC();
+                TW_END(5, tw_vi);
+                if (tail) {
+                    // zero the V rows of the keys past the end once the copies have landed (whole 128-byte rows,
+                    // so the swizzle does not matter), then tell the leader's MMA issuer
+                    ok = ok && TW(3, mbar_wait(BAR(B_FIXLOAD), fix_uses & 1));
                     const int first_bad = it.seq > t0 ? it.seq - t0 : 0;
                     const int bad_rows = SUB - first_bad;
                     for (int idx2 = lane; idx2 < 4 * bad_rows * 8; idx2 += 32) {
@@ -509,7 +545,8 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (elected) { mbar_arrive(BAR(B_FIX)); mbar_arrive(BAR(B_FIX + 1)); }   // only the last sub-block can straddle the end
+                    if (elected) mbar_arrive_cluster(lead_bars + 8u * B_FIX);   // (release, cluster scope: once per item at most)
+                    ++fix_uses;                                                // only the last sub-block of an item can straddle the end
                 }
             };
             for (int g3 = 0; g3 < 3; ++g3) fill_k3(0, g3);
@@ -521,6 +558,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     if (quarter_at(i) < nq) fill_v2(t, quarter_at(i));
             }
         }
+        if (lane == 0) TW_FLUSH(0);
         if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
         if (bad) atomicCAS(&g_tc_error, 0, ERR_PAGE);
         __syncwarp();
@@ -542,6 +580,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             uint32_t ph = 0;
             int tg0 = 0;                // tiles of the items before the current one
             int q_loads = 0, items_done = 0, fix_uses = 0;     // items_done: items that used the accumulator
+            TW_DECL;
             Cursor cur;
             cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
             Item it;
@@ -553,12 +592,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 bool o_free_waited = items_done == 0;
                 auto wait_o_free = [&]() {
                     if (!o_free_waited) {
-                        ok = ok && mbar_wait(BAR(B_OFREE), (items_done - 1) & 1);
+                        ok = ok && TW(6, mbar_wait(BAR(B_OFREE), (items_done - 1) & 1));
                         tc_fence_after_sync();
                         o_free_waited = true;
                     }
                 };
-                ok = ok && mbar_wait(BAR(B_QFULL), q_loads & 1) && mbar_wait(BAR(B_PEER_QFULL), q_loads & 1);
+                ok = ok && TW(0, mbar_wait(BAR(B_QFULL), q_loads & 1));
                 ++q_loads;
                 auto take = [&](int &sl, uint32_t &pp) {
                     sl = slot; pp = ph;
@@ -572,18 +611,21 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     for (int i = 0; i < 3; ++i) take(sl[i], phs[i]);
                     if (g3 == 0) {
                         // S[b] was last read by the softmax of the tile two before
-                        if (tg >= 2) ok = ok && mbar_wait(BAR(B_SEMPTY + b), ((tg / 2) - 1) & 1);
+                        if (tg >= 2) ok = ok && TW(1, mbar_wait(BAR(B_SEMPTY + b), ((tg / 2) - 1) & 1));
                         tc_fence_after_sync();
                     }
-                    ok = ok && mbar_wait3(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1], BAR(B_FULL + sl[2]), phs[2]);
-                    if (elected) {
 #pragma unroll
-                        for (int i = 0; i < 3; ++i) {
+                    for (int i = 0; i < 3; ++i) {
+                        // (waiting slot by slot measured 2 % faster than waiting for the three together)
+                        ok = ok && TW(2, mbar_wait(BAR(B_FULL + sl[i]), phs[i]));
+                        if (elected) {
                             const int c = 3 * g3 + i;
-                            mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)c * (Q_CHUNK >> 4),
+                            if (!(ABL & 4)) mma4_2cta(tmem + S_COL0 + b * S_COLS, q_desc + (uint32_t)c * (Q_CHUNK >> 4),
                                       rk_desc + (uint32_t)sl[i] * (SLOT >> 4), 2, 2, idesc_qk, c != 0);
                             mma_commit_2cta(BAR(B_EMPTY + sl[i]), 3);
                         }
+                    }
+                    if (elected) {
                         if (g3 == 2) {
                             mma_commit_2cta(BAR(B_SFULL + b), 3);
                             if (tk == it.n_tiles - 1) mma_commit_2cta(BAR(B_QEMPTY), 3);   // last use of this item's Q
@@ -596,15 +638,15 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     int sl[2];
                     uint32_t phs[2];
                     for (int j = 0; j < 2; ++j) take(sl[j], phs[j]);
-                    ok = ok && mbar_wait(BAR(B_PFULL + q), tg & 1);
+                    ok = ok && TW(3, mbar_wait(BAR(B_PFULL + q), tg & 1));
                     tc_fence_after_sync();      // orders the accumulation after the softmax's rescale of O
-                    ok = ok && mbar_wait2(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1]);
+                    ok = ok && TW(4, mbar_wait2(BAR(B_FULL + sl[0]), phs[0], BAR(B_FULL + sl[1]), phs[1]));
                     if (it.t_begin + (4 * t + q) * SUB + SUB > it.seq)
-                        ok = ok && mbar_wait2(BAR(B_FIX), fix_uses & 1, BAR(B_FIX + 1), fix_uses & 1);
+                        ok = ok && TW(5, mbar_wait_cluster(BAR(B_FIX), fix_uses & 1));
                     if (elected) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            mma4_2cta(tmem + j * 128, p_desc + (uint32_t)q * (P_Q >> 4), rv_desc + (uint32_t)sl[j] * (SLOT >> 4),
+                            if (!(ABL & 4)) mma4_2cta(tmem + j * 128, p_desc + (uint32_t)q * (P_Q >> 4), rv_desc + (uint32_t)sl[j] * (SLOT >> 4),
                                       16, 128, idesc_pv, (t | q) != 0);
                             mma_commit_2cta(BAR(B_EMPTY + sl[j]), 3);
                         }
@@ -634,33 +676,11 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 fix_uses += it.fix ? 1 : 0;
                 ++items_done;
             }
+            if (lane == 0) TW_FLUSH(1);
             if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_MMA);
-        } else {
-            // =========================== load relay (peer CTA) ===========================
-            // (converged warp, one elected lane signals: see the MMA issuer)
-            const bool elected = elect_one();
-            const uint32_t peer_base = map_to_cta(BAR(B_FULL), 0);
-            int slot = 0, use = 0, q_loads = 0, fix_uses = 0;
-            bool ok = true;
-            Cursor cur;
-            cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
-            Item it;
-            for (int round = 0; ok && cursor_next(cur, p, poisoned, it); ++round) {
-                if (it.n_tiles == 0) continue;
-                ok = mbar_wait(BAR(B_QFULL), q_loads & 1);
-                ++q_loads;
-                if (ok && elected) mbar_arrive_cluster_relaxed(map_to_cta(BAR(B_PEER_QFULL), 0));
-                ok = ok && walk_slots(it.n_tiles, it.n_sub, [&](bool is_v, int t, int a, int j) -> bool {
-                    if (!mbar_wait(BAR(B_FULL + slot), use & 1)) return false;
-                    if (is_v && it.t_begin + (4 * t + a) * SUB + SUB > it.seq && !mbar_wait(BAR(B_FIX + j), fix_uses & 1)) return false;
-                    if (elected) mbar_arrive_cluster_relaxed(peer_base + 8u * slot);
-                    if (++slot == NSLOT) { slot = 0; ++use; }
-                    return true;
-                });
-                fix_uses += it.fix ? 1 : 0;
-            }
-            if (!ok && lane == 0) atomicCAS(&g_tc_error, 0, ERR_RELAY);
         }
+        // (warp 1 of the peer CTA only owns the tensor-memory allocation: every copy of the pair reports to the
+        // leader's barriers by itself)
         __syncwarp();
     } else {
         // =========================== softmax + epilogue (both CTAs) ========================
@@ -679,6 +699,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
         int p_reads[2] = {0, 0};
         int tg0 = 0;                            // tiles of the items before the current one
         uint32_t r[32];
+        TW_DECL;
         Cursor cur;
         cursor_init<DECODE>(cur, p, cid, n_clusters, lane);
         Item it;
@@ -740,14 +761,15 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         }
                     }
                 }
-                if (ok && !(ok = mbar_wait(BAR(B_SFULL + b), (tg / 2) & 1))) fail = ERR_SOFTMAX;
+                if (ok && !(ok = TW(0, mbar_wait(BAR(B_SFULL + b), (tg / 2) & 1)))) fail = ERR_SOFTMAX;
                 if (L == 0 && t == 0) TL(2 + 3 * round);
+                if (L == 0) TL_TILE(tg);
                 tc_fence_after_sync();
                 // pass 1: maximum of this thread's 128 keys (no per-key masking when all are visible)
                 const bool all_visible = tok0 >= lo && tok0 + 128 <= upper && sl2 > 0.f;
                 float tmax = -CUDART_INF_F;
 #pragma unroll 1
-                for (int cp = 0; cp < 4; cp += 2) {
+                for (int cp = (ABL & 2) ? 4 : 0; cp < 4; cp += 2) {
                     // two 32-column loads in flight per wait
                     uint32_t r2[32];
                     tmem_ld32(s_addr + cp * 32, r);
@@ -775,7 +797,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 if (__any_sync(0xffffffffu, need)) {
                     // O is rescaled: every P*V of tile t-1 must have been accumulated
                     if (t > 0) {
-                        if (ok && !(ok = mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1))) fail = ERR_SOFTMAX_RESCALE;
+                        if (ok && !(ok = TW(1, mbar_wait(BAR(B_OREADY + ((tg - 1) & 1)), ((tg - 1) / 2) & 1)))) fail = ERR_SOFTMAX_RESCALE;
                         tc_fence_after_sync();
                     }
                     float alpha = 1.f;
@@ -802,10 +824,15 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 float lsum = 0.f;
 #pragma unroll 1
                 for (int cc = 0; cc < 4; ++cc) {
-                    tmem_ld32(s_addr + cc * 32, r);
-                    tmem_wait_ld();
+                    if (!(ABL & 2)) {
+                        tmem_ld32(s_addr + cc * 32, r);
+                        tmem_wait_ld();
+                    }
                     uint32_t packed[16];
-                    if (all_visible) {
+                    if (ABL & 2) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) packed[j] = 0;
+                    } else if (all_visible) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
                             const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), sl2, -m_ref));
@@ -828,7 +855,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                     const int quarter = 2 * half + (cc >> 1);
                     // the last P*V that read this quarter's previous contents is done
                     if (!(cc & 1) && p_reads[cc >> 1] > 0 && ok &&
-                        !(ok = mbar_wait(BAR(B_PEMPTY + quarter), (p_reads[cc >> 1] - 1) & 1))) {
+                        !(ok = TW(2, mbar_wait(BAR(B_PEMPTY + quarter), (p_reads[cc >> 1] - 1) & 1)))) {
                         fail = ERR_SOFTMAX_P;
                     }
                     uint8_t *prow = sP + quarter * P_Q + (row >> 3) * P_SBO + (row & 7) * 16 + (cc & 1) * 4 * 128;
@@ -859,11 +886,12 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             }
             if (ok && n_tiles > 0) {
                 const int tl = tg0 + n_tiles - 1;
-                if (!(ok = mbar_wait(BAR(B_OREADY + (tl & 1)), (tl / 2) & 1))) fail = ERR_SOFTMAX_END;
+                if (!(ok = TW(3, mbar_wait(BAR(B_OREADY + (tl & 1)), (tl / 2) & 1)))) fail = ERR_SOFTMAX_END;
                 tc_fence_after_sync();
             }
             tg0 += n_tiles;
             if (L == 0) { TL(3 + 3 * round); TL_ITEM(round, n_tiles); }
+            TW_BEGIN(tw_epi);
             // row sum = both key halves
             named_bar_sync(1, 128);
             red[L] = l_run;
@@ -971,6 +999,8 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                         }
                 }
             }
+            TW_END(4, tw_epi);
+            TW_BEGIN(tw_merge);
             if (DECODE && it.n_parts > 1 && p.tickets != nullptr) {
                 // Balanced schedule, merge in this kernel: this CTA has written its 64 rows of one piece of a cut
                 // sequence.  It then draws a ticket for (sequence, CTA rank); the CTA that draws the last one finds
@@ -982,48 +1012,76 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
                 if (L == 0) reinterpret_cast<unsigned int *>(red)[0] = atomicAdd(&p.tickets[2 * it.g + (int)rank], 1u);
                 named_bar_sync(1, 128);
                 const bool last_piece = reinterpret_cast<volatile unsigned int *>(red)[0] == (unsigned)(it.n_parts - 1);
-                if (last_piece && row_ok) {
+                if (last_piece) {
                     __threadfence();
+                    // Each of the four warps merges 16 of the CTA's 64 rows, two rows at a time; a lane owns four
+                    // consecutive d_v columns in each 128-column block, so every load and store of the warp is one
+                    // contiguous run, and all loads of a row pair are in flight together.
                     const size_t slab = (size_t)p.G * p.R;
-                    float mx = -CUDART_INF_F;
-                    for (int k = 0; k < it.n_parts; ++k)
-                        if (__ldcg(p.l_part + k * slab + grow) > 0.f) mx = fmaxf(mx, __ldcg(p.m_part + k * slab + grow));
-                    float ls = 0.f;
-                    for (int k = 0; k < it.n_parts; ++k) {
-                        const float lk = __ldcg(p.l_part + k * slab + grow);
-                        if (lk > 0.f) ls += lk * __expf(__ldcg(p.m_part + k * slab + grow) - mx);
-                    }
-                    const float inv_l = ls > 0.f ? 1.f / ls : 0.f;
-                    __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + grow * p.d_v + col0;
+                    const int np = it.n_parts < 4 ? it.n_parts : 4;        // the launcher never plans more
+                    const int w4 = warp & 3;
 #pragma unroll 1
-                    for (int cc = 0; cc < O_COLS / 16; ++cc) {
-                        float acc[16];
+                    for (int rp = 0; rp < 16; rp += 2) {
+                        float4 v[2][4][4];
+                        float wgt[2][4], mx2[2], ls2[2];
+                        size_t gr[2];
+                        bool okr[2];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-                        for (int k = 0; k < it.n_parts; ++k) {
-                            const float lk = __ldcg(p.l_part + k * slab + grow);
-                            if (lk > 0.f) {
-                                const float w = lk * __expf(__ldcg(p.m_part + k * slab + grow) - mx) * inv_l;
-                                const float4 *src = reinterpret_cast<const float4 *>(p.O_part + (k * slab + grow) * p.d_v + col0 + cc * 16);
+                        for (int e = 0; e < 2; ++e) {
+                            const int r_in = it.row0 + 64 * (int)rank + w4 * 16 + rp + e;
+                            okr[e] = r_in < p.R;
+                            gr[e] = (size_t)it.g * p.R + (okr[e] ? r_in : 0);
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const float4 v = __ldcg(src + j);
-                                    acc[4 * j] = fmaf(w, v.x, acc[4 * j]); acc[4 * j + 1] = fmaf(w, v.y, acc[4 * j + 1]);
-                                    acc[4 * j + 2] = fmaf(w, v.z, acc[4 * j + 2]); acc[4 * j + 3] = fmaf(w, v.w, acc[4 * j + 3]);
+                            for (int k = 0; k < 4; ++k)
+                                if (k < np) {
+                                    const float4 *src = reinterpret_cast<const float4 *>(p.O_part + (k * slab + gr[e]) * p.d_v) + lane;
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) v[e][k][j] = __ldcg(src + 32 * j);
                                 }
-                            }
                         }
-                        uint32_t w8[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-                            w8[e] = *reinterpret_cast<uint32_t *>(&h);
+                        for (int e = 0; e < 2; ++e) {
+                            float lk[4], mk[4];
+                            mx2[e] = -CUDART_INF_F;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                lk[k] = k < np ? __ldcg(p.l_part + k * slab + gr[e]) : 0.f;
+                                mk[k] = k < np ? __ldcg(p.m_part + k * slab + gr[e]) : -CUDART_INF_F;
+                                if (lk[k] > 0.f) mx2[e] = fmaxf(mx2[e], mk[k]);
+                            }
+                            ls2[e] = 0.f;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                wgt[e][k] = lk[k] > 0.f ? lk[k] * __expf(mk[k] - mx2[e]) : 0.f;
+                                ls2[e] += wgt[e][k];
+                            }
+                            const float inv_l = ls2[e] > 0.f ? 1.f / ls2[e] : 0.f;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) wgt[e][k] *= inv_l;
                         }
-                        st_global_v8(dst + cc * 16, w8);
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            if (!okr[e]) continue;
+                            __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + gr[e] * p.d_v + 4 * lane;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k)
+                                    if (k < np && wgt[e][k] > 0.f) {
+                                        acc.x = fmaf(wgt[e][k], v[e][k][j].x, acc.x); acc.y = fmaf(wgt[e][k], v[e][k][j].y, acc.y);
+                                        acc.z = fmaf(wgt[e][k], v[e][k][j].z, acc.z); acc.w = fmaf(wgt[e][k], v[e][k][j].w, acc.w);
+                                    }
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x, acc.y), h1 = __floats2bfloat162_rn(acc.z, acc.w);
+                                *reinterpret_cast<uint2 *>(dst + 128 * j) =
+                                    make_uint2(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1));
+                            }
+                            if (lane == 0) { p.m[gr[e]] = mx2[e]; p.l[gr[e]] = ls2[e]; }
+                        }
                     }
-                    if (half == 0) { p.m[grow] = mx; p.l[grow] = ls; }
                 }
             }
+            TW_END(5, tw_merge);
             // this CTA's softmax warps have read O out of tensor memory: the next item may overwrite it
             // (an empty item never touched the accumulator and signals nothing)
             tc_fence_before_sync();
@@ -1031,6 +1089,7 @@ fwd_tc2_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ, cons
             if (L == 0 && n_tiles > 0) mbar_arrive_cluster_relaxed(ofree_leader);
             if (L == 0) TL(4 + 3 * round);
         }
+        if (L == 0) TW_FLUSH(2);
         if (!ok) atomicCAS(&g_tc_error, 0, fail ? fail : ERR_SOFTMAX);
     }
 
@@ -1130,14 +1189,23 @@ int launch_fwd_tensor2(const FwdProblem &p_in, cudaStream_t stream) {
         // one record per launch: n_clusters, decode flag, then the stamps and the tiles per item of every pair
         static unsigned long long stamps[tc2::TL_CLUSTERS][tc2::TL_SLOTS];
         static int tiles[tc2::TL_CLUSTERS][tc2::TL_ITEMS];
+        static long long waits[tc2::TL_CLUSTERS][2][3][tc2::TW_KINDS];
+        static unsigned long long tile_ts[tc2::TL_CLUSTERS][tc2::TL_TILES];
+        static long long tile_clk[tc2::TL_CLUSTERS][tc2::TL_TILES];
         if (cudaStreamSynchronize(stream) == cudaSuccess &&
             cudaMemcpyFromSymbol(stamps, tc2::g_timeline, sizeof(stamps)) == cudaSuccess &&
+            cudaMemcpyFromSymbol(waits, tc2::g_waits, sizeof(waits)) == cudaSuccess &&
+            cudaMemcpyFromSymbol(tile_ts, tc2::g_tile_ts, sizeof(tile_ts)) == cudaSuccess &&
+            cudaMemcpyFromSymbol(tile_clk, tc2::g_tile_clk, sizeof(tile_clk)) == cudaSuccess &&
             cudaMemcpyFromSymbol(tiles, tc2::g_timeline_tiles, sizeof(tiles)) == cudaSuccess) {
             if (FILE *f = fopen(path, "ab")) {
                 const int head[4] = {n_clusters, decode ? 1 : 0, tc2::TL_SLOTS, tc2::TL_ITEMS};
                 fwrite(head, sizeof(head), 1, f);
                 fwrite(stamps, sizeof(stamps), 1, f);
                 fwrite(tiles, sizeof(tiles), 1, f);
+                fwrite(waits, sizeof(waits), 1, f);
+                fwrite(tile_ts, sizeof(tile_ts), 1, f);
+                fwrite(tile_clk, sizeof(tile_clk), 1, f);
                 fclose(f);
             }
             static const unsigned long long zero[tc2::TL_CLUSTERS][tc2::TL_SLOTS] = {};

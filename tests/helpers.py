@@ -41,8 +41,10 @@ def assert_O(got, want, bf16=True, what="O"):
         worst = float(excess.max()) if excess.size else -1.0
         assert worst <= 0 and rf <= O_REL_FRO, \
             f"{what}: max-abs {ma:.3e} exceeds 1e-2 + 2^-8|O| by {worst:.3e}; rel-Fro {rf:.3e} (<= {O_REL_FRO})"
-        if peak < 4.0:      # every value lies where the bf16 spacing is below 1e-2: the plain target applies
-            assert ma <= O_MAX_ABS, f"{what}: max-abs {ma:.3e} > {O_MAX_ABS} although max|O| = {peak:.3g} < 4"
+        if peak < 2.0:
+            # every value lies where rounding the OUTPUT to bf16 costs at most 2^-9 |O| < 4e-3, so the plain
+            # target applies (in [2, 4) that rounding alone may take 7.8e-3 of the 1e-2)
+            assert ma <= O_MAX_ABS, f"{what}: max-abs {ma:.3e} > {O_MAX_ABS} although max|O| = {peak:.3g} < 2"
     else:
         assert ma <= F32_MAX_ABS and rf <= F32_REL_FRO, \
             f"{what}: max-abs {ma:.3e} (<= {F32_MAX_ABS}), rel-Fro {rf:.3e} (<= {F32_REL_FRO})"

@@ -97,15 +97,17 @@ def test_balanced_schedule_properties_on_random_batches():
 
 
 def test_plan_of_the_headline_decode_configuration():
-    """B=128, H=128, Skv=4096: the suggested slab count selects the balanced runs merged in the attention
-    kernel, 28 tiles per CTA pair, a sequence cut at most once."""
+    """B=128, H=128, Skv=4096: one work item per sequence (the balanced runs would save four of 32 tiles per CTA
+    pair, the partial rows and merges they need cost more); forty such sequences with four slabs are handed out as
+    balanced runs merged in the attention kernel, a sequence cut into three pieces at most."""
     from flashdmla import _lib
     L = _lib.lib()
     splits = L.fdmla_decode_suggest_splits(128, 128, 4096, 576, 512, 64, 1)
-    mode, qmin, units = plan(L, 128, 128, 64, 64, splits)
-    assert (splits, mode, units) == (3, 2, 74) and qmin == 16
-    items, nts, q = walk([4096] * 128, 4096, units, qmin)
-    assert q == 28 and max(p for *_, p in items) == 2
+    assert splits == 1 and plan(L, 128, 128, 64, 64, splits)[0] == 0
+    mode, qmin, units = plan(L, 40, 64, 64, 64, 4)
+    assert (mode, units, qmin) == (2, 74, 8)
+    items, nts, q = walk([4096] * 40, 4096, units, qmin)
+    assert q == 9 and max(p for *_, p in items) == 3
     # few long sequences are cut many times: never merged by single thread blocks inside the attention kernel
     splits = L.fdmla_decode_suggest_splits(8, 128, 131072, 576, 512, 64, 1)
     mode, qmin, units = plan(L, 8, 128, 64, 2048, splits)

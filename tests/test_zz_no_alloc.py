@@ -44,14 +44,15 @@ def test_noalloc_decode_matches_the_ordinary_entry_point_twice(cuda):
     from oracle import dmla_oracle as orc
     L = _lib.lib()
     scale = 1 / math.sqrt(192)
-    ragged = torch.randint(500, 1025, (80,), generator=torch.Generator().manual_seed(9)).tolist()
+    ragged = torch.randint(2000, 4097, (40,), generator=torch.Generator().manual_seed(9)).tolist()
+    ragged[0] = 4096
     # first call: 3 splits, long ragged sequences; second call: a smaller problem with another
     # split count, so stale partials of the first call sit right where the second one works; third
-    # call: many short sequences, which the library hands out as balanced runs of tiles merged inside
+    # call: forty longer sequences, which the library hands out as balanced runs of tiles merged inside
     # the attention kernel - the schedule whose arrival counters have to start at zero although the
     # array still holds whatever the first two calls left there
     plans = []
-    for lens, H, splits, seed in (([1500, 64, 2100, 700, 129], 128, 3, 5), ([300, 1000], 64, 2, 6), (ragged, 64, 3, 7)):
+    for lens, H, splits, seed in (([1500, 64, 2100, 700, 129], 128, 3, 5), ([300, 1000], 64, 2, 6), (ragged, 64, 4, 7)):
         Q, pool, table, sl = _problem(lens, H, seed, cuda)
         plans.append(L.fdmla_decode_plan(len(lens), H, 576, 512, 64, table.shape[1], splits, 1, None, None))
         rc, O, m, l = _call_noalloc(L, Q, pool, table, sl, splits, scale)
