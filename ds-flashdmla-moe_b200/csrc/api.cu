@@ -138,8 +138,8 @@ int fdmla_get_backend(void) { return g_backend.load(); }
 int fdmla_set_single_cta(int on) { tensor_prefer_single_cta(on != 0); return FDMLA_OK; }
 const char *fdmla_last_kernel(void) { return t_last_kernel; }
 int fdmla_device_error_flag(int reset) {
-    const int fwd = tensor_error_flag(reset), bwd = bwd_tensor_error_flag(reset);
-    return fwd ? fwd : bwd;
+    const int fwd = tensor_error_flag(reset), bwd = bwd_tensor_error_flag(reset), gemm = gemm_error_flag(reset);
+    return fwd ? fwd : (bwd ? bwd : gemm);
 }
 
 int fdmla_fwd_cache_latent(const void *Q, const void *K_lat, void *O, float *m, float *l, int B,
@@ -299,6 +299,36 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_t
     if (merge_launch)
         rc = launch_merge(O_part, m_part, l_part, O, m, l, (long long)B * H, d_v, num_splits, dtype, st);
     return rc;
+}
+
+int fdmla_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
+                       long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
+                       int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
+                       int gated, void *stream) {
+    if (batch < 0 || M < 0 || N < 0 || K < 0 || lda <= 0 || ldb <= 0 || ldc <= 0 || a_rows <= 0 || b_rows <= 0 ||
+        a_brow < 0 || a_bcol < 0 || b_brow < 0 || b_bcol < 0 || c_brow < 0 || c_bcol < 0)
+        return FDMLA_ERR_INVALID;
+    if (batch == 0 || M == 0 || N == 0) return FDMLA_OK;
+    if (!A || !B || !C || (gated && !B2) || K == 0) return FDMLA_ERR_INVALID;
+    if (!tensor_kernels_allowed()) return FDMLA_ERR_UNSUPPORTED;
+    // every window must lie inside its tensor (a copy that starts outside would read another tensor's rows as zeros
+    // silently; a store outside would corrupt memory)
+    if ((long long)(batch - 1) * a_brow + M > a_rows || (long long)(batch - 1) * a_bcol + K > lda) return FDMLA_ERR_INVALID;
+    const long long b_need_rows = (long long)(batch - 1) * b_brow + (b_k_major ? N : K);
+    const long long b_need_cols = (long long)(batch - 1) * b_bcol + (b_k_major ? K : N);
+    if (b_need_rows > b_rows || b_need_cols > ldb) return FDMLA_ERR_INVALID;
+    if ((batch - 1) * c_bcol + N > ldc) return FDMLA_ERR_INVALID;
+    t_last_kernel = "tcgen05";
+    return launch_gemm_batched(A, B, B2, C, batch, M, N, K, a_rows, lda, a_brow, a_bcol, b_rows, ldb, b_brow, b_bcol,
+                               b_k_major, ldc, c_brow, c_bcol, gated, static_cast<cudaStream_t>(stream));
+}
+
+int fdmla_rope_rows(const void *x, long long ldx, void *y, long long ldy, const int32_t *pos, long long rows,
+                    int rows_per_pos, int d, float base, void *stream) {
+    if (rows < 0) return FDMLA_ERR_INVALID;
+    if (rows == 0) return FDMLA_OK;
+    if (!x || !y || !pos) return FDMLA_ERR_INVALID;
+    return launch_rope_rows(x, ldx, y, ldy, pos, rows, rows_per_pos, d, base, static_cast<cudaStream_t>(stream));
 }
 
 int fdmla_merge_lse(const float *O_part, const float *m_part, const float *l_part, void *O,

@@ -125,6 +125,14 @@ int launch_bwd_delta(const BwdProblem &p, int dtype, cudaStream_t stream);
 bool bwd_tensor_supported(const BwdProblem &p, int dtype, int grads_f32);
 int launch_bwd_tensor(const BwdProblem &p, cudaStream_t stream);
 int bwd_tensor_error_flag(int reset);
+// batched bf16 GEMM on tcgen05 (csrc/tc_gemm.cu) and the RoPE tail of the absorbed query
+int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
+                        long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
+                        int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
+                        int gated, cudaStream_t stream);
+int launch_rope_rows(const void *x, long long ldx, void *y, long long ldy, const int32_t *pos, long long rows,
+                     int rows_per_pos, int d, float base, cudaStream_t stream);
+int gemm_error_flag(int reset);
 // tcgen05 projections / weight-gradient partials for widths (128 -> 64) and (64 -> 128 transposed); they return
 // FDMLA_ERR_UNSUPPORTED for other shapes
 int launch_project_tensor(const void *X, const void *W, void *Y, long long rows, int d_in, int d_out, int w_transposed,

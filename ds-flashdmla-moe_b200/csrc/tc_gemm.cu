@@ -1,0 +1,315 @@
+// Batched bf16 GEMM on the sm_100a tensor cores (tcgen05 + TMA), for the GEMMs that sit either side of the
+// attention kernel and inside the MoE layer:
+//   * the absorbed query projection  Q'[n, h, :512] = q_nope[n, h, :] W_UK[h]^T     (batch = heads, B K-major)
+//   * the absorbed output projection o[n, h, :]     = O_lat[n, h, :] W_UV[h]       (batch = heads, B MN-major)
+//   * the expert MLPs of a MoE layer over padded packing: [E, capacity, d] x [E, d, d_ff] with the SwiGLU gate
+//     fused into the epilogue, and [E, capacity, d_ff] x [E, d_ff, d]            (batch = experts, B MN-major)
+// (README.md:16-20 of the reference names these steps; it ships no source for them.)
+//
+// C[b] (M x N) = A[b] (M x K) * B[b], fp32 accumulation, bf16 in and out.  Every operand is a window of a 2-D
+// row-major bf16 tensor: batch b of A starts at row b * a_brow, column b * a_bcol of its tensor (so a batch can run
+// down the rows - experts - or across the columns - heads of a [tokens, heads * width] activation), likewise B and C.
+// B is either K-major ([N, K] rows, the reduction index contiguous) or MN-major ([K, N] rows, the output column
+// contiguous).  Gated mode: the accumulator of a tile holds 128 columns of A*B next to the same 128 columns of A*B2
+// and the epilogue writes silu(A*B) .* (A*B2) (one [M x 128] tile of C).
+//
+// Persistent grid, one CTA per SM, 128 x 256 accumulator tiles (two of them in tensor memory, so the epilogue of one
+// tile runs under the main loop of the next), K in steps of 64 through a ring of four 48 KB stages filled by TMA in
+// the 128-byte swizzle.  Warp 0 issues the copies, warp 1 the MMAs (one elected lane of a converged warp each),
+// warps 2-5 read the accumulator (thread = row) and store bf16 rows.  Every wait is bounded; a wait that gives up
+// sets a flag that fdmla_device_error_flag reports (code 21-23) and the roles run out.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace fdmla {
+
+bool make_tensor_map_bf16(CUtensorMap *m, const void *base, long long rows, int cols, int box_rows);
+bool make_tensor_map_bf16_chunked(CUtensorMap *m, const void *base, long long rows, int cols, int box_rows, int box_chunks);
+
+namespace tcg {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 384
+constexpr int B_BYTES = BN * BK * 2;          // 32 768
+constexpr int STAGE = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE + 256;
+static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
+enum { ERR_PRODUCER = 21, ERR_MMA = 22, ERR_EPILOGUE = 23 };
+
+__device__ int g_gemm_error = 0;
+
+struct Problem {
+    int batch, M, N, K;                 // N: output columns per batch entry
+    int a_brow, a_bcol;                 // window of batch b in A's tensor: row b * a_brow, column b * a_bcol
+    int b_brow, b_bcol;                 // K-major: rows are output columns; MN-major: rows are the reduction index
+    long long c_brow, c_bcol, ldc;      // C element (b, m, n) = C[(b * c_brow + m) * ldc + b * c_bcol + n]
+    __nv_bfloat16 *C;
+    int b_k_major, gated;
+    int m_tiles, n_tiles;
+};
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmB2) {
+    using namespace ptx;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    int *err_slot = reinterpret_cast<int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto FULL = [&](int s) { return bar0 + 8u * s; };
+    auto EMPTY = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto ACC_FULL = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+    auto ACC_EMPTY = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        *err_slot = *reinterpret_cast<volatile int *>(&g_gemm_error);      // one reading for all roles
+        for (int s = 0; s < STAGES; ++s) { mbar_init(FULL(s), 1); mbar_init(EMPTY(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(ACC_FULL(a), 1); mbar_init(ACC_EMPTY(a), 128); }
+        fence_mbar_init();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const bool poisoned = *err_slot != 0;            // an earlier launch gave up a wait: do nothing until the flag is cleared
+
+    const int tiles_per_batch = p.m_tiles * p.n_tiles;
+    const long long n_tiles_total = poisoned ? 0 : (long long)p.batch * tiles_per_batch;
+    const int k_steps = p.K / BK;
+    const int out_cols = p.gated ? BN / 2 : BN;         // output columns of one tile
+    // tile -> (batch, m tile, n tile): the m tiles of one (batch, n tile) are neighbours, so CTAs that run at the same
+    // time share the B tile in L2
+    auto tile_coords = [&](long long tile, int &b, int &m0, int &n0) {
+        b = (int)(tile / tiles_per_batch);
+        const int r = (int)(tile - (long long)b * tiles_per_batch);
+        n0 = (r / p.m_tiles) * out_cols;
+        m0 = (r % p.m_tiles) * BM;
+    };
+
+    if (warp == 0) {
+        // ================================ TMA producer ================================
+        const bool elected = elect_one();
+        if (lane == 0) { prefetch_tmap(&tmA); prefetch_tmap(&tmB); if (p.gated) prefetch_tmap(&tmB2); }
+        bool ok = true;
+        int s = 0, use = 0;
+        for (long long tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
+            int b, m0, n0;
+            tile_coords(tile, b, m0, n0);
+            for (int kb = 0; kb < k_steps && ok; ++kb) {
+                if (use > 0) ok = mbar_wait(EMPTY(s), (use - 1) & 1);
+                if (ok && elected) {
+                    const uint32_t dstA = smem_u32(smem + s * STAGE), dstB = dstA + A_BYTES;
+                    mbar_arrive_expect_tx(FULL(s), STAGE);
+                    tma_load_2d(dstA, &tmA, b * p.a_bcol + kb * BK, b * p.a_brow + m0, FULL(s));
+                    if (p.b_k_major) {
+                        // [256 output columns x 64] K-major: rows of B's tensor are output columns
+                        if (!p.gated) {
+                            tma_load_2d(dstB, &tmB, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
+                        } else {
+                            tma_load_2d(dstB, &tmB, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
+                            tma_load_2d(dstB + B_BYTES / 2, &tmB2, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
+                        }
+                    } else {
+                        // [64 x 256 output columns] MN-major: four (gated: two and two) chunks of [64 rows x 128 B]
+                        const int chunk0 = (b * p.b_bcol + n0) >> 6;
+                        if (!p.gated) {
+                            tma_load_3d(dstB, &tmB, 0, b * p.b_brow + kb * BK, chunk0, FULL(s));
+                        } else {
+                            tma_load_3d(dstB, &tmB, 0, b * p.b_brow + kb * BK, chunk0, FULL(s));
+                            tma_load_3d(dstB + B_BYTES / 2, &tmB2, 0, b * p.b_brow + kb * BK, chunk0, FULL(s));
+                        }
+                    }
+                }
+                if (++s == STAGES) { s = 0; ++use; }
+            }
+        }
+        if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, ERR_PRODUCER);
+        __syncwarp();
+    } else if (warp == 1) {
+        // ================================ MMA issuer ==================================
+        const bool elected = elect_one();
+        const uint32_t idesc = make_idesc_bf16(BM, BN, 0, p.b_k_major ? 0 : 1);
+        bool ok = true;
+        int s = 0;
+        uint32_t ph = 0;
+        int n_done = 0;                              // tiles this CTA has issued
+        for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++n_done) {
+            if (!__all_sync(0xffffffffu, ok)) break;
+            const int acc = n_done & 1;
+            if (n_done >= 2) {
+                ok = ok && mbar_wait(ACC_EMPTY(acc), ((n_done >> 1) - 1) & 1);     // the epilogue has read this accumulator
+                tc_fence_after_sync();
+            }
+            for (int kb = 0; kb < k_steps; ++kb) {
+                ok = ok && mbar_wait(FULL(s), ph);
+                tc_fence_after_sync();
+                if (elected) {
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t da = make_smem_desc(a_addr + k * 32, 16, 1024, kLayoutSw128);
+                        const uint64_t db = p.b_k_major ? make_smem_desc(b_addr + k * 32, 16, 1024, kLayoutSw128)
+                                                        : make_smem_desc(b_addr + k * 2048, 8192, 1024, kLayoutSw128);
+                        mma_bf16_ss(tmem + acc * BN, da, db, idesc, (kb | k) != 0);
+                    }
+                    mma_commit(EMPTY(s));
+                    if (kb == k_steps - 1) mma_commit(ACC_FULL(acc));
+                }
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+        if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, ERR_MMA);
+        __syncwarp();
+    } else {
+        // ================================ epilogue ====================================
+        const int L = (warp & 3) * 32 + lane;                      // TMEM lane = row of the tile
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        bool ok = true;
+        int n_done = 0;
+        for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++n_done) {
+            int b, m0, n0;
+            tile_coords(tile, b, m0, n0);
+            const int acc = n_done & 1;
+            if (ok) ok = mbar_wait(ACC_FULL(acc), (n_done >> 1) & 1);
+            tc_fence_after_sync();
+            const int m = m0 + L;
+            __nv_bfloat16 *crow = p.C + ((long long)b * p.c_brow + m) * p.ldc + (long long)b * p.c_bcol + n0;
+            const uint32_t t0 = tmem + lane_base + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < out_cols / 32; ++c) {
+                uint32_t r[32], g[32];
+                if (ok) {
+                    tmem_ld32(t0 + c * 32, r);
+                    if (p.gated) tmem_ld32(t0 + BN / 2 + c * 32, g);
+                    tmem_wait_ld();
+                }
+                if (!ok || m >= p.M || n0 + c * 32 >= p.N) continue;
+#pragma unroll
+                for (int j = 0; j < 32; j += 16) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        float x0 = __uint_as_float(r[j + 2 * e]), x1 = __uint_as_float(r[j + 2 * e + 1]);
+                        if (p.gated) {
+                            x0 = silu(x0) * __uint_as_float(g[j + 2 * e]);
+                            x1 = silu(x1) * __uint_as_float(g[j + 2 * e + 1]);
+                        }
+                        __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                        w[e] = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                    st_global_v8(crow + c * 32 + j, w);
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(ACC_EMPTY(acc));                           // 128 arrivals free the accumulator
+        }
+        if (!ok) atomicCAS(&g_gemm_error, 0, ERR_EPILOGUE);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace tcg
+
+int gemm_error_flag(int reset) {
+    int v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, tcg::g_gemm_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(tcg::g_gemm_error, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
+    return v;
+}
+
+// Arguments as in fdmla_gemm_batched (include/flashdmla.h).
+int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
+                        long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
+                        int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
+                        int gated, cudaStream_t stream) {
+    using namespace tcg;
+    if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return FDMLA_OK;
+    if (K % BK != 0 || N % 64 != 0 || lda % 8 != 0 || ldb % 64 != 0 || ldc % 16 != 0) return FDMLA_ERR_UNSUPPORTED;
+    if (a_bcol % 8 != 0 || b_bcol % 64 != 0 || c_bcol % 16 != 0) return FDMLA_ERR_UNSUPPORTED;
+    if (gated && (N % 128 != 0 || !B2)) return FDMLA_ERR_UNSUPPORTED;
+    if (lda > 2147483647LL || ldb > 2147483647LL || a_rows > 2147483647LL || b_rows > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(B2)) & 15) return FDMLA_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(C) & 31) return FDMLA_ERR_UNSUPPORTED;
+    Problem p{};
+    p.batch = batch; p.M = M; p.N = N; p.K = K;
+    p.a_brow = a_brow; p.a_bcol = a_bcol; p.b_brow = b_brow; p.b_bcol = b_bcol;
+    p.c_brow = c_brow; p.c_bcol = c_bcol; p.ldc = ldc; p.C = static_cast<__nv_bfloat16 *>(C);
+    p.b_k_major = b_k_major ? 1 : 0; p.gated = gated ? 1 : 0;
+    const int out_cols = gated ? BN / 2 : BN;
+    p.m_tiles = (M + BM - 1) / BM;
+    p.n_tiles = (N + out_cols - 1) / out_cols;
+    CUtensorMap tmA, tmB, tmB2;
+    if (!make_tensor_map_bf16(&tmA, A, a_rows, (int)lda, BM)) return FDMLA_ERR_CUDA;
+    const int b_box = gated ? BN / 2 : BN;          // output columns brought by one copy
+    if (b_k_major) {
+        if (!make_tensor_map_bf16(&tmB, B, b_rows, (int)ldb, b_box)) return FDMLA_ERR_CUDA;
+        tmB2 = tmB;
+        if (gated && !make_tensor_map_bf16(&tmB2, B2, b_rows, (int)ldb, b_box)) return FDMLA_ERR_CUDA;
+    } else {
+        if (!make_tensor_map_bf16_chunked(&tmB, B, b_rows, (int)ldb, BK, b_box / 64)) return FDMLA_ERR_CUDA;
+        tmB2 = tmB;
+        if (gated && !make_tensor_map_bf16_chunked(&tmB2, B2, b_rows, (int)ldb, BK, b_box / 64)) return FDMLA_ERR_CUDA;
+    }
+    if (cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        return FDMLA_ERR_CUDA;
+    const long long tiles = (long long)batch * p.m_tiles * p.n_tiles;
+    int dev = 0, sms = kNumSMs;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    gemm_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p, tmA, tmB, tmB2);
+    return check_launch();
+}
+
+// y[r, 0:d] = rotary(x[r, 0:d], pos[r / rows_per_pos]) on pairs (2i, 2i+1) with angle pos * base^(-2i/d); x and y are
+// rows of wider tensors (row strides ldx, ldy elements).  The 64-wide RoPE tail of the absorbed query: read from the
+// per-head query, written next to the 512 latent columns the GEMM above produced.
+__global__ void rope_rows_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, __nv_bfloat16 *__restrict__ y, long long ldy,
+                                 const int32_t *__restrict__ pos, long long rows, int rows_per_pos, int d, float log2_base) {
+    const int half = d >> 1;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * half) return;
+    const long long r = idx / half;
+    const int i = (int)(idx - r * half);
+    const float inv = exp2f(-log2_base * (2.f * i) / d);
+    float sn, cs;
+    sincosf((float)pos[r / rows_per_pos] * inv, &sn, &cs);
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162 *>(x + r * ldx + 2 * i);
+    const float x0 = __low2float(v), x1 = __high2float(v);
+    *reinterpret_cast<__nv_bfloat162 *>(y + r * ldy + 2 * i) = __floats2bfloat162_rn(x0 * cs - x1 * sn, x0 * sn + x1 * cs);
+}
+
+int launch_rope_rows(const void *x, long long ldx, void *y, long long ldy, const int32_t *pos, long long rows,
+                     int rows_per_pos, int d, float base, cudaStream_t stream) {
+    if (rows <= 0) return FDMLA_OK;
+    if (d <= 0 || (d & 1) || rows_per_pos <= 0 || (ldx & 1) || (ldy & 1) || base <= 0.f) return FDMLA_ERR_INVALID;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3) return FDMLA_ERR_UNSUPPORTED;
+    const long long n = rows * (d >> 1);
+    const int threads = 256;
+    rope_rows_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(x), ldx, static_cast<__nv_bfloat16 *>(y), ldy, pos, rows, rows_per_pos, d, log2f(base));
+    return check_launch();
+}
+
+}  // namespace fdmla

@@ -10,9 +10,12 @@ the kernel work on the 576-wide latent rows while the caller keeps standard mult
                   = (q^N_h W_UK[h]^T) . c_j + rope(q^R_h) . k^R_j      <- absorbed: Q' = [q^N W_UK^T | rope(q^R)]
     out_h = (sum_j p_hj c_j) W_UV[h]                                   <- kernel returns sum_j p c_j (512 wide)
 
-The projections are plain batched GEMMs (`torch.matmul`, i.e. the vendor library); the
-attention itself is `PagedLatentCache.decode`.  `reference_decode` restates the same block
-with explicit per-head keys and values in fp32 for the tests.
+The two absorbed projections - one small GEMM per head, directly before and after the attention
+kernel - run on the library's own tensor-core GEMM (`flashdmla.gemm.absorb_query`, which also
+writes the RoPE tail of Q', and `flashdmla.gemm.project_out`; CUDA bf16 tensors only, like the
+attention kernel between them); the dense projections with the model-wide weights (`W_Q`, `W_DKV`, `W_KR`, `W_O`) are plain
+library GEMMs.  The attention itself is `PagedLatentCache.decode`.  `reference_decode` restates
+the same block with explicit per-head keys and values in fp32 for the tests.
 """
 from __future__ import annotations
 
@@ -64,6 +67,13 @@ class AbsorbedMLA:
         """h [n, d_model], pos [n] -> Q' [n, H, d_lat + d_rope]."""
         n = h.shape[0]
         q = (h @ self.W_Q).view(n, self.H, self.d_nope + self.d_rope)
+        from . import gemm
+        return gemm.absorb_query(q.contiguous(), self.W_UK, pos, self.d_nope)      # CUDA bf16 only, like the attention
+
+    def absorbed_query_torch(self, h: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """The same Q' written with torch operators, any device and dtype: what the tests of the algebra compare with."""
+        n = h.shape[0]
+        q = (h @ self.W_Q).view(n, self.H, self.d_nope + self.d_rope)
         q_lat = torch.einsum("nhd,hld->nhl", q[..., : self.d_nope], self.W_UK)
         q_rope = rope(q[..., self.d_nope:], pos[:, None].expand(n, self.H))
         return torch.cat((q_lat, q_rope), dim=-1).contiguous()
@@ -73,7 +83,8 @@ class AbsorbedMLA:
         pos = torch.tensor([cache.length(s) for s in slots], device=h.device)
         cache.append(slots, self.cache_rows(h[:, None, :], pos[:, None]))
         o_lat, _, _ = cache.decode(self.absorbed_query(h, pos), slots, self.d_lat, self.scale)
-        o = torch.einsum("nhl,hlv->nhv", o_lat, self.W_UV)
+        from . import gemm
+        o = gemm.project_out(o_lat.contiguous(), self.W_UV)
         return o.reshape(h.shape[0], self.H * self.d_vhead) @ self.W_O
 
     # ---- the same block without absorption, fp32, for tests --------------------------------

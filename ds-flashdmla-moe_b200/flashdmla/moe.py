@@ -104,6 +104,16 @@ def swiglu_mlp(x, W1, W3, W2):
     return (torch.nn.functional.silu(x @ W1) * (x @ W3)) @ W2
 
 
+def _expert_mlp_batched(xb, W1, W3, W2):
+    """[E, rows, d] through every expert's SwiGLU MLP on the library's tensor-core GEMM (gate fused into the first
+    GEMM's epilogue).  On a GPU there is no other path: a dtype or width the kernel does not take is an error.  CPU
+    tensors - the exchange tests run the host logic of the expert-parallel forward on gloo - use torch.bmm."""
+    if xb.is_cuda:
+        from . import gemm
+        return gemm.expert_mlp(xb.contiguous(), W1.contiguous(), W3.contiguous(), W2.contiguous())
+    return torch.bmm(torch.nn.functional.silu(torch.bmm(xb, W1)) * torch.bmm(xb, W3), W2)
+
+
 def expert_ranges(n_experts: int, world: int):
     """Experts of every rank as (first, count): contiguous, the remainder to the first ranks."""
     base, rem = divmod(n_experts, world)
@@ -165,7 +175,7 @@ class MoEFFN:
             check(_lib.lib().fdmla_moe_scatter(_ptr(x.contiguous()), _ptr(pos), _ptr(xp), x.shape[0], self.k, x.shape[1],
                                                _dtype_code(x), _stream(x)), "fdmla_moe_scatter")
         xb = xp.view(self.E, cap, x.shape[1])
-        yb = torch.bmm(torch.nn.functional.silu(torch.bmm(xb, self.W1)) * torch.bmm(xb, self.W3), self.W2)
+        yb = _expert_mlp_batched(xb, self.W1, self.W3, self.W2)
         sh = swiglu_mlp(x, *self.shared) if self.shared is not None else None
         return combine(yb.view(self.E * cap, x.shape[1]), pos, w, sh)
 
@@ -200,7 +210,7 @@ class MoEFFN:
         xb = x_in.view(world, n_loc, cap, d).permute(1, 0, 2, 3).reshape(n_loc, world * cap, d)
         lo = rank * n_loc
         W1, W3, W2 = self.W1[lo:lo + n_loc], self.W3[lo:lo + n_loc], self.W2[lo:lo + n_loc]
-        yb = torch.bmm(torch.nn.functional.silu(torch.bmm(xb, W1)) * torch.bmm(xb, W3), W2)
+        yb = _expert_mlp_batched(xb, W1, W3, W2)
         y_out = yb.view(n_loc, world, cap, d).permute(1, 0, 2, 3).contiguous().view(self.E * cap, d)
         y_back = torch.empty_like(y_out)
         dist.all_to_all_single(y_back, y_out, group=group)

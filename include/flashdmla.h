@@ -70,8 +70,8 @@ int fdmla_set_single_cta(int on);
 const char *fdmla_last_kernel(void);
 
 /* Device-side error flag of the tensor-core kernels on the current device:
- * 0 = none; 1..3 and 11..17 = a bounded wait inside a kernel gave up (which role
- * and which wait); 4 = a page id outside [0, num_pages) was read from a page
+ * 0 = none; 1..3, 11..17 and 21..23 = a bounded wait inside a kernel gave up (which
+ * kernel, role and wait); 4 = a page id outside [0, num_pages) was read from a page
  * table, or a sequence length outside [0, max_pages * page_size] was clamped.
  * Synchronises the device; reset != 0 clears the flag.  Returns -1 if the flag
  * cannot be read.
@@ -225,6 +225,40 @@ int fdmla_merge_lse_strided(const float *O_part, const float *m_part,
                             long long rows, int d_v, int num_parts,
                             long long part_stride_o, long long part_stride_ml,
                             int out_dtype, void *stream);
+
+/*
+ * Batched bf16 GEMM on the tensor cores, fp32 accumulation: C[b] (M x N) = A[b] (M x K) * B[b] for b < batch.
+ * It serves the GEMMs either side of the attention kernel that the reference's README.md:16-20 describes and
+ * ships no source for: the "absorbed" query and output projections of an MLA block (batch = heads) and the
+ * expert MLPs of the MoE layer over padded packing (batch = experts).
+ *   Every operand is a window of a 2-D row-major bf16 tensor with `ld*` elements per row: batch entry b of A
+ *   starts at row b * a_brow and column b * a_bcol of a tensor of a_rows rows, so that a batch may run down the
+ *   rows (experts) or across the columns (heads of a [tokens, heads * width] activation); B and C likewise.
+ *   b_k_major != 0: B's tensor holds [N, K] windows (rows = output columns, the reduction index contiguous);
+ *   b_k_major == 0: [K, N] windows (rows = reduction index, the output column contiguous).
+ *   gated != 0: C = silu(A * B) .* (A * B2) (the SwiGLU gate of an expert MLP in the GEMM's epilogue); B2 has
+ *   B's geometry.  B2 is ignored otherwise and may be NULL.
+ *   Limits: K % 64 == 0, N % 64 == 0 (gated: % 128), lda % 8 == 0, ldb % 64 == 0, ldc % 16 == 0, a_bcol % 8 == 0,
+ *   b_bcol % 64 == 0, c_bcol % 16 == 0, A, B 16-byte and C 32-byte aligned; FDMLA_ERR_UNSUPPORTED otherwise, and
+ *   when the kernel family is forced to the portable one (there is no CUDA-core GEMM in this library).
+ *   Windows that do not fit their tensors are refused (FDMLA_ERR_INVALID).
+ */
+int fdmla_gemm_batched(const void *A, const void *B, const void *B2, void *C,
+                       int batch, int M, int N, int K, long long a_rows,
+                       long long lda, int a_brow, int a_bcol, long long b_rows,
+                       long long ldb, int b_brow, int b_bcol, int b_k_major,
+                       long long ldc, long long c_brow, long long c_bcol,
+                       int gated, void *stream);
+
+/*
+ * Rotary embedding of `rows` bf16 rows of width d that sit inside wider tensors (row strides ldx, ldy elements):
+ * y[r, 2i], y[r, 2i+1] = rotation of x[r, 2i], x[r, 2i+1] by the angle pos[r / rows_per_pos] * base^(-2i/d).
+ * The RoPE tail of the absorbed query: read from the per-head query, written next to the 512 latent columns
+ * that fdmla_gemm_batched produced (README.md:16; no source in the reference).
+ */
+int fdmla_rope_rows(const void *x, long long ldx, void *y, long long ldy,
+                    const int32_t *pos, long long rows, int rows_per_pos, int d,
+                    float base, void *stream);
 
 /*
  * On-the-fly DMLA backward.  Inputs of the forward plus its outputs O, m, l

@@ -14,7 +14,7 @@ def test_absorption_is_an_identity_cpu():
     hs = torch.randn(T, 96, generator=g)
     rows = blk.cache_rows(hs[None], torch.arange(T)[None])[0]            # [T, 40]
     h = hs[-1]
-    Qp = blk.absorbed_query(h[None], torch.tensor([T - 1]))[0]           # [H, 40]
+    Qp = blk.absorbed_query_torch(h[None], torch.tensor([T - 1]))[0]     # [H, 40]
     s = (Qp @ rows.T) * blk.scale
     p = torch.softmax(s, dim=-1)
     o_lat = p @ rows[:, :32]
@@ -45,6 +45,9 @@ def test_absorbed_decode_step_matches_per_head_attention(cuda):
         cache.append([s], blk.cache_rows(h, torch.arange(n, device=cuda)[None]))
     for step in range(3):                                                # three decode steps
         h = (torch.randn(3, 256, generator=g) * 0.5).to(torch.bfloat16).to(cuda)
+        pos = torch.tensor([cache.length(s) for s in slots], device=cuda)
+        Qk, Qt = blk.absorbed_query(h, pos), blk.absorbed_query_torch(h, pos)     # the GEMM + RoPE kernels against torch
+        assert (Qk.float() - Qt.float()).abs().max() <= 2e-2 * Qt.float().abs().max()
         out = blk.decode(cache, slots, h)
         assert flashdmla.last_kernel() == "tcgen05"
         rows = cache.gather(slots, max(lens) + step + 1)
