@@ -261,6 +261,10 @@ def main():
                     help="B,H,S of the prefill measurement (default 4,128,8192); a reduced shape is used for ncu captures")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill measurement (profiling aid)")
     ap.add_argument("--only-moe", action="store_true", help="run only the MoE plumbing measurement (profiling aid)")
+    ap.add_argument("--only-gemm", action="store_true", help="run only the batched-GEMM measurement (profiling aid)")
+    ap.add_argument("--gemm-experts", type=int, default=64, help="experts of the GEMM measurement (fewer for ncu captures)")
+    ap.add_argument("--kernel-launches", type=int, default=200,
+                    help="launches behind the kernel-only median timings (fewer for ncu launch lists)")
     ap.add_argument("--batch", type=int, default=0,
                     help="decode sequences per GPU (default 128); smaller values give the reduced case used for ncu captures")
     args = ap.parse_args()
@@ -293,6 +297,13 @@ def main():
         pf = bench_prefill(dev, rank, world, tf_burst, tf_sust)
         if rank == 0:
             print(json.dumps({"prefill": pf, "device_error_flag": flashdmla.device_error_flag()}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.only_gemm:
+        if rank == 0:
+            print(json.dumps({"gemm": bench_gemm(dev, tf_burst, hbm_peak, E=args.gemm_experts),
+                              "device_error_flag": flashdmla.device_error_flag()}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -353,17 +364,17 @@ def main():
                                             ptr(mp), ptr(lp), B, H, D_QK, D_V, PAGE, SKV // PAGE, pool.shape[0], splits, 0,
                                             -1, SCALE, _lib.BF16, stream), "fdmla_decode_paged")
         return f
-    k_ms = median_launch_ms(kernel_call(table))
+    k_ms = median_launch_ms(kernel_call(table), launches=args.kernel_launches)
     # control: the same launch with every sequence's page table aliased onto the pages of 8 sequences
     # (38 MB of distinct cache rows, resident in L2), i.e. the kernel with HBM taken out of the picture
     alias_table = table[:8].repeat((B + 7) // 8, 1)[:B].contiguous()
-    k_l2_ms = median_launch_ms(kernel_call(alias_table))
+    k_l2_ms = median_launch_ms(kernel_call(alias_table), launches=args.kernel_launches)
     achieved = DECODE_BYTES / (k_ms * 1e-3) / 1e9
 
     e2e = bench_e2e(dev, world, Q, pool, table, seqlens, splits, ws, args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
-    prefill = on_the_fly = moe_plumbing = long_context = context_prefill = None
+    prefill = on_the_fly = moe_plumbing = long_context = context_prefill = gemm_line = None
     if not args.no_prefill:
         prefill = bench_prefill(dev, rank, world, tf_burst, tf_sust)
         if world > 1:
@@ -374,6 +385,7 @@ def main():
         if rank == 0:
             on_the_fly = bench_on_the_fly(dev, tf_burst)
             moe_plumbing = bench_moe_plumbing(dev, hbm_peak)
+            gemm_line = bench_gemm(dev, tf_burst, hbm_peak)
 
     err = flashdmla.device_error_flag()
     if rank == 0:
@@ -394,7 +406,7 @@ def main():
                                            "scaled by the number of sequences",
                          "peak_source": peak_src,
                          "kernel": "fwd_tc2_kernel (2-CTA tcgen05 split-KV decode)", "kernel_ms": k_ms,
-                         "kernel_ms_method": "median of 200 back-to-back C-ABI calls, one CUDA event between calls",
+                         "kernel_ms_method": f"median of {args.kernel_launches} back-to-back C-ABI calls, one CUDA event between calls",
                          "algorithmic_bytes": DECODE_BYTES, "tensor_tflops": DECODE_FLOP / (k_ms * 1e-3) / 1e12,
                          "kernel_ms_l2_resident_control": k_l2_ms,
                          "tiles_per_pair_max": tiles_per_pair_max, "pairs": n_units, "pairs_idle_frac": pairs_idle_frac,
@@ -405,6 +417,7 @@ def main():
             "context_parallel_prefill": context_prefill,
             "on_the_fly": on_the_fly,
             "moe_plumbing": moe_plumbing,
+            "gemm": gemm_line,
             "device_error_flag": err,
         }
         if cpu is not None:
@@ -699,6 +712,63 @@ def bench_on_the_fly(dev, tf_peak, iters=5):
     return out
 
 
+def bench_gemm(dev, tf_burst, hbm_peak, E=64):
+    """The library's batched tensor-core GEMM on its three uses: the expert MLPs of a MoE layer over padded packing
+    (E=64 experts x 640 rows, d=4096, d_ff=1024: gate+up GEMM with the SwiGLU gate in its epilogue, then the down
+    GEMM), with the same arithmetic on the vendor library's batched GEMM beside it for scale, and the absorbed
+    query / output projections of an MLA block at the decode batch (n=128 tokens, H=128 heads; replayed from a CUDA
+    graph, because one launch is shorter than a Python call)."""
+    from flashdmla import gemm
+    g = torch.Generator(device=dev).manual_seed(5)
+    mk = lambda *sh, std=0.1: (torch.randn(*sh, generator=g, device=dev) * std).to(torch.bfloat16)
+    rows, d, f = 640, 4096, 1024
+    xb, W1, W3, W2 = mk(E, rows, d), mk(E, d, f, std=0.02), mk(E, d, f, std=0.02), mk(E, f, d, std=0.02)
+    h = torch.empty(E, rows, f, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(E, rows, d, dtype=torch.bfloat16, device=dev)
+    g1 = lambda: gemm.gemm_batched(xb.view(E * rows, d), W1.view(E * d, f), h.view(E * rows, f), E, rows, f, d,
+                                   a_brow=rows, b_brow=d, c_brow=rows, gate=W3.view(E * d, f))
+    g2 = lambda: gemm.gemm_batched(h.view(E * rows, f), W2.view(E * f, d), y.view(E * rows, d), E, rows, d, f,
+                                   a_brow=rows, b_brow=f, c_brow=rows)
+    t1, t2 = median_launch_ms(g1, launches=20, warmup=3), median_launch_ms(g2, launches=20, warmup=3)
+    lib_ms = median_launch_ms(lambda: torch.bmm(torch.nn.functional.silu(torch.bmm(xb, W1)) * torch.bmm(xb, W3), W2),
+                              launches=20, warmup=3)
+    fl1, fl2 = 2.0 * E * rows * d * 2 * f, 2.0 * E * rows * f * d
+    del xb, W1, W3, W2, h, y
+    n, Hh = 128, 128
+    q, WUK, WUV, o_lat = mk(n, Hh, 192), mk(Hh, 512, 128), mk(Hh, 512, 128), mk(n, Hh, 512)
+    Qo = torch.empty(n, Hh, 576, dtype=torch.bfloat16, device=dev)
+    oo = torch.empty(n, Hh, 128, dtype=torch.bfloat16, device=dev)
+    ga = lambda: gemm.gemm_batched(q.view(n, Hh * 192), WUK.view(Hh * 512, 128), Qo.view(n, Hh * 576), Hh, n, 512, 128,
+                                   a_bcol=192, b_brow=512, b_k_major=True, c_bcol=576)
+    gp = lambda: gemm.gemm_batched(o_lat.view(n, Hh * 512), WUV.view(Hh * 512, 128), oo.view(n, Hh * 128), Hh, n, 128, 512,
+                                   a_bcol=512, b_brow=512, c_bcol=128)
+
+    def graph_ms(fn, reps=20):
+        st = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(st):
+            fn()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=st):
+                for _ in range(reps):
+                    fn()
+        torch.cuda.synchronize()
+        return median_launch_ms(gr.replay, launches=10, warmup=2) / reps
+    ta, tp = graph_ms(ga), graph_ms(gp)
+    ba, bp = (n * Hh * 128 + Hh * 512 * 128 + n * Hh * 512) * 2, (n * Hh * 512 + Hh * 512 * 128 + n * Hh * 128) * 2
+    return {"kernel": "tcg::gemm_kernel (tcgen05, TMA ring of 4 x 48 KB, 128 x 256 tiles, two accumulators in tensor memory)",
+            "expert_mlp_workload": f"E={E} x {rows} rows, d={d}, d_ff={f}, bf16 (padded packing of T=4096, top-8, capacity 1.25)",
+            "gate_up_gemm_ms": t1, "gate_up_gemm_tflops": fl1 / (t1 * 1e-3) / 1e12, "down_gemm_ms": t2,
+            "down_gemm_tflops": fl2 / (t2 * 1e-3) / 1e12,
+            "expert_mlp_tflops": (fl1 + fl2) / ((t1 + t2) * 1e-3) / 1e12,
+            "expert_mlp_frac_of_measured_bf16_peak": (fl1 + fl2) / ((t1 + t2) * 1e-3) / 1e12 / tf_burst,
+            "vendor_library_same_arithmetic_ms": lib_ms, "vendor_library_tflops": (fl1 + fl2) / (lib_ms * 1e-3) / 1e12,
+            "absorbed_query_gemm_us": ta * 1e3, "absorbed_output_gemm_us": tp * 1e3,
+            "absorbed_query_gbs_l2_resident": ba / (ta * 1e-3) / 1e9, "absorbed_output_gbs_l2_resident": bp / (tp * 1e-3) / 1e9,
+            "absorbed_workload": f"n={n} tokens, H={Hh}: [n,128]x[128,512] and [n,512]x[512,128] per head, CUDA-graph replay, "
+                                 f"operands resident in L2 (42 MB)"}
+
+
 def bench_moe_plumbing(dev, hbm_peak, iters=5):
     """The MoE kernels around the expert GEMMs at T=4096 tokens, E=256 experts, top-8, d=7168 bf16 (the shape of a
     DeepSeek-V3 MoE layer; capacity factor 1.25): gate, packing, row gather, weighted combine.  Algorithmic bytes:
@@ -730,7 +800,7 @@ def bench_moe_plumbing(dev, hbm_peak, iters=5):
     scatter_ms = t_of(lambda: moe.scatter(x, pos, perm.shape[0]))
     comb_ms = t_of(lambda: moe.combine(xp, pos, w, sh))
     gb = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9
-    # a whole layer (padded packing, expert MLPs as three batched library GEMMs, shared expert), smaller model
+    # a whole layer (padded packing, expert MLPs on the library's batched tensor-core GEMM, shared expert), smaller model
     layer = moe.MoEFFN(d_model=4096, d_ff=1024, n_experts=64, top_k=8, capacity_factor=1.25, device=dev, seed=1)
     xl = (torch.randn(T, 4096, generator=g, device=dev) * 0.1).to(torch.bfloat16)
     layer_ms = t_of(lambda: layer.forward_batched(xl))
