@@ -1,6 +1,6 @@
 """Build libflashdmla.so (sm_100a only) in-tree with nvcc.
 
-    python ds-flashdmla-moe_b200/build.py [--force] [--verbose] [--timeline]
+    python ds-flashdmla-moe_b200/build.py [--force] [--verbose] [--timeline [--ablate BITS]]
 
 Every .cu under csrc/ is compiled with
 `-gencode arch=compute_100a,code=sm_100a -lineinfo` and linked into
@@ -11,8 +11,12 @@ a machine without a GPU driver (symbol checks, CPU-only test runs).
 --timeline builds a second library, flashdmla/libflashdmla_timeline.so, with
 -DFDMLA_TIMELINE: the 2-CTA forward kernel then stamps what every CTA pair does
 with the global timer and the launcher appends the stamps of every launch to
-the file named by FDMLA_TIMELINE_FILE (select the library with FLASHDMLA_LIB).
-A development aid; the ordinary library contains none of it.
+the file named by FDMLA_TIMELINE_FILE (select the library with FLASHDMLA_LIB;
+timeline_report.py beside this file runs a decode launch that way and prints the
+summary).  --ablate BITS (with --timeline) builds libflashdmla_timeline_ablBITS.so,
+in which that kernel leaves out one stage of its pipeline - 1: the K/V copies, 2:
+the softmax arithmetic, 4: the MMAs - so that the cost of the rest can be timed;
+its results are garbage.  Development aids; the ordinary library contains none of it.
 """
 from __future__ import annotations
 
@@ -43,10 +47,11 @@ def _newest_header() -> float:
     return max(os.path.getmtime(h) for h in hs)
 
 
-def build(force: bool = False, verbose: bool = False, timeline: bool = False) -> str:
-    obj_dir = OBJ + "_timeline" if timeline else OBJ
-    out = OUT.replace(".so", "_timeline.so") if timeline else OUT
-    extra = ["-DFDMLA_TIMELINE"] if timeline else []
+def build(force: bool = False, verbose: bool = False, timeline: bool = False, ablate: int = 0) -> str:
+    tag = ("_timeline" + (f"_abl{ablate}" if ablate else "")) if timeline else ""
+    obj_dir = OBJ + tag
+    out = OUT.replace(".so", tag + ".so")
+    extra = (["-DFDMLA_TIMELINE"] + ([f"-DFDMLA_ABLATE={ablate}"] if ablate else [])) if timeline else []
     os.makedirs(obj_dir, exist_ok=True)
     hdr = _newest_header()
     jobs = []
@@ -75,4 +80,5 @@ def build(force: bool = False, verbose: bool = False, timeline: bool = False) ->
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, timeline="--timeline" in sys.argv))
+    abl = int(sys.argv[sys.argv.index("--ablate") + 1]) if "--ablate" in sys.argv else 0
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, timeline="--timeline" in sys.argv, ablate=abl))
