@@ -30,8 +30,10 @@ namespace fdmla {
 
 __device__ int g_tc_error = 0;   // first time-out code seen by any CTA (0 = none)
 
-template <int NQC_, int NVC_, int T_, int STAGES_, bool SEPV_, int VSPLIT_>
+template <int NQC_, int NVC_, int T_, int STAGES_, bool SEPV_, int VSPLIT_, int NSBUF_ = 2, int CTAS_PER_SM_ = 1>
 struct TcCfg {
+    static constexpr int NSBUF = NSBUF_;    // S accumulators in tensor memory (2: Q K^T of the next tile runs under the softmax)
+    static constexpr int CTAS_PER_SM = CTAS_PER_SM_;   // CTAs meant to share an SM (launch bound; shared and tensor memory must fit)
     static constexpr int NQC = NQC_;        // 64-column chunks of d_qk
     static constexpr int NVC = NVC_;        // 64-column chunks of d_v owned by one CTA
     static constexpr int T = T_;            // keys per tile
@@ -49,13 +51,18 @@ struct TcCfg {
     static constexpr int P_SBO = (T / 8) * 128;   // 8-row group stride of the un-swizzled P tile
     static constexpr int O_COLS = NVC * 64;
     static constexpr int S_COL0 = O_COLS;
-    static constexpr int TMEM_COLS = (O_COLS + 2 * T) <= 128 ? 128 : ((O_COLS + 2 * T) <= 256 ? 256 : 512);
+    static constexpr int TMEM_COLS = (O_COLS + NSBUF * T) <= 128 ? 128 : ((O_COLS + NSBUF * T) <= 256 ? 256 : 512);
     static constexpr int NBARS = 1 + 2 * STAGES + 1 + 2 + 2 + 1 + 1;
-    static constexpr int SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + NBARS * 8 + 16;
+    // room to round the dynamic shared memory up to 1 KB; two CTAs per SM only fit with 896 B of it, which is enough
+    // for a base that is 128-byte aligned (the kernel checks and reports instead of running past its allocation)
+    static constexpr int ALIGN_SLACK = CTAS_PER_SM > 1 ? 896 : 1024;
+    static constexpr int SMEM_BYTES = ALIGN_SLACK + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + NBARS * 8 + 16;
     static constexpr int D_QK = NQC * 64;
     static constexpr int D_V = NVC * 64 * VSPLIT;
-    static_assert(O_COLS + 2 * T <= 512, "TMEM overflow");
+    static_assert(O_COLS + NSBUF * T <= 512 && TMEM_COLS * CTAS_PER_SM <= 512, "TMEM overflow");
+    static_assert(NSBUF == 1 || NSBUF == 2, "one or two S accumulators");
     static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
+    static_assert(CTAS_PER_SM * (SMEM_BYTES + 1024) <= 233472, "the CTAs meant to share an SM do not fit its 228 KB");
     static_assert(T % 32 == 0 && T <= 256, "tile size");
 };
 
@@ -69,7 +76,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <class C>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, C::CTAS_PER_SM)
 fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
     using namespace ptx;
@@ -111,8 +118,12 @@ fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
     const int blk_hi = hi < blk_vis ? hi : blk_vis;
     const int t_begin = (lo / T) * T;
     // once any CTA has reported a failed wait the rest of the grid does no work
-    const bool poisoned = *reinterpret_cast<volatile int *>(&g_tc_error) != 0 &&
-                          *reinterpret_cast<volatile int *>(&g_tc_error) != ERR_PAGE;
+    bool poisoned = *reinterpret_cast<volatile int *>(&g_tc_error) != 0 &&
+                    *reinterpret_cast<volatile int *>(&g_tc_error) != ERR_PAGE;
+    if (smem + (C::SMEM_BYTES - C::ALIGN_SLACK) > smem_raw + C::SMEM_BYTES) {     // base less aligned than assumed
+        if (threadIdx.x == 0) atomicCAS(&g_tc_error, 0, ERR_PRODUCER);
+        poisoned = true;
+    }
     const int n_tiles = (blk_hi > lo && !poisoned) ? (blk_hi - t_begin + T - 1) / T : 0;
 
     // ---- set-up -----------------------------------------------------------------
@@ -201,10 +212,10 @@ fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
             const uint32_t sQ_a = smem_u32(sQ), sKV_a = smem_u32(sKV), sP_a = smem_u32(sP);
             bool ok = mbar_wait(BAR(B_QFULL), 0);
             auto issue_qk = [&](int t) -> bool {
-                const int stage = t % STAGES, b = t & 1;
+                const int stage = t % STAGES, b = t % C::NSBUF;
                 if (!mbar_wait(BAR(B_KVFULL + stage), (t / STAGES) & 1)) return false;
                 if (t_begin + t * T + T > seq && !mbar_wait(BAR(B_KVFIX), 0)) return false;
-                if (t >= 2 && !mbar_wait(BAR(B_SEMPTY + b), ((t / 2) - 1) & 1)) return false;
+                if (t >= C::NSBUF && !mbar_wait(BAR(B_SEMPTY + b), ((t / C::NSBUF) - 1) & 1)) return false;
                 tc_fence_after_sync();
                 const uint32_t kbase = sKV_a + stage * C::STAGE_BYTES;
                 if (elected) {
@@ -268,24 +279,33 @@ fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
         bool ok = true;
         uint32_t r[32];
         for (int t = 0; t < n_tiles; ++t) {
-            const int b = t & 1, t0 = t_begin + t * T;
-            ok = mbar_wait(BAR(B_SFULL + b), (t / 2) & 1);
+            const int b = t % C::NSBUF, t0 = t_begin + t * T;
+            ok = mbar_wait(BAR(B_SFULL + b), (t / C::NSBUF) & 1);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t s_addr = tmem + lane_base + C::S_COL0 + b * T;
-            // pass 1: tile maximum of the visible scores (base-2 units)
+            // pass 1: tile maximum of the visible scores (base-2 units); no per-key masking when this row sees the whole tile
+            const bool all_visible = t0 >= lo && t0 + T <= upper && sl2 > 0.f;
             float tmax = -CUDART_INF_F;
+            auto max_of = [&](const uint32_t (&v)[32], int cc) {
+                if (all_visible) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(v[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = t0 + cc * 32 + j;
+                        if (tok >= lo && tok < upper) tmax = fmaxf(tmax, __uint_as_float(v[j]) * sl2);
+                    }
+                }
+            };
 #pragma unroll 1
             for (int cc = 0; cc < T / 32; ++cc) {
                 tmem_ld32(s_addr + cc * 32, r);
                 tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int tok = t0 + cc * 32 + j;
-                    const float v = (tok >= lo && tok < upper) ? __uint_as_float(r[j]) * sl2 : -CUDART_INF_F;
-                    tmax = fmaxf(tmax, v);
-                }
+                max_of(r, cc);
             }
+            if (all_visible) tmax *= sl2;     // the fast path took the maximum of the raw scores (sl2 > 0)
             const float m_new = fmaxf(m_true, tmax);
             const bool need = m_new > m_ref + 8.f;       // also true for the first finite maximum
             // P*V of the previous tile must be done before O is rescaled or P overwritten
@@ -318,26 +338,40 @@ fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
             // pass 2: P = 2^(s - m_ref) in bf16, K-major un-swizzled core matrices
             float lsum = 0.f;
             uint8_t *prow = sP + (row_in_tile >> 3) * C::P_SBO + (row_in_tile & 7) * 16;
+            auto emit_p = [&](const uint32_t (&v)[32], int cc) {
+                uint32_t packed[16];
+                if (all_visible) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(v[j]), sl2, -m_ref));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(v[j + 1]), sl2, -m_ref));
+                        lsum += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const int tok = t0 + cc * 32 + j;
+                        const float p0 = (tok >= lo && tok < upper) ? fast_exp2(fmaf(__uint_as_float(v[j]), sl2, -m_ref)) : 0.f;
+                        const float p1 = (tok + 1 >= lo && tok + 1 < upper) ? fast_exp2(fmaf(__uint_as_float(v[j + 1]), sl2, -m_ref)) : 0.f;
+                        lsum += p0 + p1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                }
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc)
+                    *reinterpret_cast<uint4 *>(prow + (cc * 4 + kc) * 128) =
+                        make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
+            };
 #pragma unroll 1
             for (int cc = 0; cc < T / 32; ++cc) {
                 if (T > 32) {
                     tmem_ld32(s_addr + cc * 32, r);
                     tmem_wait_ld();
                 }
-                uint32_t packed[16];
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int tok = t0 + cc * 32 + j;
-                    const float p0 = (tok >= lo && tok < upper) ? fast_exp2(__uint_as_float(r[j]) * sl2 - m_ref) : 0.f;
-                    const float p1 = (tok + 1 >= lo && tok + 1 < upper) ? fast_exp2(__uint_as_float(r[j + 1]) * sl2 - m_ref) : 0.f;
-                    lsum += p0 + p1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h);
-                }
-#pragma unroll
-                for (int kc = 0; kc < 4; ++kc)
-                    *reinterpret_cast<uint4 *>(prow + (cc * 4 + kc) * 128) =
-                        make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
+                emit_p(r, cc);
             }
             l_run += lsum;
             tc_fence_before_sync();
@@ -409,8 +443,14 @@ fwd_tc_kernel(const FwdProblem p, const __grid_constant__ CUtensorMap tmQ,
 // Host side
 // --------------------------------------------------------------------------------------
 using MlaCfg = TcCfg<9, 4, 32, 2, false, 2>;    // d_qk 576, d_v 512 in two 256-column halves
-using OtfCfg = TcCfg<1, 1, 128, 4, true, 1>;    // d_qk = d_v = 64, separate V tensor
-using Cl64Cfg = TcCfg<1, 1, 128, 4, false, 1>;  // d_qk = d_v = 64, V = K
+// 64-wide heads: three CTAs share an SM (64-key tiles, one S accumulator, two KV stages: 65 KB of shared memory and
+// 128 tensor-memory columns each), so that one CTA's softmax - the exponentials bound this shape, not the MMAs - runs
+// under the others' MMAs and every scheduler has three softmax warps to switch between.  Measured on config 4b's
+// shape (forward with the projections): one CTA per SM with 128-key tiles and two S accumulators 1.33 ms, two CTAs
+// per SM 1.00 ms, with the unmasked fast path of the softmax 0.76 ms, three CTAs with 64-key tiles 0.68 ms; keeping
+// the 64 scores of a thread in registers between the two passes spills under the three-CTA register bound (0.84 ms).
+using OtfCfg = TcCfg<1, 1, 64, 2, true, 1, 1, 3>;    // d_qk = d_v = 64, separate V tensor
+using Cl64Cfg = TcCfg<1, 1, 64, 2, false, 1, 1, 3>;  // d_qk = d_v = 64, V = K
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -506,6 +546,9 @@ static int launch_cfg(const FwdProblem &p, cudaStream_t stream) {
     }
     auto kern = fwd_tc_kernel<C>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+        return FDMLA_ERR_CUDA;
+    if (C::CTAS_PER_SM > 1 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return FDMLA_ERR_CUDA;
     dim3 grid(((p.R + 127) / 128) * C::VSPLIT, p.G, p.num_splits);
     kern<<<grid, TC_THREADS, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
