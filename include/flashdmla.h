@@ -322,8 +322,9 @@ int fdmla_cache_gather(const void *kv_pool, const int32_t *page_table,
  * -> per-expert packing (bucket + exclusive scan) -> expert MLP -> combine and
  * shared-expert add; the reference lists csrc/moe/router_topk.cu,
  * pack_dispatch.cu, combine_scatter.cu at README.md:48-53 but ships none).
- * The expert MLP itself is a plain grouped GEMM and is left to the caller's
- * GEMM library; these four calls are what surrounds it.
+ * The expert MLPs themselves are two grouped GEMMs: fdmla_gemm_batched above with
+ * the experts as the batch (the first one with the SwiGLU gate in its epilogue);
+ * the calls below are what surrounds them.
  * -------------------------------------------------------------------------- */
 
 /*
