@@ -431,7 +431,7 @@ def bench_e2e(dev, world, Q, pool, table, seqlens, splits, ws, steps):
     """End to end through the public operator with HOST buffers: every step copies its inputs (Q, page table,
     lengths) from pinned host memory and its results (O, m, l) back.  One staging buffer per direction - the three
     tensors packed at 256-byte offsets - so that a step is ONE copy in and ONE copy out; the device side works on
-    views of the staging buffers.  The copies run on their own streams with two sets of buffers, so the copy-in of
+    views of the staging buffers.  The copies run on their own streams with three sets of buffers, so the copy-in of
     step i+1 and the copy-out of step i-1 overlap the kernel of step i.  The same schedule without the kernel gives
     the ceiling the host link sets (`copy_only_ms`)."""
     import flashdmla
@@ -440,7 +440,7 @@ def bench_e2e(dev, world, Q, pool, table, seqlens, splits, ws, steps):
     o_tab, o_len, n_in = al(nQ), al(nQ) + al(ntab), al(nQ) + al(ntab) + al(nlen)
     nO, nm = B * H * D_V * 2, B * H * 4
     o_m, o_l, n_out = al(nO), al(nO) + al(nm), al(nO) + 2 * al(nm)
-    NB = 2
+    NB = 3
     h_in = torch.empty(n_in, dtype=torch.uint8).pin_memory()
     h_in[:nQ].copy_(Q.cpu().view(torch.uint8).reshape(-1))
     h_in[o_tab:o_tab + ntab].copy_(table.cpu().view(torch.uint8).reshape(-1))
@@ -522,7 +522,7 @@ def bench_e2e(dev, world, Q, pool, table, seqlens, splits, ws, steps):
             "result_matches_resident_run": same,
             "note": "paged KV pool stays resident in HBM (it is the cache); every step moves Q, page table, seqlens in "
                     "and O, m, l out, one copy per direction from/to one pinned staging buffer, on their own streams, "
-                    "double-buffered; copy_only_ms is the same schedule without the kernel"}
+                    "three sets of buffers; copy_only_ms is the same schedule without the kernel"}
 
 
 def _median_over_ranks(ms, world):
