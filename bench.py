@@ -288,7 +288,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     import flashdmla
     from flashdmla import _lib
 
@@ -596,7 +597,29 @@ def bench_long_context(dev, rank, world, steps=50, warmup=10):
     med = lambda a, b: statistics.median(e[a].elapsed_time(e[b]) for e in evs)
     local_ms, ag_ms, merge_ms = (_median_over_ranks(med(0, 1), world), _median_over_ranks(med(1, 2), world),
                                  _median_over_ranks(med(2, 3), world))
-    total_ms = time_steps(plain, steps, 3, world) / steps
+    eager_ms = time_steps(plain, steps, 3, world) / steps
+    # the step as a serving loop would run it: buffers allocated once, captured into a CUDA graph, replayed
+    dec = parallel.SequenceParallelDecoder(B8, H, D_QK, D_V, PAGE, int(llen.max().item()), dev, scale=SCALE)
+    dec.step(Q, lpool, ltab, llen)
+    torch.cuda.synchronize()
+    dist.barrier()
+    prealloc_ms = time_steps(lambda: dec.step(Q, lpool, ltab, llen), steps, 3, world) / steps
+    graph_ms = None
+    captured = 1
+    try:
+        dec.capture(Q, lpool, ltab, llen)
+    except Exception as exc:                          # capture of the collective refused by this NCCL / torch build
+        captured = 0
+        sys.stderr.write(f"rank {rank}: long-context step not captured into a CUDA graph: {exc}\n")
+    flag = torch.tensor([captured], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)       # every rank replays, or none does
+    if int(flag.item()) == 1:
+        graph_ms = time_steps(dec.replay, steps, 3, world) / steps
+        res[0] = dec.replay()
+    else:
+        res[0] = dec.step(Q, lpool, ltab, llen)
+    torch.cuda.synchronize()
+    total_ms = graph_ms if graph_ms is not None else prealloc_ms
     O, m, l = res[0]
     err = float((O.float() - O1.float()).abs().max())
     msg_bytes = B8 * H * (D_V + 2) * 4
@@ -604,6 +627,12 @@ def bench_long_context(dev, rank, world, steps=50, warmup=10):
     return {"workload": f"long-context decode B={B8} H={H} Skv~U[16384,131072] page={PAGE}, KV split over {world} GPUs "
                         f"(sequence lengths {lens})",
             "tokens_per_s": B8 / (total_ms * 1e-3), "ms_per_step": total_ms,
+            "ms_per_step_how": ("whole step replayed from a CUDA graph (SequenceParallelDecoder)" if graph_ms is not None
+                                else "eager steps on preallocated buffers (SequenceParallelDecoder)"),
+            "ms_per_step_eager_python": eager_ms, "ms_per_step_preallocated": prealloc_ms, "ms_per_step_graph": graph_ms,
+            "phase_times_note": "local / all-gather / merge are CUDA-event spans of the eager Python step: they include the "
+                                "host's enqueue gaps",
+            "local_splits": dec.splits,
             "local_ms": local_ms, "allgather_ms": ag_ms, "merge_ms": merge_ms,
             "bytes_out": msg_bytes, "bytes_in": (world - 1) * msg_bytes,
             "allgather_busbw_gbs": (world - 1) * msg_bytes / (ag_ms * 1e-3) / 1e9,

@@ -301,6 +301,43 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool, const int32_t *page_t
     return rc;
 }
 
+int fdmla_decode_paged_partial(const void *Q, const void *kv_pool, const int32_t *page_table, const int32_t *seqlens,
+                               float *O_out, float *m_out, float *l_out, float *O_part, float *m_part, float *l_part,
+                               int B, int H, int d_qk, int d_v, int page_size, int max_pages, int num_pages,
+                               int num_splits, float scale, int dtype, void *stream) {
+    if (!dtype_ok(dtype)) return FDMLA_ERR_INVALID;
+    if (B < 0 || H < 0 || d_qk <= 0 || d_v <= 0 || d_v > d_qk || page_size <= 0 || max_pages < 0 || num_pages < 0 ||
+        num_splits < 1)
+        return FDMLA_ERR_INVALID;
+    if (B == 0 || H == 0) return FDMLA_OK;
+    if (!Q || !kv_pool || !page_table || !seqlens || !O_out || !m_out || !l_out) return FDMLA_ERR_INVALID;
+    if (num_splits > 1 && (!O_part || !m_part || !l_part)) return FDMLA_ERR_WORKSPACE;
+    if (B > 65535 || (long long)max_pages * page_size > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    FwdProblem p{};
+    p.Q = Q; p.K = kv_pool; p.V = nullptr; p.page_table = page_table; p.seqlens = seqlens;
+    p.O = nullptr; p.m = nullptr; p.l = nullptr;
+    p.G = B; p.R = H; p.Sq = 1; p.Skv = max_pages * page_size; p.d_qk = d_qk; p.d_v = d_v;
+    p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages;
+    p.num_splits = num_splits; p.kv_begin = 0; p.kv_end = -1; p.causal = 0; p.scale = scale;
+    if (num_splits == 1) {        // one piece per sequence: the attention kernel writes the result itself
+        p.O_part = O_out; p.m_part = m_out; p.l_part = l_out;
+        return run_forward(p, dtype, st);
+    }
+    p.O_part = O_part; p.m_part = m_part; p.l_part = l_part;
+    if (H <= 128 && H >= 2 && g_backend.load() != FDMLA_BACKEND_PORTABLE && !tensor_single_cta_preferred() &&
+        fwd_tensor2_supported(p, dtype)) {
+        // balanced runs of tiles, every piece a partial; a sequence is cut into at most num_splits pieces
+        const int nt_max = (int)(((long long)max_pages * page_size + 255) / 256);
+        p.balanced = 2;
+        p.quota_min = (nt_max + num_splits - 2) / (num_splits - 1);
+        if (p.quota_min < 1) p.quota_min = 1;
+    }
+    const int rc = run_forward(p, dtype, st);
+    if (rc) return rc;
+    return launch_merge(O_part, m_part, l_part, O_out, m_out, l_out, (long long)B * H, d_v, num_splits, FDMLA_F32, st);
+}
+
 int fdmla_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
                        long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
                        int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,

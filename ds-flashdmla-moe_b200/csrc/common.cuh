@@ -60,7 +60,7 @@ struct FwdProblem {
     float scale;
     // Balanced decode schedule of the 2-CTA tensor kernel (0 = off): keys are handed out as contiguous
     // runs of 256-key tiles, at least quota_min per CTA pair; num_splits then counts the partial slabs.
-    int balanced, quota_min;
+    int balanced, quota_min;     // balanced: 0 no, 1 with a final output, 2 every piece (also of uncut sequences) a partial
     // Balanced schedule only: arrival counters [2 G], zero at launch.  When given, the CTA that finishes the last
     // piece of a cut sequence merges the pieces itself and no merge kernel is needed; nullptr = merge kernel.
     unsigned int *tickets;

@@ -331,7 +331,7 @@ __device__ __forceinline__ bool cursor_next(Cursor &c, const FwdProblem &p, bool
     it.n_sub = (it.hi > it.lo && !poisoned) ? (it.hi - it.lo + SUB - 1) / SUB : 0;
     it.n_tiles = (it.n_sub + 3) / 4;
     it.fix = it.n_sub > 0 && it.t_begin + it.n_sub * SUB > seq;
-    it.final_out = ta == 0 && tb == nt;
+    it.final_out = ta == 0 && tb == nt && p.balanced != 2;      // balanced == 2: partials only, nothing is final
     it.split = c.cid - first / c.quota;                         // piece index within the sequence
     it.n_parts = (first + nt - 1) / c.quota - first / c.quota + 1;
     return true;
@@ -1162,9 +1162,10 @@ bool fwd_tensor2_supported(const FwdProblem &p, int dtype) {
 int launch_fwd_tensor2(const FwdProblem &p_in, cudaStream_t stream) {
     FwdProblem p = p_in;
     // the balanced schedule is for one row tile per KV group, the whole key range and a final output
-    if (p.balanced && (p.R > 128 || p.causal || p.num_splits < 2 || p.quota_min < 1 || !p.O || !p.O_part || p.kv_begin > 0 ||
-                       p.kv_end >= 0))
+    if (p.balanced && (p.R > 128 || p.causal || p.num_splits < 2 || p.quota_min < 1 || (!p.O && p.balanced != 2) || !p.O_part ||
+                       p.kv_begin > 0 || p.kv_end >= 0))
         p.balanced = 0;
+    if (p.balanced == 2) { p.O = nullptr; p.tickets = nullptr; }       // balanced runs, every piece a partial
     if (!p.balanced && p.num_splits > 1) p.O = nullptr;      // equal splits: partials only
     if (!p.balanced || p.Sq != 1) p.tickets = nullptr;
     CUtensorMap tmQ, tmK, tmV, tmO;

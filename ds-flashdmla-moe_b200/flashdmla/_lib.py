@@ -31,6 +31,7 @@ SIGNATURES = {
     "fdmla_fwd_on_the_fly_workspace_bytes": (_sz, [_i] * 5),
     "fdmla_fwd_on_the_fly": (_i, [_vp] * 9 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),
     "fdmla_decode_paged": (_i, [_vp] * 10 + [_i] * 10 + [_f, _i, _vp]),
+    "fdmla_decode_paged_partial": (_i, [_vp] * 10 + [_i] * 8 + [_f, _i, _vp]),
     "fdmla_decode_suggest_splits": (_i, [_i] * 7),
     "fdmla_decode_plan": (_i, [_i] * 8 + [_vp, _vp]),
     "fdmla_decode_paged_noalloc_max_rows": (_sz, [_i]),

@@ -284,6 +284,65 @@ def flash_dmla_paged_decode(Q, kv_pool, page_table, seqlens, d_v, scale=None, nu
     return O, m, l
 
 
+def suggest_partial_slabs(B: int, H: int, max_tokens: int, page_size: int = 64) -> int:
+    """Scratch slabs for flash_dmla_paged_decode_partial: enough that a run of tiles (the work of one CTA pair) may be
+    half as long as it would be if every sequence had max_tokens keys, so ragged batches still balance; 1 when the
+    batch alone fills the GPU."""
+    import ctypes
+    units = ctypes.c_int(0)
+    max_pages = max((int(max_tokens) + page_size - 1) // page_size, 1)
+    _lib.lib().fdmla_decode_plan(B, H, 576, 512, page_size, max_pages, 2, _lib.BF16, None, ctypes.byref(units))
+    pairs = units.value or 74
+    tiles = max((int(max_tokens) + 255) // 256, 1)
+    if B >= pairs or H > 128 or H < 2:
+        return 1
+    run = max(-(-B * tiles // pairs), 1)
+    return int(min(64, max(2, 2 * -(-tiles // run) + 1)))
+
+
+def flash_dmla_paged_decode_partial(Q, kv_pool, page_table, seqlens, d_v, scale=None, num_splits=None, out=None,
+                                    scratch=None):
+    """Attention of Q [B,H,d_qk] over the whole of this paged cache as an fp32 partial result: O [B,H,d_v] normalised
+    by its own l, m, l [B,H] - what a rank that holds one slice of every sequence sends to its peers.  out: three
+    contiguous fp32 tensors to write into (views of a message buffer); scratch: (O_part [S,B,H,d_v], m_part, l_part
+    [S,B,H]) fp32 for num_splits = S > 1, allocated when missing."""
+    _need_cuda(Q, kv_pool, page_table, seqlens)
+    _same_dtype(Q, kv_pool)
+    if page_table.dtype != torch.int32 or seqlens.dtype != torch.int32:
+        raise FlashDMLAError("page_table and seqlens must be int32")
+    Q, kv_pool, page_table, seqlens = Q.contiguous(), kv_pool.contiguous(), page_table.contiguous(), seqlens.contiguous()
+    B, H, d_qk = Q.shape
+    num_pages, page_size, _ = kv_pool.shape
+    max_pages = page_table.shape[1]
+    if scale is None:
+        scale = 1.0 / math.sqrt(d_qk)
+    dev = Q.device
+    if num_splits is None:
+        num_splits = suggest_partial_slabs(B, H, max_pages * page_size, page_size) if (d_qk, d_v) == (576, 512) else 1
+    S = max(1, int(num_splits))
+    if out is None:
+        out = (torch.empty(B, H, d_v, dtype=torch.float32, device=dev), torch.empty(B, H, dtype=torch.float32, device=dev),
+               torch.empty(B, H, dtype=torch.float32, device=dev))
+    O, m, l = out
+    for t, n in ((O, B * H * d_v), (m, B * H), (l, B * H)):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n or t.device != dev:
+            raise FlashDMLAError("out must be contiguous float32 tensors of B*H*d_v, B*H and B*H elements")
+    Op = mp = lp = None
+    if S > 1:
+        if scratch is None:
+            scratch = (torch.empty(S, B, H, d_v, dtype=torch.float32, device=dev), torch.empty(S, B, H, dtype=torch.float32, device=dev),
+                       torch.empty(S, B, H, dtype=torch.float32, device=dev))
+        Op, mp, lp = scratch
+        if Op.numel() < S * B * H * d_v or mp.numel() < S * B * H or lp.numel() < S * B * H:
+            raise FlashDMLAError("scratch too small for num_splits")
+    with torch.cuda.device(dev):
+        check(_lib.lib().fdmla_decode_paged_partial(
+            _ptr(Q), _ptr(kv_pool), _ptr(page_table), _ptr(seqlens), _ptr(O), _ptr(m), _ptr(l), _ptr(Op), _ptr(mp), _ptr(lp),
+            B, H, d_qk, int(d_v), page_size, max_pages, num_pages, S, float(scale), _dtype_code(Q), _stream(Q)),
+            "fdmla_decode_paged_partial")
+    return O, m, l
+
+
 def _part_stride(t: torch.Tensor, inner: int) -> Optional[int]:
     """Stride between parts if everything behind the leading dim is dense (inner elements), else None."""
     if t.shape[0] == 1:

@@ -121,17 +121,13 @@ def sequence_parallel_decode(Q, local_pool, local_page_table, local_seqlens, d_v
     mO, mm, ml = message_views(msg, (B, H), d_v)
     if decode_fn is None:
         from . import ops
-        splits = num_splits
-        if splits is None:
-            span = max(int(local_page_table.shape[1]) * int(local_pool.shape[1]), 1)
-            splits = ops.suggest_splits(B, H, span, Q.shape[-1], d_v, int(local_pool.shape[1]), Q.dtype)
-        if splits == 1:      # the attention kernel writes the message itself
-            ops.flash_dmla_paged_decode(Q, local_pool, local_page_table, local_seqlens, d_v, scale, num_splits=1,
-                                        partial_only=True, out=(mO[None], mm[None], ml[None]))
-        else:                # split-KV partials, merged (in fp32) into the message
-            Op, mp, lp = ops.flash_dmla_paged_decode(Q, local_pool, local_page_table, local_seqlens, d_v, scale,
-                                                     num_splits=splits, partial_only=True)
-            ops.merge_partials(Op, mp, lp, torch.float32, out=(mO, mm, ml))
+        # the rank's partial straight into its message: one call, the library picks the schedule and merges its pieces
+        if num_splits is None:
+            num_splits = (ops.suggest_partial_slabs(B, H, int(local_page_table.shape[1]) * int(local_pool.shape[1]),
+                                                    int(local_pool.shape[1])) if (Q.shape[-1], d_v) == (576, 512) else 1)
+        scratch = workspace.get(num_splits, B, H, d_v, Q.device) if (workspace is not None and num_splits > 1) else None
+        ops.flash_dmla_paged_decode_partial(Q, local_pool, local_page_table, local_seqlens, d_v, scale,
+                                            num_splits=num_splits, out=(mO, mm, ml), scratch=scratch)
     else:
         O_loc, m_loc, l_loc = decode_fn(Q, local_pool, local_page_table, local_seqlens, d_v, scale)
         mO.copy_(O_loc); mm.copy_(m_loc); ml.copy_(l_loc)
@@ -148,6 +144,68 @@ def sequence_parallel_decode(Q, local_pool, local_page_table, local_seqlens, d_v
     res = merge_fn(O_p, m_p, l_p, out_dtype or Q.dtype)
     rec(3)
     return res
+
+
+class SequenceParallelDecoder:
+    """`sequence_parallel_decode` for a serving loop: every buffer of the step (split-KV partials, the rank's
+    message, the gathered stack, the result) is allocated once, the split count is chosen once, and the step can
+    be captured into a CUDA graph - local attention, local merge, the NCCL all-gather and the final merge replay as
+    one launch, which matters when a rank's slice is attended in tens of microseconds and a Python host would
+    otherwise spend longer enqueueing the step than the GPUs spend running it.
+
+    B, H, d_qk, d_v, page_size: the problem; max_local_tokens: the longest slice any sequence has on this rank
+    (fixes the split count).  The tensors handed to `step` may change from call to call; a captured graph replays on
+    the tensors it was captured with (update them in place).
+    """
+
+    def __init__(self, B: int, H: int, d_qk: int, d_v: int, page_size: int, max_local_tokens: int, device,
+                 dtype=torch.bfloat16, scale: Optional[float] = None, group: Optional[dist.ProcessGroup] = None,
+                 num_splits: Optional[int] = None):
+        from . import ops
+        self.B, self.H, self.d_v, self.scale, self.group = B, H, d_v, scale, group
+        self.world = dist.get_world_size(group)
+        n = B * H * (d_v + 2)
+        self.msg = torch.empty(n, dtype=torch.float32, device=device)
+        self.flat = torch.empty(self.world * n, dtype=torch.float32, device=device)
+        self.out = (torch.empty(B, H, d_v, dtype=dtype, device=device), torch.empty(B, H, dtype=torch.float32, device=device),
+                    torch.empty(B, H, dtype=torch.float32, device=device))
+        self.splits = int(num_splits) if num_splits else (ops.suggest_partial_slabs(B, H, max(int(max_local_tokens), 1), page_size)
+                                                          if (d_qk, d_v) == (576, 512) else 1)
+        s = self.splits
+        self.part = None if s == 1 else (torch.empty(s, B, H, d_v, dtype=torch.float32, device=device),
+                                         torch.empty(s, B, H, dtype=torch.float32, device=device),
+                                         torch.empty(s, B, H, dtype=torch.float32, device=device))
+        self.graph = None
+
+    def step(self, Q, local_pool, local_page_table, local_seqlens):
+        """One decode step; returns (O [B,H,d_v], m, l) - the same tensors every call."""
+        from . import ops
+        mO, mm, ml = message_views(self.msg, (self.B, self.H), self.d_v)
+        ops.flash_dmla_paged_decode_partial(Q, local_pool, local_page_table, local_seqlens, self.d_v, self.scale,
+                                            num_splits=self.splits, out=(mO, mm, ml), scratch=self.part)
+        dist.all_gather_into_tensor(self.flat, self.msg, group=self.group)
+        O_p, m_p, l_p = message_views(self.flat.view(self.world, -1), (self.B, self.H), self.d_v)
+        ops.merge_partials(O_p, m_p, l_p, self.out[0].dtype, out=self.out)
+        return self.out
+
+    def capture(self, Q, local_pool, local_page_table, local_seqlens, warmup: int = 3):
+        """Capture one step on these tensors into a CUDA graph (after `warmup` eager steps, which also bring up the
+        NCCL communicator); `replay()` then runs it.  Every rank must capture and replay the same number of times."""
+        for _ in range(max(1, warmup)):
+            self.step(Q, local_pool, local_page_table, local_seqlens)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream(device=Q.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                self.step(Q, local_pool, local_page_table, local_seqlens)
+        torch.cuda.synchronize()
+        self.graph = graph
+        return self
+
+    def replay(self):
+        self.graph.replay()
+        return self.out
 
 
 # --------------------------------------------------------------------------- #

@@ -154,6 +154,24 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool,
                        int num_splits, int kv_begin, int kv_end, float scale,
                        int dtype, void *stream);
 
+/*
+ * One rank's partial result of a decode whose KV sequences are split over several GPUs: attention of Q over the
+ * whole of THIS cache (the rank's slice of every sequence), returned as fp32 O_out [B, H, d_v] normalised by its own
+ * l_out, with m_out, l_out [B, H] - the three blocks of the message the ranks exchange and then merge with
+ * fdmla_merge_lse_strided.  O_part / m_part / l_part [num_splits, ...] are private scratch (NULL for num_splits
+ * == 1): the library cuts the work as it likes (on the tcgen05 path: the 256-key tiles of all sequences in equal
+ * contiguous runs, which suits few long ragged sequences) and merges the pieces into the output itself.
+ * Replaces the per-rank part of fa2_forward_mpi (csrc/attention/fa2_fwd_mpi.cu:76-90: each rank's fa2_forward over
+ * its rows), for the split along the keys that long-context decode needs.
+ */
+int fdmla_decode_paged_partial(const void *Q, const void *kv_pool,
+                               const int32_t *page_table, const int32_t *seqlens,
+                               float *O_out, float *m_out, float *l_out,
+                               float *O_part, float *m_part, float *l_part,
+                               int B, int H, int d_qk, int d_v, int page_size,
+                               int max_pages, int num_pages, int num_splits,
+                               float scale, int dtype, void *stream);
+
 /* Split count (number of scratch slabs) the library would choose for a decode
  * problem.  No reference counterpart. */
 int fdmla_decode_suggest_splits(int B, int H, int max_seqlen, int d_qk, int d_v,

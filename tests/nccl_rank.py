@@ -49,6 +49,21 @@ def sequence_parallel_case(dev, world, rank):
     Of, mf, lf = orc.decode_paged(Q.float().numpy(), pool.float().numpy(), table.numpy(), sl.numpy(), 512, sc)
     assert_O(O, Of)
     assert_stats(m, l, mf, lf)
+    # the same step with every buffer allocated once, eagerly and replayed from a CUDA graph (three split counts:
+    # the attention kernel writing the message itself, and split-KV partials merged into it)
+    from flashdmla.parallel import SequenceParallelDecoder
+    Qd, pd, td, ld = Q.to(dev), pool.to(dev), ltable.to(dev), llens.to(dev)
+    for splits in (1, 3, None):
+        dec = SequenceParallelDecoder(len(lens), H, 576, 512, ps, int(llens.max()), dev, scale=sc, num_splits=splits)
+        O2, m2, l2 = (t.clone() for t in dec.step(Qd, pd, td, ld))
+        assert_O(O2, Of)
+        assert_stats(m2, l2, mf, lf)
+        dec.capture(Qd, pd, td, ld)
+        for t in dec.out:
+            t.zero_()
+        O3, m3, l3 = dec.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(O3, O2) and torch.equal(m3, m2) and torch.equal(l3, l2)
 
 
 def expert_parallel_case(dev, world, rank):

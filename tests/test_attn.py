@@ -134,6 +134,25 @@ def test_paged_decode_ragged(dims, splits, dtype, backend, cuda):
     assert_stats(m, l, mr, lr)
 
 
+@pytest.mark.parametrize("case", [((576, 512, 64), 128, 1), ((576, 512, 64), 128, 2), ((576, 512, 64), 128, 5), ((576, 512, 64), 128, 21),
+                                  ((576, 512, 64), 6, 4), ((576, 512, 64), 128, None), ((64, 32, 16), 6, 3), ((160, 128, 8), 6, 1)])
+def test_paged_decode_partial_for_the_exchange(case, backend, cuda):
+    """fdmla_decode_paged_partial: one rank's fp32 (O, m, l) over its whole cache, whatever the schedule behind it
+    (one piece, equal splits or balanced runs of tiles with every piece a partial), an empty sequence included."""
+    from flashdmla import ops
+    (dq, dv, ps), H, splits = case
+    lens = [37 * ps + 5, 0, ps, 90 * ps, 1, 11 * ps - 1]
+    B = len(lens)
+    Q, pool, table, sl = _paged(B, H, lens, dq, ps, torch.bfloat16, std=0.1)
+    sc = 1 / math.sqrt(dq)
+    O, m, l = ops.flash_dmla_paged_decode_partial(Q.to(cuda), pool.to(cuda), table.to(cuda), sl.to(cuda), dv, sc, num_splits=splits)
+    assert O.dtype == torch.float32 and tuple(O.shape) == (B, H, dv)
+    Or, mr, lr = orc.decode_paged(Q.float(), pool.float(), table, sl, dv, sc)
+    assert_O(O.to(torch.bfloat16), Or)
+    assert_stats(m, l, mr, lr)
+    assert float(O[1].abs().max()) == 0.0 and float(l[1].abs().max()) == 0.0      # the empty sequence
+
+
 def test_paged_decode_heads_128_and_window(backend, cuda):
     """H=128 (one full 128-row tile), 576/512 dims, and an attended window with partials."""
     import flashdmla
