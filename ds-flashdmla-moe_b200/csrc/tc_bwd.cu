@@ -40,14 +40,25 @@ constexpr int HALF = 64;                  // streamed indices per pipeline step 
 constexpr int E_BYTES = TILE * HALF * 2;  // 16 384: one elementwise result of a half tile (A operand, K = 64)
 constexpr int E_SBO = (HALF / 8) * 128;   // 1 024: stride between 8-row groups of the un-swizzled layout
 constexpr int VEC_BYTES = 2 * 4 * TILE * 4;
+// One streamed-tile buffer, one half-tile set of T1/T2 in tensor memory and one of E1/E2 in shared memory, so that TWO
+// CTAs share an SM (101 KB of shared memory and 256 tensor-memory columns each): while one CTA's elementwise warps wait
+// for their next half tile's score GEMMs - which with single buffers can only start when the previous half has been
+// read - the other CTA's are working.  (Everything double-buffered in one CTA per SM measured 8 % slower.)
+constexpr bool LEAN = true;
+constexpr int N_SBUF = 1;                 // streamed-tile buffers
+constexpr int N_HBUF = 1;                 // half-tile buffers of T1/T2 and E1/E2
 // barriers
 constexpr int B_OWNER = 0, B_FULL = 1, B_EMPTY = 3, B_SREADY = 5, B_PREADY = 7, B_DONE = 9, NBARS = 10;
-constexpr int SMEM_BYTES = 1024 + 2 * OP_BYTES + 4 * OP_BYTES + 4 * E_BYTES + VEC_BYTES + NBARS * 8 + 16;
+constexpr int SMEM_BYTES = 1024 + 2 * OP_BYTES + N_SBUF * 2 * OP_BYTES + 2 * N_HBUF * E_BYTES + VEC_BYTES + NBARS * 8 + 16;
 static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
+static_assert(!LEAN || 2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs do not fit an SM's shared memory");
 constexpr int THREADS = 288;              // 8 elementwise warps (two per TMEM lane quarter) + the control warp
 constexpr int CTRL_WARP = 8;
-// tensor memory columns
-constexpr int C_T1 = 0, C_T2 = 128, C_ACC1 = 256, C_ACC2 = 320, TMEM_COLS = 512;     // T1/T2: two 64-column halves each
+// tensor memory columns (T1/T2: N_HBUF 64-column halves each)
+constexpr int C_T1 = 0, C_T2 = N_HBUF * HALF, C_ACC1 = 2 * N_HBUF * HALF, C_ACC2 = C_ACC1 + D, TMEM_COLS = LEAN ? 256 : 512;
+static_assert(C_ACC2 + D <= TMEM_COLS, "tensor memory overflow");
+__device__ __forceinline__ int sbuf_of(int i) { return LEAN ? 0 : (i & 1); }     // streamed tile i -> its buffer
+__device__ __forceinline__ int hbuf_of(int h) { return LEAN ? 0 : h; }           // half h -> its T / E buffer
 enum { MODE_DKV = 0, MODE_DQ = 1 };
 enum { ERR_BWD = 21 };
 
@@ -60,7 +71,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, LEAN ? 2 : 1)
 bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
     using namespace ptx;
@@ -69,9 +80,9 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
     uint8_t *sA1 = smem;                      // owner tile 1 (K or Q)
     uint8_t *sA2 = sA1 + OP_BYTES;            // owner tile 2 (V or dO)
     uint8_t *sB = sA2 + OP_BYTES;             // streamed tiles: [buf][B1 | B2]
-    uint8_t *sE1 = sB + 4 * OP_BYTES;         // P^T, one buffer per half tile (MODE_DKV only)
-    uint8_t *sE2 = sE1 + 2 * E_BYTES;         // dS^T / dS, one buffer per half tile
-    float *vec = reinterpret_cast<float *>(sE2 + 2 * E_BYTES);    // [buf][m, 1/l, D, last visible key][128]  (MODE_DKV)
+    uint8_t *sE1 = sB + N_SBUF * 2 * OP_BYTES;   // P^T, one buffer per half-tile buffer (MODE_DKV only)
+    uint8_t *sE2 = sE1 + N_HBUF * E_BYTES;       // dS^T / dS
+    float *vec = reinterpret_cast<float *>(sE2 + N_HBUF * E_BYTES);    // [buf][m, 1/l, D, last visible key][128]  (MODE_DKV)
     uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(vec) + VEC_BYTES);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + NBARS);
     const uint32_t bar0 = smem_u32(bars);
@@ -137,8 +148,8 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
             bool ok = true;
             constexpr uint32_t idesc_t = make_idesc_bf16(128, 128, 0, 0);       // T = A B^T, both K-major
             constexpr uint32_t idesc_acc = make_idesc_bf16(128, 64, 0, 1);      // acc += E B, B MN-major
-            auto load_stream = [&](int i) {          // streamed tile i -> buffer i & 1
-                const int buf = i & 1;
+            auto load_stream = [&](int i) {          // streamed tile i -> its buffer
+                const int buf = sbuf_of(i);
                 if (elected) {
                     const int row = str_rows_base + (s_first + i) * TILE;
                     mbar_arrive_expect_tx(BAR(B_FULL + buf), 2 * OP_BYTES);
@@ -162,7 +173,7 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 if (str0 + TILE > limit) {
                     const int first_bad = limit > str0 ? limit - str0 : 0;
                     const int n16 = (TILE - first_bad) * 8;
-                    uint8_t *b = sB + (i & 1) * 2 * OP_BYTES;
+                    uint8_t *b = sB + sbuf_of(i) * 2 * OP_BYTES;
                     for (int idx = lane; idx < 2 * n16; idx += 32) {
                         const int t = idx / n16, rem = idx - t * n16;
                         *reinterpret_cast<uint4 *>(b + t * OP_BYTES + (first_bad + rem / 8) * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
@@ -172,66 +183,63 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 }
             };
             load_stream(0);
-            if (n_stream > 1) load_stream(1);
             ok = mbar_wait(BAR(B_OWNER), 0);
             constexpr uint32_t idesc_th = make_idesc_bf16(128, HALF, 0, 0);
             // Score GEMMs of one half tile (64 streamed rows): T1[h] = A1 B1[h]^T, T2[h] = A2 B2[h]^T
             auto issue_t = [&](int i, int h) {
-                const uint32_t b1 = smem_u32(sB + (i & 1) * 2 * OP_BYTES) + h * (HALF * 128), b2 = b1 + OP_BYTES;
+                const uint32_t b1 = smem_u32(sB + sbuf_of(i) * 2 * OP_BYTES) + h * (HALF * 128), b2 = b1 + OP_BYTES;
                 if (elected) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        mma_bf16_ss(tmem + C_T1 + h * HALF, make_smem_desc(smem_u32(sA1) + k * 32, 16, 1024, kLayoutSw128),
+                        mma_bf16_ss(tmem + C_T1 + hbuf_of(h) * HALF, make_smem_desc(smem_u32(sA1) + k * 32, 16, 1024, kLayoutSw128),
                                     make_smem_desc(b1 + k * 32, 16, 1024, kLayoutSw128), idesc_th, k != 0);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        mma_bf16_ss(tmem + C_T2 + h * HALF, make_smem_desc(smem_u32(sA2) + k * 32, 16, 1024, kLayoutSw128),
+                        mma_bf16_ss(tmem + C_T2 + hbuf_of(h) * HALF, make_smem_desc(smem_u32(sA2) + k * 32, 16, 1024, kLayoutSw128),
                                     make_smem_desc(b2 + k * 32, 16, 1024, kLayoutSw128), idesc_th, k != 0);
                     mma_commit(BAR(B_SREADY + h));
                 }
             };
             // Accumulating GEMMs of one half tile: acc1 += E1[h] B2[h], acc2 += E2[h] B1[h] (reduction over its 64 rows)
             auto issue_acc = [&](int i, int h) {
-                const uint32_t b1 = smem_u32(sB + (i & 1) * 2 * OP_BYTES) + h * (HALF * 128), b2 = b1 + OP_BYTES;
+                const uint32_t b1 = smem_u32(sB + sbuf_of(i) * 2 * OP_BYTES) + h * (HALF * 128), b2 = b1 + OP_BYTES;
                 if (elected) {
                     if (MODE == MODE_DKV) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            mma_bf16_ss(tmem + C_ACC1, make_smem_desc(smem_u32(sE1 + h * E_BYTES) + k * 256, 128, E_SBO, kLayoutNone),
+                            mma_bf16_ss(tmem + C_ACC1, make_smem_desc(smem_u32(sE1 + hbuf_of(h) * E_BYTES) + k * 256, 128, E_SBO, kLayoutNone),
                                         make_smem_desc(b2 + k * 2048, OP_BYTES, 1024, kLayoutSw128), idesc_acc, (i | h | k) != 0);
                     }
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        mma_bf16_ss(tmem + C_ACC2, make_smem_desc(smem_u32(sE2 + h * E_BYTES) + k * 256, 128, E_SBO, kLayoutNone),
+                        mma_bf16_ss(tmem + C_ACC2, make_smem_desc(smem_u32(sE2 + hbuf_of(h) * E_BYTES) + k * 256, 128, E_SBO, kLayoutNone),
                                     make_smem_desc(b1 + k * 2048, OP_BYTES, 1024, kLayoutSw128), idesc_acc, (i | h | k) != 0);
-                    if (h == 1) mma_commit(BAR(B_EMPTY + (i & 1)));      // the tile's buffer has been read for the last time
+                    if (h == 1) mma_commit(BAR(B_EMPTY + sbuf_of(i)));      // the tile's buffer has been read for the last time
                 }
             };
             ok = ok && mbar_wait(BAR(B_FULL), 0);
             fix_tail(0);
             tc_fence_after_sync();
             issue_t(0, 0);
-            issue_t(0, 1);
             for (int i = 0; i < n_stream; ++i) {
                 if (!__all_sync(0xffffffffu, ok)) break;
-                for (int h = 0; h < 2; ++h) {
-                    // the elementwise warps have turned T[h] of tile i into E[h]
-                    ok = ok && mbar_wait(BAR(B_PREADY + h), i & 1);
+                // single buffers: T(i, 1) may overwrite T(i, 0) once the elementwise warps have read it (PREADY 0), and
+                // is issued behind acc(i, 0), so that its completion also says E(i, 0) has been consumed; the next
+                // tile's copy waits until acc(i, 1) has read this tile's buffer for the last time
+                ok = ok && mbar_wait(BAR(B_PREADY + 0), i & 1);
+                tc_fence_after_sync();
+                issue_acc(i, 0);
+                issue_t(i, 1);
+                ok = ok && mbar_wait(BAR(B_PREADY + 1), i & 1);
+                tc_fence_after_sync();
+                issue_acc(i, 1);
+                if (i + 1 < n_stream) {
+                    ok = ok && mbar_wait(BAR(B_EMPTY), i & 1);
+                    load_stream(i + 1);
+                    ok = ok && mbar_wait(BAR(B_FULL), (i + 1) & 1);
+                    fix_tail(i + 1);
                     tc_fence_after_sync();
-                    issue_acc(i, h);
-                    if (i + 1 < n_stream) {
-                        // ... and T[h] is free for the next tile's half, which overlaps the other half's elementwise work
-                        if (h == 0) {
-                            ok = ok && mbar_wait(BAR(B_FULL + ((i + 1) & 1)), ((i + 1) >> 1) & 1);
-                            fix_tail(i + 1);
-                            tc_fence_after_sync();
-                        }
-                        issue_t(i + 1, h);
-                    }
-                }
-                if (i + 2 < n_stream) {
-                    ok = ok && mbar_wait(BAR(B_EMPTY + (i & 1)), (i >> 1) & 1);
-                    load_stream(i + 2);
+                    issue_t(i + 1, 0);
                 }
             }
             if (elected) mma_commit(BAR(B_DONE));
@@ -293,8 +301,8 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 if (ok) ok = mbar_wait(BAR(B_SREADY + h), i & 1);
                 tc_fence_after_sync();
                 uint32_t t1[32], t2[32];
-                tmem_ld32(tmem + lane_base + C_T1 + cc * 32, t1);
-                tmem_ld32(tmem + lane_base + C_T2 + cc * 32, t2);
+                tmem_ld32(tmem + lane_base + C_T1 + (2 * hbuf_of(h) + cg) * 32, t1);
+                tmem_ld32(tmem + lane_base + C_T2 + (2 * hbuf_of(h) + cg) * 32, t2);
                 tmem_wait_ld();
                 uint32_t e1[16], e2[16];
 #pragma unroll
@@ -338,7 +346,7 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                     }
                 }
                 // A-operand layout of the half tile: 8x8 core matrices, K (the streamed index) inside a core row
-                const int rowoff = h * E_BYTES + (L >> 3) * E_SBO + (L & 7) * 16 + (cc & 1) * 4 * 128;
+                const int rowoff = hbuf_of(h) * E_BYTES + (L >> 3) * E_SBO + (L & 7) * 16 + (cc & 1) * 4 * 128;
 #pragma unroll
                 for (int kc = 0; kc < 4; ++kc) {
                     if (MODE == MODE_DKV)
@@ -443,6 +451,10 @@ int launch_bwd_tensor(const BwdProblem &p, cudaStream_t stream) {
     auto kdq = tcb::bwd_tc_kernel<tcb::MODE_DQ>;
     if (cudaFuncSetAttribute(kdkv, cudaFuncAttributeMaxDynamicSharedMemorySize, tcb::SMEM_BYTES) != cudaSuccess ||
         cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, tcb::SMEM_BYTES) != cudaSuccess)
+        return FDMLA_ERR_CUDA;
+    if (tcb::LEAN &&
+        (cudaFuncSetAttribute(kdkv, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+         cudaFuncSetAttribute(kdq, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess))
         return FDMLA_ERR_CUDA;
     kdkv<<<dim3((p.Skv + tcb::TILE - 1) / tcb::TILE, p.G), tcb::THREADS, tcb::SMEM_BYTES, stream>>>(p, tmQ, tmdO, tmK, tmV);
     int rc = check_launch();
