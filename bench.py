@@ -261,6 +261,8 @@ def main():
                     help="B,H,S of the prefill measurement (default 4,128,8192); a reduced shape is used for ncu captures")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill measurement (profiling aid)")
     ap.add_argument("--only-moe", action="store_true", help="run only the MoE plumbing measurement (profiling aid)")
+    ap.add_argument("--only-otf", action="store_true", help="run only the on-the-fly forward/backward measurement (profiling aid)")
+    ap.add_argument("--otf-shape", default="", help="B,H,S of the on-the-fly measurement (a reduced shape for ncu captures)")
     ap.add_argument("--only-gemm", action="store_true", help="run only the batched-GEMM measurement (profiling aid)")
     ap.add_argument("--gemm-experts", type=int, default=64, help="experts of the GEMM measurement (fewer for ncu captures)")
     ap.add_argument("--kernel-launches", type=int, default=200,
@@ -298,6 +300,14 @@ def main():
         pf = bench_prefill(dev, rank, world, tf_burst, tf_sust)
         if rank == 0:
             print(json.dumps({"prefill": pf, "device_error_flag": flashdmla.device_error_flag()}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.only_otf:
+        if rank == 0:
+            shape = tuple(int(x) for x in args.otf_shape.split(",")) if args.otf_shape else None
+            print(json.dumps({"on_the_fly": bench_on_the_fly(dev, tf_burst, only_shape=shape),
+                              "device_error_flag": flashdmla.device_error_flag()}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -700,7 +710,7 @@ def bench_prefill(dev, rank, world, tf_burst, tf_sust, iters=10, warmup=3):
             "tokens_per_s": PF_B * PF_S / (ms * 1e-3)}
 
 
-def bench_on_the_fly(dev, tf_peak, iters=5):
+def bench_on_the_fly(dev, tf_peak, iters=5, only_shape=None):
     """On-the-fly mode (per-head K, V projected to 64-wide latents), causal, forward and backward through the
     autograd operator, at B=8,H=16,S=4096 (the training-backward configuration) and at B=4,H=16,S=2048 (the
     single-GPU forward configuration).  FLOP: attention 4 S(S+1)/2 64 per head forward (two GEMMs), five GEMMs
@@ -736,6 +746,8 @@ def bench_on_the_fly(dev, tf_peak, iters=5):
                 "fwd_frac_of_measured_bf16_peak": fwd_flop / (f * 1e-3) / 1e12 / tf_peak,
                 "bwd_frac_of_measured_bf16_peak": bwd_flop / (b * 1e-3) / 1e12 / tf_peak,
                 "tokens_per_s_fwd": B4 * S4 / (f * 1e-3), "kernel_family": flashdmla.last_kernel()}
+    if only_shape is not None:
+        return one(*only_shape)
     out = one(8, 16, 4096)
     out["config1"] = one(4, 16, 2048)
     return out
