@@ -845,8 +845,11 @@ def bench_moe_plumbing(dev, hbm_peak, iters=5):
     layer = moe.MoEFFN(d_model=4096, d_ff=1024, n_experts=64, top_k=8, capacity_factor=1.25, device=dev, seed=1)
     xl = (torch.randn(T, 4096, generator=g, device=dev) * 0.1).to(torch.bfloat16)
     layer_ms = t_of(lambda: layer.forward_batched(xl))
+    layer_grouped_ms = t_of(lambda: layer.forward(xl))
     del layer
-    return {"layer_batched_ms": layer_ms,
+    return {"layer_batched_ms": layer_ms, "layer_grouped_ms": layer_grouped_ms,
+            "layer_grouped_how": "MoEFFN.forward: ragged packing, the expert MLPs as two launches of the grouped GEMM that reads "
+                                 "the experts' row ranges on the device (no padding rows, no host read-back)",
             "layer_workload": "MoEFFN.forward_batched T=4096 d=4096 d_ff=1024 E=64 top-8 + shared expert, bf16",
             "workload": f"MoE plumbing T={T} E={E} top-{k} d={d} bf16, capacity {cap} ({rows} packed rows)",
             "gate_ms": gate_ms, "pack_ms": pack_ms, "gather_ms": gather_ms, "scatter_ms": scatter_ms, "combine_ms": comb_ms,

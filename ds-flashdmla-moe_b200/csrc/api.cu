@@ -357,7 +357,23 @@ int fdmla_gemm_batched(const void *A, const void *B, const void *B2, void *C, in
     if ((batch - 1) * c_bcol + N > ldc) return FDMLA_ERR_INVALID;
     t_last_kernel = "tcgen05";
     return launch_gemm_batched(A, B, B2, C, batch, M, N, K, a_rows, lda, a_brow, a_bcol, b_rows, ldb, b_brow, b_bcol,
-                               b_k_major, ldc, c_brow, c_bcol, gated, static_cast<cudaStream_t>(stream));
+                               b_k_major, ldc, c_brow, c_bcol, gated, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int fdmla_gemm_grouped(const void *A, const void *B, const void *B2, void *C, const int32_t *row_offsets, int groups,
+                       int total_rows, int N, int K, long long lda, long long b_rows, long long ldb, int b_brow,
+                       int b_k_major, long long ldc, int gated, void *stream) {
+    if (groups < 0 || total_rows < 0 || N < 0 || K < 0 || lda <= 0 || ldb <= 0 || ldc <= 0 || b_rows <= 0 || b_brow < 0)
+        return FDMLA_ERR_INVALID;
+    if (groups == 0 || total_rows == 0 || N == 0) return FDMLA_OK;
+    if (!A || !B || !C || !row_offsets || (gated && !B2) || K == 0) return FDMLA_ERR_INVALID;
+    if (!tensor_kernels_allowed()) return FDMLA_ERR_UNSUPPORTED;
+    if (K > lda || N > ldc) return FDMLA_ERR_INVALID;
+    const long long b_need_rows = (long long)(groups - 1) * b_brow + (b_k_major ? N : K);
+    if (b_need_rows > b_rows || (b_k_major ? K : N) > ldb) return FDMLA_ERR_INVALID;
+    t_last_kernel = "tcgen05";
+    return launch_gemm_batched(A, B, B2, C, groups, total_rows, N, K, total_rows, lda, 0, 0, b_rows, ldb, b_brow, 0, b_k_major,
+                               ldc, 0, 0, gated, row_offsets, static_cast<cudaStream_t>(stream));
 }
 
 int fdmla_rope_rows(const void *x, long long ldx, void *y, long long ldy, const int32_t *pos, long long rows,

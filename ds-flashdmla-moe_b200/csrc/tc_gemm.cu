@@ -53,6 +53,46 @@ struct Problem {
     __nv_bfloat16 *C;
     int b_k_major, gated;
     int m_tiles, n_tiles;
+    // Grouped (ragged) mode: batch entry b owns rows [row_offsets[b], row_offsets[b + 1]) of A's and C's tensors (read on the
+    // device: the packed rows of a MoE layer, whose per-expert counts the host never sees); M is then only an upper bound.
+    const int32_t *row_offsets;
+};
+
+// Walks the tiles of a launch in increasing order: tile -> (batch entry, first row, first column, rows of the entry).
+struct TileWalker {
+    int b = 0;
+    long long base = 0;          // tiles of the entries before b
+    int m0, n0, rows, row0;      // of the located tile: first row inside the entry, first output column, the entry's rows
+                                 // and its first row in A's / C's tensor (grouped mode)
+    __device__ __forceinline__ bool locate(const Problem &p, long long tile, int out_cols) {
+        if (!p.row_offsets) {
+            const int per = p.m_tiles * p.n_tiles;
+            if (tile >= (long long)p.batch * per) return false;
+            b = (int)(tile / per);
+            const int r = (int)(tile - (long long)b * per);
+            n0 = (r / p.m_tiles) * out_cols;
+            m0 = (r % p.m_tiles) * BM;
+            rows = p.M;
+            row0 = 0;
+            return true;
+        }
+        while (b < p.batch) {
+            const int lo = __ldg(p.row_offsets + b), hi = __ldg(p.row_offsets + b + 1);
+            const int mt = (hi - lo + BM - 1) / BM;
+            const long long tb = (long long)(mt > 0 ? mt : 0) * p.n_tiles;
+            if (tile < base + tb) {
+                const int r = (int)(tile - base);
+                n0 = (r / mt) * out_cols;
+                m0 = (r % mt) * BM;
+                rows = hi - lo;
+                row0 = lo;
+                return true;
+            }
+            base += tb;
+            ++b;
+        }
+        return false;
+    }
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -86,18 +126,10 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
     const uint32_t tmem = *tmem_slot;
     const bool poisoned = *err_slot != 0;            // an earlier launch gave up a wait: do nothing until the flag is cleared
 
-    const int tiles_per_batch = p.m_tiles * p.n_tiles;
-    const long long n_tiles_total = poisoned ? 0 : (long long)p.batch * tiles_per_batch;
     const int k_steps = p.K / BK;
     const int out_cols = p.gated ? BN / 2 : BN;         // output columns of one tile
-    // tile -> (batch, m tile, n tile): the m tiles of one (batch, n tile) are neighbours, so CTAs that run at the same
-    // time share the B tile in L2
-    auto tile_coords = [&](long long tile, int &b, int &m0, int &n0) {
-        b = (int)(tile / tiles_per_batch);
-        const int r = (int)(tile - (long long)b * tiles_per_batch);
-        n0 = (r / p.m_tiles) * out_cols;
-        m0 = (r % p.m_tiles) * BM;
-    };
+    // tile -> (batch entry, m tile, n tile): the m tiles of one (entry, n tile) are neighbours, so CTAs that run at the
+    // same time share the B tile in L2.  Every role walks the same tiles with its own TileWalker.
 
     if (warp == 0) {
         // ================================ TMA producer ================================
@@ -105,15 +137,16 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         if (lane == 0) { prefetch_tmap(&tmA); prefetch_tmap(&tmB); if (p.gated) prefetch_tmap(&tmB2); }
         bool ok = true;
         int s = 0, use = 0;
-        for (long long tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-            int b, m0, n0;
-            tile_coords(tile, b, m0, n0);
+        TileWalker w;
+        for (long long tile = blockIdx.x; !poisoned && ok && w.locate(p, tile, out_cols); tile += gridDim.x) {
+            const int b = w.b, m0 = w.m0, n0 = w.n0;
+            const int a_row = (p.row_offsets ? w.row0 : b * p.a_brow) + m0;
             for (int kb = 0; kb < k_steps && ok; ++kb) {
                 if (use > 0) ok = mbar_wait(EMPTY(s), (use - 1) & 1);
                 if (ok && elected) {
                     const uint32_t dstA = smem_u32(smem + s * STAGE), dstB = dstA + A_BYTES;
                     mbar_arrive_expect_tx(FULL(s), STAGE);
-                    tma_load_2d(dstA, &tmA, b * p.a_bcol + kb * BK, b * p.a_brow + m0, FULL(s));
+                    tma_load_2d(dstA, &tmA, b * p.a_bcol + kb * BK, a_row, FULL(s));
                     if (p.b_k_major) {
                         // [256 output columns x 64] K-major: rows of B's tensor are output columns
                         if (!p.gated) {
@@ -146,7 +179,8 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         int s = 0;
         uint32_t ph = 0;
         int n_done = 0;                              // tiles this CTA has issued
-        for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++n_done) {
+        TileWalker w;
+        for (long long tile = blockIdx.x; !poisoned && w.locate(p, tile, out_cols); tile += gridDim.x, ++n_done) {
             if (!__all_sync(0xffffffffu, ok)) break;
             const int acc = n_done & 1;
             if (n_done >= 2) {
@@ -179,14 +213,15 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         bool ok = true;
         int n_done = 0;
-        for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++n_done) {
-            int b, m0, n0;
-            tile_coords(tile, b, m0, n0);
+        TileWalker w;
+        for (long long tile = blockIdx.x; !poisoned && w.locate(p, tile, out_cols); tile += gridDim.x, ++n_done) {
+            const int b = w.b, m0 = w.m0, n0 = w.n0;
             const int acc = n_done & 1;
             if (ok) ok = mbar_wait(ACC_FULL(acc), (n_done >> 1) & 1);
             tc_fence_after_sync();
             const int m = m0 + L;
-            __nv_bfloat16 *crow = p.C + ((long long)b * p.c_brow + m) * p.ldc + (long long)b * p.c_bcol + n0;
+            __nv_bfloat16 *crow = p.C + ((p.row_offsets ? (long long)w.row0 : (long long)b * p.c_brow) + m) * p.ldc +
+                                  (long long)b * p.c_bcol + n0;
             const uint32_t t0 = tmem + lane_base + acc * BN;
 #pragma unroll 1
             for (int c = 0; c < out_cols / 32; ++c) {
@@ -196,7 +231,7 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
                     if (p.gated) tmem_ld32(t0 + BN / 2 + c * 32, g);
                     tmem_wait_ld();
                 }
-                if (!ok || m >= p.M || n0 + c * 32 >= p.N) continue;
+                if (!ok || m >= w.rows || n0 + c * 32 >= p.N) continue;
 #pragma unroll
                 for (int j = 0; j < 32; j += 16) {
                     uint32_t w[8];
@@ -239,11 +274,12 @@ int gemm_error_flag(int reset) {
     return v;
 }
 
-// Arguments as in fdmla_gemm_batched (include/flashdmla.h).
+// Arguments as in fdmla_gemm_batched (include/flashdmla.h); with row_offsets (fdmla_gemm_grouped) M is the total number
+// of rows and batch entry b owns rows [row_offsets[b], row_offsets[b + 1]) of A and C.
 int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
                         long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
                         int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
-                        int gated, cudaStream_t stream) {
+                        int gated, const int32_t *row_offsets, cudaStream_t stream) {
     using namespace tcg;
     if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return FDMLA_OK;
     if (K % BK != 0 || N % 64 != 0 || lda % 8 != 0 || ldb % 64 != 0 || ldc % 16 != 0) return FDMLA_ERR_UNSUPPORTED;
@@ -257,6 +293,7 @@ int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, i
     p.a_brow = a_brow; p.a_bcol = a_bcol; p.b_brow = b_brow; p.b_bcol = b_bcol;
     p.c_brow = c_brow; p.c_bcol = c_bcol; p.ldc = ldc; p.C = static_cast<__nv_bfloat16 *>(C);
     p.b_k_major = b_k_major ? 1 : 0; p.gated = gated ? 1 : 0;
+    p.row_offsets = row_offsets;
     const int out_cols = gated ? BN / 2 : BN;
     p.m_tiles = (M + BM - 1) / BM;
     p.n_tiles = (N + out_cols - 1) / out_cols;
@@ -274,7 +311,8 @@ int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, i
     }
     if (cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
         return FDMLA_ERR_CUDA;
-    const long long tiles = (long long)batch * p.m_tiles * p.n_tiles;
+    // grouped mode: M is the total of all entries' rows; every entry may add one partly filled row tile
+    const long long tiles = row_offsets ? ((long long)(M + BM - 1) / BM + batch) * p.n_tiles : (long long)batch * p.m_tiles * p.n_tiles;
     int dev = 0, sms = kNumSMs;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = (int)(tiles < sms ? tiles : sms);

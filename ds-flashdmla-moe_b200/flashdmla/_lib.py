@@ -39,6 +39,7 @@ SIGNATURES = {
     "fdmla_merge_lse": (_i, [_vp] * 6 + [_ll, _i, _i, _i, _vp]),
     "fdmla_merge_lse_strided": (_i, [_vp] * 6 + [_ll, _i, _i, _ll, _ll, _i, _vp]),
     "fdmla_gemm_batched": (_i, [_vp] * 4 + [_i] * 4 + [_ll, _ll, _i, _i, _ll, _ll, _i, _i, _i, _ll, _ll, _ll, _i, _vp]),
+    "fdmla_gemm_grouped": (_i, [_vp] * 5 + [_i] * 4 + [_ll, _ll, _ll, _i, _i, _ll, _i, _vp]),
     "fdmla_rope_rows": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _f, _vp]),
     "fdmla_bwd_on_the_fly_workspace_bytes": (_sz, [_i] * 7),
     "fdmla_bwd_on_the_fly": (_i, [_vp] * 15 + [_sz] + [_i] * 6 + [_f, _i, _i, _vp]),

@@ -85,3 +85,30 @@ def expert_mlp(xb: torch.Tensor, W1: torch.Tensor, W3: torch.Tensor, W2: torch.T
     gemm_batched(h.view(E * rows, f), W2.view(E * f, d), y.view(E * rows, d), E, rows, d, f,
                  a_brow=rows, b_brow=f, c_brow=rows)
     return y
+
+
+def gemm_grouped(A2: torch.Tensor, B2d: torch.Tensor, C2: torch.Tensor, row_offsets: torch.Tensor, N: int, K: int, *,
+                 b_brow: int, b_k_major: bool = False, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C[rows of group g] = A[rows of group g] B[g] with the groups' row ranges read on the device (row_offsets: int32
+    [groups + 1]); see fdmla_gemm_grouped in flashdmla.h."""
+    _need(A2, B2d, C2, gate)
+    if row_offsets.dtype != torch.int32 or not row_offsets.is_cuda or not row_offsets.is_contiguous():
+        raise FlashDMLAError("row_offsets must be a contiguous CUDA int32 tensor")
+    with torch.cuda.device(A2.device):
+        check(lib().fdmla_gemm_grouped(_ptr(A2), _ptr(B2d), _ptr(gate), _ptr(C2), _ptr(row_offsets), row_offsets.numel() - 1,
+                                       A2.shape[0], N, K, A2.shape[1], B2d.shape[0], B2d.shape[1], b_brow, int(bool(b_k_major)),
+                                       C2.shape[1], int(gate is not None), _stream(A2)), "fdmla_gemm_grouped")
+    return C2
+
+
+def expert_mlp_grouped(xp: torch.Tensor, row_offsets: torch.Tensor, W1: torch.Tensor, W3: torch.Tensor, W2: torch.Tensor) -> torch.Tensor:
+    """xp [rows, d] packed by expert (expert e owns rows row_offsets[e] .. row_offsets[e + 1]), W1, W3 [E, d, d_ff],
+    W2 [E, d_ff, d] -> [rows, d]; rows past row_offsets[E] are left unwritten.  Nothing is read back to the host."""
+    _need(xp, W1, W3, W2)
+    rows, d = xp.shape
+    E, _, f = W1.shape
+    h = torch.empty(rows, f, dtype=xp.dtype, device=xp.device)
+    gemm_grouped(xp, W1.view(E * d, f), h, row_offsets, f, d, b_brow=d, gate=W3.view(E * d, f))
+    y = torch.empty(rows, d, dtype=xp.dtype, device=xp.device)
+    gemm_grouped(h, W2.view(E * f, d), y, row_offsets, d, f, b_brow=f)
+    return y

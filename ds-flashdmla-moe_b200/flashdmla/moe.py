@@ -154,12 +154,10 @@ class MoEFFN:
         cap = self.capacity(x.shape[0]) if capacity is None else int(capacity)
         idx, w, pos, perm, offsets = self._route(x, cap)
         xp = scatter(x, pos, perm.shape[0])
-        yp = torch.zeros_like(xp)
-        offs = offsets.tolist()                    # the expert GEMMs are launched per expert from the host
-        for e in range(self.E):
-            lo, hi = offs[e], offs[e + 1]
-            if hi > lo:
-                yp[lo:hi] = swiglu_mlp(xp[lo:hi], self.W1[e], self.W3[e], self.W2[e])
+        # one grouped GEMM launch per MLP stage: the experts' row ranges are read from `offsets` on the device, no padding
+        # rows are multiplied and nothing comes back to the host
+        from . import gemm
+        yp = gemm.expert_mlp_grouped(xp, offsets, self.W1, self.W3, self.W2)
         sh = swiglu_mlp(x, *self.shared) if self.shared is not None else None
         return combine(yp, pos, w, sh)
 

@@ -269,6 +269,20 @@ int fdmla_gemm_batched(const void *A, const void *B, const void *B2, void *C,
                        int gated, void *stream);
 
 /*
+ * The same GEMM over groups of rows whose sizes only the device knows: group g owns rows
+ * [row_offsets[g], row_offsets[g + 1]) of A [total_rows, lda] and of C [total_rows, ldc] (row_offsets: groups + 1
+ * int32 in device memory, ascending, row_offsets[groups] <= total_rows) and multiplies them with its own window of B
+ * (rows g * b_brow ... of a tensor of b_rows rows; K-major or MN-major as above).  This is the expert MLP over the
+ * packed rows of fdmla_moe_pack without padding and without reading the counts back to the host (the "grouped GEMM"
+ * of the reference's advertised csrc/moe, README.md:19,48-53; no source there).  gated as above.
+ */
+int fdmla_gemm_grouped(const void *A, const void *B, const void *B2, void *C,
+                       const int32_t *row_offsets, int groups, int total_rows,
+                       int N, int K, long long lda, long long b_rows,
+                       long long ldb, int b_brow, int b_k_major, long long ldc,
+                       int gated, void *stream);
+
+/*
  * Rotary embedding of `rows` bf16 rows of width d that sit inside wider tensors (row strides ldx, ldy elements):
  * y[r, 2i], y[r, 2i+1] = rotation of x[r, 2i], x[r, 2i+1] by the angle pos[r / rows_per_pos] * base^(-2i/d).
  * The RoPE tail of the absorbed query: read from the per-head query, written next to the 512 latent columns

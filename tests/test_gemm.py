@@ -88,3 +88,31 @@ def test_absorbed_projections(n, cuda):
     o_lat = _rand((n, H, d_lat), 11, 0.5)
     o = gemm.project_out(o_lat.to(cuda), W_UV.to(cuda))
     _close(o, torch.einsum("nhl,hlv->nhv", o_lat.float(), W_UV.float()), "absorbed output projection")
+
+
+@pytest.mark.gpu
+def test_gemm_grouped_ragged_rows(cuda):
+    """Groups of 0, 1, 127, 128, 129 and 300 rows, their ranges read on the device; rows past the last group stay untouched."""
+    from flashdmla import gemm
+    counts = [0, 1, 127, 128, 129, 0, 300, 5]
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    rows, E, d, f = int(offs[-1]) + 40, len(counts), 192, 256
+    A, W1, W3 = _rand((rows, d), 21, 0.5), _rand((E, d, f), 22, 0.08), _rand((E, d, f), 23, 0.08)
+    C = torch.full((rows, f), 7.0, dtype=torch.bfloat16, device=cuda)
+    gemm.gemm_grouped(A.to(cuda), W1.to(cuda).view(E * d, f), C, offs.to(cuda), f, d, b_brow=d, gate=W3.to(cuda).view(E * d, f))
+    torch.cuda.synchronize()
+    want = torch.full((rows, f), 7.0)
+    for e in range(E):
+        lo, hi = int(offs[e]), int(offs[e + 1])
+        want[lo:hi] = torch.nn.functional.silu(A[lo:hi].float() @ W1[e].float()) * (A[lo:hi].float() @ W3[e].float())
+    _close(C[: int(offs[-1])], want[: int(offs[-1])], "grouped gated GEMM")
+    assert (C[int(offs[-1]):].float() == 7.0).all()
+    # K-major weights, ungated
+    W2 = _rand((E, 64, f), 24, 0.08)                      # [E, N=64, K=f]
+    C2 = torch.zeros(rows, 64, dtype=torch.bfloat16, device=cuda)
+    gemm.gemm_grouped(C, W2.to(cuda).view(E * 64, f), C2, offs.to(cuda), 64, f, b_brow=64, b_k_major=True)
+    want2 = torch.zeros(rows, 64)
+    for e in range(E):
+        lo, hi = int(offs[e]), int(offs[e + 1])
+        want2[lo:hi] = C[lo:hi].float().cpu() @ W2[e].float().T
+    _close(C2[: int(offs[-1])], want2[: int(offs[-1])], "grouped GEMM, K-major weights")

@@ -259,3 +259,16 @@ def test_batched_layer_replays_as_a_cuda_graph(cuda):
         torch.cuda.synchronize()
         want = layer.forward_batched(x)
         assert torch.equal(out, want)
+    # the ragged layer (grouped GEMM over device-side row ranges) reads nothing back either
+    with torch.cuda.stream(side):
+        layer.forward(x_in)
+    torch.cuda.synchronize()
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):
+        out2 = layer.forward(x_in)
+    x = (torch.randn(96, 128, generator=g) * 0.5).to(torch.bfloat16).to(cuda)
+    x_in.copy_(x)
+    graph2.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out2, layer.forward(x))
+    assert (out2.float() - layer.forward_batched(x).float()).abs().max() <= 2e-2 * out2.float().abs().max()
