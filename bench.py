@@ -385,7 +385,7 @@ def main():
     e2e = bench_e2e(dev, world, Q, pool, table, seqlens, splits, ws, args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
-    prefill = on_the_fly = moe_plumbing = long_context = context_prefill = gemm_line = None
+    prefill = on_the_fly = moe_plumbing = long_context = context_prefill = gemm_line = cl_bwd = None
     if not args.no_prefill:
         prefill = bench_prefill(dev, rank, world, tf_burst, tf_sust)
         if world > 1:
@@ -397,6 +397,7 @@ def main():
             on_the_fly = bench_on_the_fly(dev, tf_burst)
             moe_plumbing = bench_moe_plumbing(dev, hbm_peak)
             gemm_line = bench_gemm(dev, tf_burst, hbm_peak)
+            cl_bwd = bench_cache_latent_bwd(dev, tf_burst)
 
     err = flashdmla.device_error_flag()
     if rank == 0:
@@ -429,6 +430,7 @@ def main():
             "on_the_fly": on_the_fly,
             "moe_plumbing": moe_plumbing,
             "gemm": gemm_line,
+            "cache_latent_bwd": cl_bwd,
             "device_error_flag": err,
         }
         if cpu is not None:
@@ -751,6 +753,31 @@ def bench_on_the_fly(dev, tf_peak, iters=5, only_shape=None):
     out = one(8, 16, 4096)
     out["config1"] = one(4, 16, 2048)
     return out
+
+
+def bench_cache_latent_bwd(dev, tf_peak, iters=5):
+    """Cache-latent backward at B=1, H=128, Sq=Skv=1024, d=576/512, causal, through the autograd operator: tensor-core
+    GEMMs over a score workspace (unfused).  FLOP counted for the visible half only: 2 (3 x 576 + 2 x 512) per score."""
+    import flashdmla
+    Bc, Hc, Sc = 1, 128, 1024
+    g = torch.Generator(device=dev).manual_seed(55)
+    Q = (torch.randn(Bc, Hc, Sc, D_QK, generator=g, device=dev) * 0.1).to(torch.bfloat16).requires_grad_(True)
+    K = (torch.randn(Bc, Sc, D_QK, generator=g, device=dev) * 0.1).to(torch.bfloat16).requires_grad_(True)
+    dO = torch.randn(Bc, Hc, Sc, D_V, generator=g, device=dev).to(torch.bfloat16)
+    ts = []
+    for _ in range(iters + 2):
+        Q.grad = K.grad = None
+        O, m, l = flashdmla.flash_dmla_cache_latent(Q, K, D_V, SCALE, True)
+        a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); O.backward(dO); b2.record(); torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b2))
+    ms = statistics.median(ts[2:])
+    flop = 2.0 * Bc * Hc * (Sc * (Sc + 1) / 2) * (3 * D_QK + 2 * D_V)
+    return {"workload": f"cache-latent backward B={Bc} H={Hc} Sq=Skv={Sc} d=576/512 causal (autograd operator)", "ms": ms,
+            "tflops_visible_half": flop / (ms * 1e-3) / 1e12, "frac_of_measured_bf16_peak": flop / (ms * 1e-3) / 1e12 / tf_peak,
+            "kernel_family": flashdmla.last_kernel(),
+            "how": "five tcgen05 GEMM launches and one elementwise kernel per chunk of query rows (the masked half of the "
+                   "scores is computed too)"}
 
 
 def bench_gemm(dev, tf_burst, hbm_peak, E=64):

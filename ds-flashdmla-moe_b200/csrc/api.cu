@@ -484,9 +484,14 @@ int fdmla_bwd_on_the_fly(const void *Q, const void *K, const void *V, const void
 
 size_t fdmla_bwd_cache_latent_workspace_bytes(int B, int H, int Sq, int Skv, int d_qk, int d_v,
                                               int dtype) {
-    (void)Skv; (void)d_qk; (void)d_v;
     if (B <= 0 || H <= 0 || Sq <= 0 || !dtype_ok(dtype)) return 0;
-    return align256((size_t)B * H * Sq * 4);
+    size_t need = align256((size_t)B * H * Sq * 4);
+    // bf16 with widths and key counts that are multiples of 64 runs as tensor-core GEMMs over a score workspace
+    if (dtype == FDMLA_BF16 && Skv > 0 && d_qk > 0 && d_v > 0 && d_qk % 64 == 0 && d_v % 64 == 0 && Skv % 64 == 0) {
+        const size_t t = bwd_cache_latent_tensor_workspace(B, (long long)H * Sq, Skv, d_qk);
+        if (t > need) need = t;
+    }
+    return need;
 }
 
 int fdmla_bwd_cache_latent(const void *Q, const void *K_lat, const void *O, const float *m,
@@ -504,6 +509,11 @@ int fdmla_bwd_cache_latent(const void *Q, const void *K_lat, const void *O, cons
     p.dQ = dQ; p.dK = dK_lat; p.dV = nullptr;
     p.G = B; p.R = H * Sq; p.Sq = Sq; p.Skv = Skv; p.d_qk = d_qk; p.d_v = d_v;
     p.causal = causal ? 1 : 0; p.scale = scale;
+    if (bwd_cache_latent_tensor_supported(p, dtype)) {
+        t_last_kernel = "tcgen05";
+        return launch_bwd_cache_latent_tensor(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    }
+    t_last_kernel = "portable";
     return launch_bwd_portable(p, dtype, /*grads_f32=*/0, static_cast<cudaStream_t>(stream));
 }
 

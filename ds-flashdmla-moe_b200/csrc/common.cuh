@@ -129,7 +129,12 @@ int bwd_tensor_error_flag(int reset);
 int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
                         long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
                         int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
-                        int gated, const int32_t *row_offsets, cudaStream_t stream);
+                        int gated, const int32_t *row_offsets, cudaStream_t stream, float alpha = 1.f, int c_f32 = 0,
+                        int accumulate = 0);
+// cache-latent backward as GEMMs on the tensor cores with the score matrices in a workspace (csrc/cl_bwd.cu)
+bool bwd_cache_latent_tensor_supported(const BwdProblem &p, int dtype);
+size_t bwd_cache_latent_tensor_workspace(int G, long long R, int Skv, int d_qk);
+int launch_bwd_cache_latent_tensor(const BwdProblem &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int launch_rope_rows(const void *x, long long ldx, void *y, long long ldy, const int32_t *pos, long long rows,
                      int rows_per_pos, int d, float base, cudaStream_t stream);
 int gemm_error_flag(int reset);

@@ -50,8 +50,10 @@ struct Problem {
     int a_brow, a_bcol;                 // window of batch b in A's tensor: row b * a_brow, column b * a_bcol
     int b_brow, b_bcol;                 // K-major: rows are output columns; MN-major: rows are the reduction index
     long long c_brow, c_bcol, ldc;      // C element (b, m, n) = C[(b * c_brow + m) * ldc + b * c_bcol + n]
-    __nv_bfloat16 *C;
+    void *C;                            // bf16, or fp32 when c_f32
     int b_k_major, gated;
+    int c_f32, accumulate;              // fp32 output; accumulate (fp32 only): C += alpha A B instead of C = alpha A B
+    float alpha;
     int m_tiles, n_tiles;
     // Grouped (ragged) mode: batch entry b owns rows [row_offsets[b], row_offsets[b + 1]) of A's and C's tensors (read on the
     // device: the packed rows of a MoE layer, whose per-expert counts the host never sees); M is then only an upper bound.
@@ -220,8 +222,10 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
             if (ok) ok = mbar_wait(ACC_FULL(acc), (n_done >> 1) & 1);
             tc_fence_after_sync();
             const int m = m0 + L;
-            __nv_bfloat16 *crow = p.C + ((p.row_offsets ? (long long)w.row0 : (long long)b * p.c_brow) + m) * p.ldc +
-                                  (long long)b * p.c_bcol + n0;
+            const long long c_off = ((p.row_offsets ? (long long)w.row0 : (long long)b * p.c_brow) + m) * p.ldc +
+                                    (long long)b * p.c_bcol + n0;
+            __nv_bfloat16 *crow = static_cast<__nv_bfloat16 *>(p.C) + c_off;
+            float *crow_f = static_cast<float *>(p.C) + c_off;
             const uint32_t t0 = tmem + lane_base + acc * BN;
 #pragma unroll 1
             for (int c = 0; c < out_cols / 32; ++c) {
@@ -232,12 +236,28 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
                     tmem_wait_ld();
                 }
                 if (!ok || m >= w.rows || n0 + c * 32 >= p.N) continue;
+                if (p.c_f32) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint32_t w8[8];
+                        float4 o0 = make_float4(0.f, 0.f, 0.f, 0.f), o1 = o0;
+                        if (p.accumulate) {
+                            o0 = *reinterpret_cast<const float4 *>(crow_f + c * 32 + j);
+                            o1 = *reinterpret_cast<const float4 *>(crow_f + c * 32 + j + 4);
+                        }
+                        const float old[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) w8[e] = __float_as_uint(fmaf(p.alpha, __uint_as_float(r[j + e]), old[e]));
+                        st_global_v8(crow_f + c * 32 + j, w8);
+                    }
+                    continue;
+                }
 #pragma unroll
                 for (int j = 0; j < 32; j += 16) {
                     uint32_t w[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        float x0 = __uint_as_float(r[j + 2 * e]), x1 = __uint_as_float(r[j + 2 * e + 1]);
+                        float x0 = __uint_as_float(r[j + 2 * e]) * p.alpha, x1 = __uint_as_float(r[j + 2 * e + 1]) * p.alpha;
                         if (p.gated) {
                             x0 = silu(x0) * __uint_as_float(g[j + 2 * e]);
                             x1 = silu(x1) * __uint_as_float(g[j + 2 * e + 1]);
@@ -279,10 +299,11 @@ int gemm_error_flag(int reset) {
 int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
                         long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
                         int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
-                        int gated, const int32_t *row_offsets, cudaStream_t stream) {
+                        int gated, const int32_t *row_offsets, cudaStream_t stream, float alpha, int c_f32, int accumulate) {
     using namespace tcg;
     if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return FDMLA_OK;
-    if (K % BK != 0 || N % 64 != 0 || lda % 8 != 0 || ldb % 64 != 0 || ldc % 16 != 0) return FDMLA_ERR_UNSUPPORTED;
+    if (K % BK != 0 || N % 64 != 0 || lda % 8 != 0 || ldb % 64 != 0 || ldc % (c_f32 ? 8 : 16) != 0) return FDMLA_ERR_UNSUPPORTED;
+    if ((accumulate && !c_f32) || (gated && c_f32)) return FDMLA_ERR_UNSUPPORTED;
     if (a_bcol % 8 != 0 || b_bcol % 64 != 0 || c_bcol % 16 != 0) return FDMLA_ERR_UNSUPPORTED;
     if (gated && (N % 128 != 0 || !B2)) return FDMLA_ERR_UNSUPPORTED;
     if (lda > 2147483647LL || ldb > 2147483647LL || a_rows > 2147483647LL || b_rows > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
@@ -291,7 +312,8 @@ int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, i
     Problem p{};
     p.batch = batch; p.M = M; p.N = N; p.K = K;
     p.a_brow = a_brow; p.a_bcol = a_bcol; p.b_brow = b_brow; p.b_bcol = b_bcol;
-    p.c_brow = c_brow; p.c_bcol = c_bcol; p.ldc = ldc; p.C = static_cast<__nv_bfloat16 *>(C);
+    p.c_brow = c_brow; p.c_bcol = c_bcol; p.ldc = ldc; p.C = C;
+    p.alpha = alpha; p.c_f32 = c_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
     p.b_k_major = b_k_major ? 1 : 0; p.gated = gated ? 1 : 0;
     p.row_offsets = row_offsets;
     const int out_cols = gated ? BN / 2 : BN;

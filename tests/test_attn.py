@@ -309,6 +309,40 @@ def test_cache_latent_backward(dtype, backend, cuda):
     assert rel_fro(Qd.grad, dQ) <= tol and rel_fro(Kd.grad, dK) <= tol
 
 
+@pytest.mark.parametrize("shape", [(2, 3, 100, 128, 192, 128, True), (1, 4, 64, 192, 576, 512, True), (1, 2, 300, 256, 576, 512, False),
+                                   (1, 2, 130, 64, 64, 64, True)])
+def test_cache_latent_backward_on_tensor_cores(shape, cuda):
+    """bf16 with d_qk, d_v and Skv multiples of 64: the backward runs as GEMMs on the tensor cores over a score
+    workspace (row counts that are not multiples of the 128-row tile, Sq != Skv, causal and not)."""
+    import flashdmla
+    B, H, Sq, Skv, dq, dv, causal = shape
+    Q = _rand((B, H, Sq, dq), 0.3, 61, torch.bfloat16)
+    K = _rand((B, Skv, dq), 0.3, 62, torch.bfloat16)
+    dO = _rand((B, H, Sq, dv), 1.0, 63, torch.bfloat16)
+    sc = 1 / math.sqrt(dq)
+    Qd, Kd = Q.to(cuda).requires_grad_(True), K.to(cuda).requires_grad_(True)
+    O, m, l = flashdmla.flash_dmla_cache_latent(Qd, Kd, dv, sc, causal)
+    O.backward(dO.to(cuda))
+    # the same call through the C ABI on this thread (autograd runs the backward on a thread of its own, and the name
+    # of the last kernel family is kept per thread)
+    from flashdmla import _lib
+    L = _lib.lib()
+    dQ2, dK2 = torch.empty_like(Qd), torch.empty_like(Kd)
+    ws = torch.empty(L.fdmla_bwd_cache_latent_workspace_bytes(B, H, Sq, Skv, dq, dv, _lib.BF16), dtype=torch.uint8, device=cuda)
+    dOd = dO.to(cuda)
+    rc = L.fdmla_bwd_cache_latent(Qd.data_ptr(), Kd.data_ptr(), O.data_ptr(), m.data_ptr(), l.data_ptr(), dOd.data_ptr(),
+                                  dQ2.data_ptr(), dK2.data_ptr(), ws.data_ptr(), ws.numel(), B, H, Sq, Skv, dq, dv, sc, int(causal),
+                                  _lib.BF16, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and flashdmla.last_kernel() == "tcgen05"
+    assert torch.equal(dQ2, Qd.grad) and torch.equal(dK2, Kd.grad)
+    Or, mr, lr = orc.fwd_cache_latent(Q.float(), K.float(), dv, sc, causal)
+    dQ, dK = orc.bwd_cache_latent(Q.float(), K.float(), Or, mr, lr, dO.float(), sc, causal)
+    print(f"[parity] cache-latent backward {shape}: dQ rel-Fro {rel_fro(Qd.grad, dQ):.3e}, dK rel-Fro {rel_fro(Kd.grad, dK):.3e}")
+    assert rel_fro(Qd.grad, dQ) <= 2e-2 and rel_fro(Kd.grad, dK) <= 2e-2
+    assert flashdmla.device_error_flag() == 0
+
+
 def test_production_shapes_run_on_tensor_cores(cuda):
     """bf16 MLA / d=64 shapes dispatch to the tcgen05 kernels, and no kernel reported a
     timed-out wait or a bad page id."""
