@@ -2,6 +2,7 @@
 
     python ds-flashdmla-moe_b200/build.py --timeline [--ablate BITS]
     python ds-flashdmla-moe_b200/timeline_report.py [--batch 128] [--skv 4096] [--splits 1] [--ablate 0,1,2,4,3]
+    python ds-flashdmla-moe_b200/timeline_report.py --prefill 1,16,8192
 
 Runs the DeepSeek-V3-shape decode (H=128, 576-wide rows, page 64, seeded synthetic cache) on the library built with
 -DFDMLA_TIMELINE, which stamps what every CTA pair of the 2-CTA forward kernel does (global timer) and adds up the SM
@@ -86,7 +87,24 @@ def summarise(rec, label):
             print(f"   {rname}, CTA {rk}, thousands of SM cycles (median): {s}")
 
 
+def run_prefill(args):
+    import torch
+    import flashdmla
+    dev = torch.device("cuda:0")
+    Bp, Hp, Sp = (int(x) for x in args.prefill.split(","))
+    g = torch.Generator(device=dev).manual_seed(77)
+    K = (torch.randn(Bp, Sp, 576, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    Q = (torch.randn(Bp, Hp, Sp, 576, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    for _ in range(3):
+        flashdmla.flash_dmla_cache_latent(Q, K, 512, 1 / math.sqrt(192), True)
+    torch.cuda.synchronize()
+    summarise(parse(os.environ["FDMLA_TIMELINE_FILE"])[-1], f"causal prefill B={Bp} H={Hp} S={Sp} ablate={args.one}")
+    print(f"   device error flag {flashdmla.device_error_flag()}")
+
+
 def run_one(args):
+    if args.prefill:
+        return run_prefill(args)
     import torch
     import flashdmla
     dev = torch.device("cuda:0")
@@ -111,6 +129,7 @@ def main():
     ap.add_argument("--skv", type=int, default=4096)
     ap.add_argument("--splits", type=int, default=1)
     ap.add_argument("--ablate", default="0", help="comma-separated list of ablation builds to run (0 = none)")
+    ap.add_argument("--prefill", default="", help="B,H,S: time a causal prefill of that shape instead of the decode")
     ap.add_argument("--one", type=int, default=-1, help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.one >= 0:
@@ -122,7 +141,8 @@ def main():
         with tempfile.TemporaryDirectory() as tmp:
             env = dict(os.environ, FLASHDMLA_LIB=lib, FDMLA_TIMELINE_FILE=os.path.join(tmp, "timeline.bin"))
             subprocess.run([sys.executable, os.path.abspath(__file__), "--batch", str(args.batch), "--skv", str(args.skv),
-                            "--splits", str(args.splits), "--one", str(abl)], env=env, check=True)
+                            "--splits", str(args.splits), "--one", str(abl)] + (["--prefill", args.prefill] if args.prefill else []),
+                           env=env, check=True)
 
 
 if __name__ == "__main__":
