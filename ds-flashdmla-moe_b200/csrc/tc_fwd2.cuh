@@ -950,14 +950,9 @@ for (int i = 0; i < 4; ++i) {
                 }
                 if (row == 0) bulk_wait_read<0>();       // before the next item's P is written (barrier below)
             } else {
-#pragma unroll 1
-                for (int cc = 0; cc < O_COLS / 32; ++cc) {
-                    uint32_t o[32];
-                    if (n_tiles > 0 && ok) {
-                        tmem_ld32(tmem + lane_base + cc * 32, o);
-                        tmem_wait_ld();
-                    }
-                    if (!row_ok) continue;
+                // two 32-column reads of the accumulator in flight: the second is loaded while the first is converted and stored
+                auto put = [&](const uint32_t (&o)[32], const int cc) {
+                    if (!row_ok) return;
                     // 32-byte stores: a lane fills whole sectors of its own row
                     if (final_out) {
                         __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + grow * p.d_v + col0 + cc * 32;
@@ -983,6 +978,22 @@ for (int i = 0; i < 4; ++i) {
                             st_global_v8(dst + j, w);
                         }
                     }
+                };
+                const bool read_o = n_tiles > 0 && ok;
+                uint32_t oa[32], ob[32];
+                if (read_o) tmem_ld32(tmem + lane_base, oa);
+#pragma unroll 1
+                for (int cp = 0; cp < O_COLS / 64; ++cp) {
+                    if (read_o) {
+                        tmem_wait_ld();
+                        tmem_ld32(tmem + lane_base + (2 * cp + 1) * 32, ob);
+                    }
+                    put(oa, 2 * cp);
+                    if (read_o) {
+                        tmem_wait_ld();
+                        if (cp + 1 < O_COLS / 64) tmem_ld32(tmem + lane_base + (2 * cp + 2) * 32, oa);
+                    }
+                    put(ob, 2 * cp + 1);
                 }
             }
             if (row_ok && half == 0) {
@@ -1018,13 +1029,12 @@ for (int i = 0; i < 4; ++i) {
                     __threadfence();
                     // Each of the four warps merges 16 of the CTA's 64 rows, two rows at a time; a lane owns four
                     // consecutive d_v columns in each 128-column block, so every load and store of the warp is one
-                    // contiguous run, and all loads of a row pair are in flight together.
+                    // contiguous run; the loads of one piece of a row pair are in flight together.
                     const size_t slab = (size_t)p.G * p.R;
                     const int np = it.n_parts < 4 ? it.n_parts : 4;        // the launcher never plans more
                     const int w4 = warp & 3;
 #pragma unroll 1
                     for (int rp = 0; rp < 16; rp += 2) {
-                        float4 v[2][4][4];
                         float wgt[2][4], mx2[2], ls2[2];
                         size_t gr[2];
                         bool okr[2];
@@ -1033,16 +1043,6 @@ for (int i = 0; i < 4; ++i) {
                             const int r_in = it.row0 + 64 * (int)rank + w4 * 16 + rp + e;
                             okr[e] = r_in < p.R;
                             gr[e] = (size_t)it.g * p.R + (okr[e] ? r_in : 0);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                if (k < np) {
-                                    const float4 *src = reinterpret_cast<const float4 *>(p.O_part + (k * slab + gr[e]) * p.d_v) + lane;
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) v[e][k][j] = __ldcg(src + 32 * j);
-                                }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
                             float lk[4], mk[4];
                             mx2[e] = -CUDART_INF_F;
 #pragma unroll
@@ -1061,20 +1061,40 @@ for (int i = 0; i < 4; ++i) {
 #pragma unroll
                             for (int k = 0; k < 4; ++k) wgt[e][k] *= inv_l;
                         }
+                        // part by part: the eight loads of a part (two rows) are in flight together
+                        float4 acc[2][4];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) acc[e][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                        for (int k = 0; k < np; ++k) {
+                            float4 v[2][4];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const float4 *src = reinterpret_cast<const float4 *>(p.O_part + (k * slab + gr[e]) * p.d_v) + lane;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[e][j] = __ldcg(src + 32 * j);
+                            }
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const float wk = k == 0 ? wgt[e][0] : (k == 1 ? wgt[e][1] : (k == 2 ? wgt[e][2] : wgt[e][3]));
+                                if (wk > 0.f) {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        acc[e][j].x = fmaf(wk, v[e][j].x, acc[e][j].x); acc[e][j].y = fmaf(wk, v[e][j].y, acc[e][j].y);
+                                        acc[e][j].z = fmaf(wk, v[e][j].z, acc[e][j].z); acc[e][j].w = fmaf(wk, v[e][j].w, acc[e][j].w);
+                                    }
+                                }
+                            }
+                        }
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
                             if (!okr[e]) continue;
                             __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.O) + gr[e] * p.d_v + 4 * lane;
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                                for (int k = 0; k < 4; ++k)
-                                    if (k < np && wgt[e][k] > 0.f) {
-                                        acc.x = fmaf(wgt[e][k], v[e][k][j].x, acc.x); acc.y = fmaf(wgt[e][k], v[e][k][j].y, acc.y);
-                                        acc.z = fmaf(wgt[e][k], v[e][k][j].z, acc.z); acc.w = fmaf(wgt[e][k], v[e][k][j].w, acc.w);
-                                    }
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x, acc.y), h1 = __floats2bfloat162_rn(acc.z, acc.w);
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[e][j].x, acc[e][j].y), h1 = __floats2bfloat162_rn(acc[e][j].z, acc[e][j].w);
                                 *reinterpret_cast<uint2 *>(dst + 128 * j) =
                                     make_uint2(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1));
                             }
