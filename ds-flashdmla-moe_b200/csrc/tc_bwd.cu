@@ -24,6 +24,8 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -305,37 +307,52 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                 tmem_ld32(tmem + lane_base + C_T2 + (2 * hbuf_of(h) + cg) * 32, t2);
                 tmem_wait_ld();
                 uint32_t e1[16], e2[16];
+                // Is every score of this warp's 32 x 32 block visible (no key past the end, no causal mask)?  Then the
+                // per-score visibility tests are skipped.  The answer is the same in every lane of the warp.
+                bool all_vis;
+                if (MODE == MODE_DKV) {
+                    const int r_first = str0 + cc * 32, r_last = r_first + 31;
+                    all_vis = r_last < p.R && own0 + TILE - 1 < p.Skv &&
+                              (!p.causal || (r_first / p.Sq == r_last / p.Sq && own0 + TILE - 1 <= (r_first % p.Sq) + off));
+                } else {
+                    const int key_last = str0 + cc * 32 + 31;
+                    all_vis = __all_sync(0xffffffffu, own_ok && key_last < p.Skv && (!p.causal || key_last <= pos_lane + off));
+                }
+                auto block = [&](auto fast_tag) {
+                constexpr bool FAST = decltype(fast_tag)::value;
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
                     // four consecutive columns (streamed indices) at a time: their row statistics come as
                     // one 16-byte shared-memory read per array (MODE_DKV) or from registers (MODE_DQ)
                     const int c0 = cc * 32 + j;
                     float m2[4], il[4], dd[4];
-                    bool vis[4];
+                    bool vis[4] = {true, true, true, true};
                     if (MODE == MODE_DKV) {
                         const float4 a = *reinterpret_cast<const float4 *>(vb + c0);
                         const float4 b = *reinterpret_cast<const float4 *>(vb + TILE + c0);
                         const float4 d = *reinterpret_cast<const float4 *>(vb + 2 * TILE + c0);
-                        const int4 k = *reinterpret_cast<const int4 *>(vb + 3 * TILE + c0);
                         m2[0] = a.x; m2[1] = a.y; m2[2] = a.z; m2[3] = a.w;
                         il[0] = b.x; il[1] = b.y; il[2] = b.z; il[3] = b.w;
                         dd[0] = d.x; dd[1] = d.y; dd[2] = d.z; dd[3] = d.w;
-                        vis[0] = own_ok && own_idx <= k.x; vis[1] = own_ok && own_idx <= k.y;
-                        vis[2] = own_ok && own_idx <= k.z; vis[3] = own_ok && own_idx <= k.w;
+                        if (!FAST) {
+                            const int4 k = *reinterpret_cast<const int4 *>(vb + 3 * TILE + c0);
+                            vis[0] = own_ok && own_idx <= k.x; vis[1] = own_ok && own_idx <= k.y;
+                            vis[2] = own_ok && own_idx <= k.z; vis[3] = own_ok && own_idx <= k.w;
+                        }
                     } else {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int key = str0 + c0 + e;
                             m2[e] = m2_lane; il[e] = il_lane; dd[e] = D_lane;
-                            vis[e] = own_ok && key < p.Skv && (!p.causal || key <= pos_lane + off);
+                            if (!FAST) vis[e] = own_ok && key < p.Skv && (!p.causal || key <= pos_lane + off);
                         }
                     }
                     float pv[4], dsv[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float pr = vis[e] ? fast_exp2(fmaf(__uint_as_float(t1[j + e]), sl2, -m2[e])) * il[e] : 0.f;
+                        const float pr = (FAST || vis[e]) ? fast_exp2(fmaf(__uint_as_float(t1[j + e]), sl2, -m2[e])) * il[e] : 0.f;
                         pv[e] = pr;
-                        dsv[e] = vis[e] ? pr * (__uint_as_float(t2[j + e]) - dd[e]) : 0.f;
+                        dsv[e] = (FAST || vis[e]) ? pr * (__uint_as_float(t2[j + e]) - dd[e]) : 0.f;
                     }
 #pragma unroll
                     for (int e = 0; e < 4; e += 2) {
@@ -345,6 +362,9 @@ bwd_tc_kernel(const BwdProblem p, const __grid_constant__ CUtensorMap tmQ, const
                         e2[(j + e) >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                     }
                 }
+                };
+                if (all_vis) block(std::true_type{});
+                else block(std::false_type{});
                 // A-operand layout of the half tile: 8x8 core matrices, K (the streamed index) inside a core row
                 const int rowoff = hbuf_of(h) * E_BYTES + (L >> 3) * E_SBO + (L & 7) * 16 + (cc & 1) * 4 * 128;
 #pragma unroll
