@@ -57,6 +57,10 @@ def test_argument_validation_needs_no_gpu():
     # empty problems are a successful no-op, as in the reference (vanallia_attn.cu:95)
     assert L.fdmla_fwd_cache_latent(None, None, None, None, None, 0, 1, 1, 1, 16, 16, 1.0, 1, 0, None) == 0
     assert L.fdmla_merge_lse(None, None, None, None, None, None, 0, 16, 2, 0, None) == 0
+    # the per-rank partial of the sequence-split decode: empty batch is a no-op, missing outputs and scratch are refused
+    assert L.fdmla_decode_paged_partial(None, None, None, None, None, None, None, None, None, None, 0, 8, 576, 512, 64, 4, 4, 1, 0.1, 1, None) == 0
+    assert L.fdmla_decode_paged_partial(None, None, None, None, None, None, None, None, None, None, 2, 8, 576, 512, 64, 4, 4, 1, 0.1, 1, None) == -1
+    assert L.fdmla_decode_paged_partial(1, 1, 1, 1, 1, 1, 1, None, None, None, 2, 8, 576, 512, 64, 4, 4, 3, 0.1, 1, None) == -4
     assert L.fdmla_decode_paged(None, None, None, None, None, None, None, None, None, None,
                                 1, 1, 16, 16, 0, 1, 1, 1, 0, -1, 1.0, 0, None) == -1   # page_size 0
     assert L.fdmla_fwd_on_the_fly_workspace_bytes(2, 2, 16, 8, 1) == 2 * 256 * ((2 * 2 * 16 * 8 * 2 + 255) // 256)

@@ -28,6 +28,9 @@ def test_gemm_argument_validation_needs_no_gpu():
     assert L.fdmla_gemm_batched(None, None, None, None, 1, 8, 64, 64, 8, 64, 0, 0, 64, 64, 0, 0, 1, 64, 0, 0, 0, None) == -1
     assert L.fdmla_gemm_batched(1, 1, None, 1, 2, 8, 64, 64, 8, 64, 8, 0, 64, 64, 0, 0, 1, 64, 0, 0, 0, None) == -1   # A window past a_rows
     assert L.fdmla_gemm_batched(1, 1, None, 1, 1, 8, 64, 64, 8, 64, 0, 0, 64, 64, 0, 0, 1, 64, 0, 0, 1, None) == -1   # gated without B2
+    assert L.fdmla_gemm_grouped(None, None, None, None, None, 0, 128, 64, 64, 64, 64, 64, 64, 1, 64, 0, None) == 0
+    assert L.fdmla_gemm_grouped(None, None, None, None, None, 2, 128, 64, 64, 64, 64, 64, 64, 1, 64, 0, None) == -1
+    assert L.fdmla_gemm_grouped(1, 1, None, 1, 1, 2, 128, 64, 64, 64, 64, 64, 64, 1, 64, 0, None) == -1     # B window of group 1 past b_rows
     assert L.fdmla_rope_rows(None, 64, None, 64, None, 0, 1, 64, 10000.0, None) == 0
     assert L.fdmla_rope_rows(None, 64, None, 64, None, 4, 1, 64, 10000.0, None) == -1
 
