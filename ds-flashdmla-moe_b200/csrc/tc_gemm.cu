@@ -18,11 +18,20 @@
 // the 128-byte swizzle.  Warp 0 issues the copies, warp 1 the MMAs (one elected lane of a converged warp each),
 // warps 2-5 read the accumulator (thread = row) and store bf16 rows.  Every wait is bounded; a wait that gives up
 // sets a flag that fdmla_device_error_flag reports (code 21-23) and the roles run out.
+//
+// Problems whose batch entries fill 256-row tiles as well as 128-row ones run the same kernel over CTA pairs (clusters of two,
+// tcgen05.mma.cta_group::2): a tile is 256 x 256, each CTA loads its 128 rows of A and HALF of the B tile (128
+// output columns) and holds its 128 rows of the accumulator, so a k step costs 32 KB of shared memory per CTA
+// instead of 48 KB (six stages) and B crosses L2 -> shared memory once per pair.  Both CTAs' copies signal the
+// leader's "full" barrier directly (cta_group::2 loads, no multicast); the leader's warp 1 issues the pair's MMAs
+// and its commits arrive on the "empty" / "accumulator full" barriers of both CTAs.  In gated mode the leader's
+// half of the B tile is B and the peer's is B2.  FDMLA_GEMM_PAIR=0 / 1 in the environment forces one form.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -34,13 +43,18 @@ bool make_tensor_map_bf16_chunked(CUtensorMap *m, const void *base, long long ro
 
 namespace tcg {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;          // 16 384
-constexpr int B_BYTES = BN * BK * 2;          // 32 768
-constexpr int STAGE = A_BYTES + B_BYTES;
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int A_BYTES = BM * BK * 2;          // 16 384: the 128 rows of A one CTA loads per k step
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE + 256;
-static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
+template <bool PAIR> struct Cfg {
+    static constexpr int TILE_M = PAIR ? 2 * BM : BM;             // rows of one accumulator tile (both CTAs of a pair)
+    static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2; // of one CTA: 16 384 / 32 768
+    static constexpr int STAGES = PAIR ? 6 : 4;
+    static constexpr int STAGE = A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE + 256;
+    static_assert(SMEM_BYTES <= kMaxSmemPerBlock, "shared memory overflow");
+    static_assert((2 * STAGES + 4) * 8 + 8 <= 256, "barriers overflow their space");
+};
 enum { ERR_PRODUCER = 21, ERR_MMA = 22, ERR_EPILOGUE = 23 };
 
 __device__ int g_gemm_error = 0;
@@ -66,26 +80,26 @@ struct TileWalker {
     long long base = 0;          // tiles of the entries before b
     int m0, n0, rows, row0;      // of the located tile: first row inside the entry, first output column, the entry's rows
                                  // and its first row in A's / C's tensor (grouped mode)
-    __device__ __forceinline__ bool locate(const Problem &p, long long tile, int out_cols) {
+    __device__ __forceinline__ bool locate(const Problem &p, long long tile, int out_cols, int tile_m) {
         if (!p.row_offsets) {
             const int per = p.m_tiles * p.n_tiles;
             if (tile >= (long long)p.batch * per) return false;
             b = (int)(tile / per);
             const int r = (int)(tile - (long long)b * per);
             n0 = (r / p.m_tiles) * out_cols;
-            m0 = (r % p.m_tiles) * BM;
+            m0 = (r % p.m_tiles) * tile_m;
             rows = p.M;
             row0 = 0;
             return true;
         }
         while (b < p.batch) {
             const int lo = __ldg(p.row_offsets + b), hi = __ldg(p.row_offsets + b + 1);
-            const int mt = (hi - lo + BM - 1) / BM;
+            const int mt = (hi - lo + tile_m - 1) / tile_m;
             const long long tb = (long long)(mt > 0 ? mt : 0) * p.n_tiles;
             if (tile < base + tb) {
                 const int r = (int)(tile - base);
                 n0 = (r / mt) * out_cols;
-                m0 = (r % mt) * BM;
+                m0 = (r % mt) * tile_m;
                 rows = hi - lo;
                 row0 = lo;
                 return true;
@@ -99,10 +113,13 @@ struct TileWalker {
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmB2) {
     using namespace ptx;
+    using C = Cfg<PAIR>;
+    constexpr int STAGES = C::STAGES, STAGE = C::STAGE, B_BYTES = C::B_BYTES, TILE_M = C::TILE_M;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE);
@@ -114,19 +131,29 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
     auto ACC_FULL = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
     auto ACC_EMPTY = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // pair form: CTA `rank` of the cluster owns rows [128 rank, +128) of every tile and half of its B operand
+    const int rank = PAIR ? (int)cluster_ctarank() : 0;
+    const long long first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
+    const long long tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
 
     if (threadIdx.x == 0) {
         *err_slot = *reinterpret_cast<volatile int *>(&g_gemm_error);      // one reading for all roles
         for (int s = 0; s < STAGES; ++s) { mbar_init(FULL(s), 1); mbar_init(EMPTY(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(ACC_FULL(a), 1); mbar_init(ACC_EMPTY(a), 128); }
+        // accumulator free: every epilogue thread arrives; pair form: one arrival per CTA, on the leader's barrier
+        for (int a = 0; a < 2; ++a) { mbar_init(ACC_FULL(a), 1); mbar_init(ACC_EMPTY(a), PAIR ? 2 : 128); }
         fence_mbar_init();
     }
-    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    if (warp == 1) {
+        if (PAIR) { tmem_alloc_2cta(smem_u32(tmem_slot), 512); tmem_relinquish_2cta(); }
+        else { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    }
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR) { __syncwarp(); cluster_sync_all(); }      // the peer's barriers exist before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const bool poisoned = *err_slot != 0;            // an earlier launch gave up a wait: do nothing until the flag is cleared
+    // an earlier launch gave up a wait: do nothing until the flag is cleared (both CTAs of a pair take the leader's reading)
+    const bool poisoned = (PAIR ? (int)ld_shared_cluster_u32(map_to_cta(smem_u32(err_slot), 0)) : *err_slot) != 0;
 
     const int k_steps = p.K / BK;
     const int out_cols = p.gated ? BN / 2 : BN;         // output columns of one tile
@@ -137,34 +164,38 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         // ================================ TMA producer ================================
         const bool elected = elect_one();
         if (lane == 0) { prefetch_tmap(&tmA); prefetch_tmap(&tmB); if (p.gated) prefetch_tmap(&tmB2); }
+        const uint32_t full_lead = PAIR ? map_to_cta(FULL(0), 0) : 0;     // the leader's "full" barriers
         bool ok = true;
         int s = 0, use = 0;
         TileWalker w;
-        for (long long tile = blockIdx.x; !poisoned && ok && w.locate(p, tile, out_cols); tile += gridDim.x) {
+        for (long long tile = first_tile; !poisoned && ok && w.locate(p, tile, out_cols, TILE_M); tile += tile_step) {
             const int b = w.b, m0 = w.m0, n0 = w.n0;
-            const int a_row = (p.row_offsets ? w.row0 : b * p.a_brow) + m0;
+            const int a_row = (p.row_offsets ? w.row0 : b * p.a_brow) + m0 + rank * BM;
             for (int kb = 0; kb < k_steps && ok; ++kb) {
                 if (use > 0) ok = mbar_wait(EMPTY(s), (use - 1) & 1);
                 if (ok && elected) {
                     const uint32_t dstA = smem_u32(smem + s * STAGE), dstB = dstA + A_BYTES;
-                    mbar_arrive_expect_tx(FULL(s), STAGE);
-                    tma_load_2d(dstA, &tmA, b * p.a_bcol + kb * BK, a_row, FULL(s));
-                    if (p.b_k_major) {
-                        // [256 output columns x 64] K-major: rows of B's tensor are output columns
-                        if (!p.gated) {
-                            tma_load_2d(dstB, &tmB, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
-                        } else {
-                            tma_load_2d(dstB, &tmB, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
-                            tma_load_2d(dstB + B_BYTES / 2, &tmB2, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
-                        }
+                    if constexpr (PAIR) {
+                        const uint32_t full = full_lead + 8u * s;
+                        if (rank == 0) mbar_arrive_expect_tx(FULL(s), 2 * STAGE);     // both CTAs' bytes
+                        tma_load_2d_pair(dstA, &tmA, b * p.a_bcol + kb * BK, a_row, full);
+                        // this CTA's half of B: 128 output columns; gated: the leader brings B, the peer B2
+                        const CUtensorMap *tb = (p.gated && rank) ? &tmB2 : &tmB;
+                        const int n_half = n0 + (p.gated ? 0 : rank * (BN / 2));
+                        if (p.b_k_major) tma_load_2d_pair(dstB, tb, b * p.b_bcol + kb * BK, b * p.b_brow + n_half, full);
+                        else tma_load_3d_pair(dstB, tb, 0, b * p.b_brow + kb * BK, (b * p.b_bcol + n_half) >> 6, full);
                     } else {
-                        // [64 x 256 output columns] MN-major: four (gated: two and two) chunks of [64 rows x 128 B]
-                        const int chunk0 = (b * p.b_bcol + n0) >> 6;
-                        if (!p.gated) {
-                            tma_load_3d(dstB, &tmB, 0, b * p.b_brow + kb * BK, chunk0, FULL(s));
+                        mbar_arrive_expect_tx(FULL(s), STAGE);
+                        tma_load_2d(dstA, &tmA, b * p.a_bcol + kb * BK, a_row, FULL(s));
+                        if (p.b_k_major) {
+                            // [256 output columns x 64] K-major: rows of B's tensor are output columns
+                            tma_load_2d(dstB, &tmB, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
+                            if (p.gated) tma_load_2d(dstB + B_BYTES / 2, &tmB2, b * p.b_bcol + kb * BK, b * p.b_brow + n0, FULL(s));
                         } else {
+                            // [64 x 256 output columns] MN-major: four (gated: two and two) chunks of [64 rows x 128 B]
+                            const int chunk0 = (b * p.b_bcol + n0) >> 6;
                             tma_load_3d(dstB, &tmB, 0, b * p.b_brow + kb * BK, chunk0, FULL(s));
-                            tma_load_3d(dstB + B_BYTES / 2, &tmB2, 0, b * p.b_brow + kb * BK, chunk0, FULL(s));
+                            if (p.gated) tma_load_3d(dstB + B_BYTES / 2, &tmB2, 0, b * p.b_brow + kb * BK, chunk0, FULL(s));
                         }
                     }
                 }
@@ -174,15 +205,15 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, ERR_PRODUCER);
         __syncwarp();
     } else if (warp == 1) {
-        // ================================ MMA issuer ==================================
+        // ================================ MMA issuer (pair form: the leader's only) ==================================
         const bool elected = elect_one();
-        const uint32_t idesc = make_idesc_bf16(BM, BN, 0, p.b_k_major ? 0 : 1);
+        const uint32_t idesc = make_idesc_bf16(TILE_M, BN, 0, p.b_k_major ? 0 : 1);
         bool ok = true;
         int s = 0;
         uint32_t ph = 0;
         int n_done = 0;                              // tiles this CTA has issued
         TileWalker w;
-        for (long long tile = blockIdx.x; !poisoned && w.locate(p, tile, out_cols); tile += gridDim.x, ++n_done) {
+        for (long long tile = first_tile; !poisoned && rank == 0 && w.locate(p, tile, out_cols, TILE_M); tile += tile_step, ++n_done) {
             if (!__all_sync(0xffffffffu, ok)) break;
             const int acc = n_done & 1;
             if (n_done >= 2) {
@@ -199,10 +230,16 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
                         const uint64_t da = make_smem_desc(a_addr + k * 32, 16, 1024, kLayoutSw128);
                         const uint64_t db = p.b_k_major ? make_smem_desc(b_addr + k * 32, 16, 1024, kLayoutSw128)
                                                         : make_smem_desc(b_addr + k * 2048, 8192, 1024, kLayoutSw128);
-                        mma_bf16_ss(tmem + acc * BN, da, db, idesc, (kb | k) != 0);
+                        if constexpr (PAIR) mma_bf16_ss_2cta(tmem + acc * BN, da, db, idesc, (kb | k) != 0);
+                        else mma_bf16_ss(tmem + acc * BN, da, db, idesc, (kb | k) != 0);
                     }
-                    mma_commit(EMPTY(s));
-                    if (kb == k_steps - 1) mma_commit(ACC_FULL(acc));
+                    if constexpr (PAIR) {
+                        mma_commit_2cta(EMPTY(s), 3);
+                        if (kb == k_steps - 1) mma_commit_2cta(ACC_FULL(acc), 3);
+                    } else {
+                        mma_commit(EMPTY(s));
+                        if (kb == k_steps - 1) mma_commit(ACC_FULL(acc));
+                    }
                 }
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
@@ -211,17 +248,18 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         __syncwarp();
     } else {
         // ================================ epilogue ====================================
-        const int L = (warp & 3) * 32 + lane;                      // TMEM lane = row of the tile
+        const int L = (warp & 3) * 32 + lane;                      // TMEM lane = row of this CTA's part of the tile
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t acc_empty_lead = PAIR ? map_to_cta(ACC_EMPTY(0), 0) : 0;
         bool ok = true;
         int n_done = 0;
         TileWalker w;
-        for (long long tile = blockIdx.x; !poisoned && w.locate(p, tile, out_cols); tile += gridDim.x, ++n_done) {
+        for (long long tile = first_tile; !poisoned && w.locate(p, tile, out_cols, TILE_M); tile += tile_step, ++n_done) {
             const int b = w.b, m0 = w.m0, n0 = w.n0;
             const int acc = n_done & 1;
             if (ok) ok = mbar_wait(ACC_FULL(acc), (n_done >> 1) & 1);
             tc_fence_after_sync();
-            const int m = m0 + L;
+            const int m = m0 + rank * BM + L;
             const long long c_off = ((p.row_offsets ? (long long)w.row0 : (long long)b * p.c_brow) + m) * p.ldc +
                                     (long long)b * p.c_bcol + n0;
             __nv_bfloat16 *crow = static_cast<__nv_bfloat16 *>(p.C) + c_off;
@@ -269,16 +307,46 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
                 }
             }
             tc_fence_before_sync();
-            mbar_arrive(ACC_EMPTY(acc));                           // 128 arrivals free the accumulator
+            if constexpr (PAIR) {
+                named_bar_sync(1, 128);                                // this CTA's 128 rows have been read ...
+                if (L == 0) mbar_arrive_cluster_relaxed(acc_empty_lead + 8u * acc);   // ... one arrival per CTA frees the accumulator
+            } else {
+                mbar_arrive(ACC_EMPTY(acc));                           // 128 arrivals free the accumulator
+            }
         }
         if (!ok) atomicCAS(&g_gemm_error, 0, ERR_EPILOGUE);
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR) { __syncwarp(); cluster_sync_all(); }      // neither CTA leaves while the pair can still touch its memory
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem, 512);
+        if (PAIR) tmem_dealloc_2cta(tmem, 512); else tmem_dealloc(tmem, 512);
     }
+}
+
+// CTA pairs that can be resident at once (cached per device); 0 if clusters of two cannot be launched
+static int max_pairs(int dev, int sms) {
+    static std::atomic<int> cached[64];
+    if (dev < 0 || dev >= 64) return sms / 2;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n != 0) return n > 0 ? n : 0;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * (unsigned)(sms / 2));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, gemm_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = -1;
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
+    return n > 0 ? n : 0;
 }
 
 }  // namespace tcg
@@ -316,12 +384,23 @@ int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, i
     p.alpha = alpha; p.c_f32 = c_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
     p.b_k_major = b_k_major ? 1 : 0; p.gated = gated ? 1 : 0;
     p.row_offsets = row_offsets;
+    int dev = 0, sms = kNumSMs;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // CTA pairs with 256-row tiles when that pads an entry's rows no further than 128-row tiles would (ragged entries:
+    // when they are tall enough for the half tile more that each may waste not to matter)
+    static const int forced = [] { const char *e = getenv("FDMLA_GEMM_PAIR"); return e && *e ? atoi(e) : -1; }();
+    bool pair = row_offsets ? (long long)M >= 512LL * batch : (M > BM && ((M + BM - 1) / BM) % 2 == 0);
+    if (forced >= 0) pair = forced != 0;
+    const int pairs = pair ? max_pairs(dev, sms) : 0;
+    if (pairs <= 0) pair = false;
+    const int tile_m = pair ? 2 * BM : BM;
     const int out_cols = gated ? BN / 2 : BN;
-    p.m_tiles = (M + BM - 1) / BM;
+    p.m_tiles = (M + tile_m - 1) / tile_m;
     p.n_tiles = (N + out_cols - 1) / out_cols;
     CUtensorMap tmA, tmB, tmB2;
     if (!make_tensor_map_bf16(&tmA, A, a_rows, (int)lda, BM)) return FDMLA_ERR_CUDA;
-    const int b_box = gated ? BN / 2 : BN;          // output columns brought by one copy
+    // output columns brought by one copy: a CTA of a pair brings 128 (all of its half: B, or B2 in the peer when gated)
+    const int b_box = (gated || pair) ? BN / 2 : BN;
     if (b_k_major) {
         if (!make_tensor_map_bf16(&tmB, B, b_rows, (int)ldb, b_box)) return FDMLA_ERR_CUDA;
         tmB2 = tmB;
@@ -331,14 +410,26 @@ int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, i
         tmB2 = tmB;
         if (gated && !make_tensor_map_bf16_chunked(&tmB2, B2, b_rows, (int)ldb, BK, b_box / 64)) return FDMLA_ERR_CUDA;
     }
-    if (cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-        return FDMLA_ERR_CUDA;
     // grouped mode: M is the total of all entries' rows; every entry may add one partly filled row tile
-    const long long tiles = row_offsets ? ((long long)(M + BM - 1) / BM + batch) * p.n_tiles : (long long)batch * p.m_tiles * p.n_tiles;
-    int dev = 0, sms = kNumSMs;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long tiles = row_offsets ? ((long long)(M + tile_m - 1) / tile_m + batch) * p.n_tiles : (long long)batch * p.m_tiles * p.n_tiles;
+    if (pair) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(2 * (unsigned)(tiles < pairs ? tiles : pairs));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, gemm_kernel<true>, p, tmA, tmB, tmB2) != cudaSuccess) { cudaGetLastError(); return FDMLA_ERR_CUDA; }
+        return check_launch();
+    }
+    if (cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES) != cudaSuccess)
+        return FDMLA_ERR_CUDA;
     const int grid = (int)(tiles < sms ? tiles : sms);
-    gemm_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p, tmA, tmB, tmB2);
+    gemm_kernel<false><<<grid, THREADS, Cfg<false>::SMEM_BYTES, stream>>>(p, tmA, tmB, tmB2);
     return check_launch();
 }
 
