@@ -242,7 +242,7 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 merge_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
              const float *__restrict__ l_part, TO *__restrict__ O, float *__restrict__ m,
-             float *__restrict__ l, long long rows, int d_v, int P, size_t so, size_t sml) {
+             float *__restrict__ l, long long rows, int d_v, int P, size_t so, size_t sml, bool vec) {
     const int lane = threadIdx.x & 31;
     const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
     for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
@@ -268,7 +268,7 @@ merge_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
                 if (lp > 0.f) {
                     const float w = lp * __expf(m_part[q * sml + r] - mx) * inv;
                     const float *src = O_part + (size_t)q * so + (size_t)r * d_v;
-                    if (c + 3 < d_v && (d_v & 3) == 0) {
+                    if (vec && c + 3 < d_v) {
                         const float4 v = *reinterpret_cast<const float4 *>(src + c);
                         acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
                         acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
@@ -290,7 +290,7 @@ template <typename TO>
 __global__ void __launch_bounds__(128)
 merge_row_block_kernel(const float *__restrict__ O_part, const float *__restrict__ m_part,
                        const float *__restrict__ l_part, TO *__restrict__ O, float *__restrict__ m,
-                       float *__restrict__ l, long long rows, int d_v, int P, size_t so, size_t sml) {
+                       float *__restrict__ l, long long rows, int d_v, int P, size_t so, size_t sml, bool vec) {
     const long long r = blockIdx.x;
     if (l_part[r] < 0.f) return;
     float mx = -CUDART_INF_F;
@@ -310,7 +310,7 @@ merge_row_block_kernel(const float *__restrict__ O_part, const float *__restrict
             if (lp > 0.f) {
                 const float w = lp * __expf(m_part[q * sml + r] - mx) * inv;
                 const float *src = O_part + (size_t)q * so + (size_t)r * d_v;
-                if (c + 3 < d_v && (d_v & 3) == 0) {
+                if (vec && c + 3 < d_v) {
                     const float4 v = *reinterpret_cast<const float4 *>(src + c);
                     acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
                     acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
@@ -332,13 +332,16 @@ int launch_merge_strided(const float *O_part, const float *m_part, const float *
                          float *m, float *l, long long rows, int d_v, int num_parts, size_t part_stride_o,
                          size_t part_stride_ml, int out_dtype, cudaStream_t stream) {
     if (rows <= 0) return FDMLA_OK;
+    // 16-byte loads of O_part only where every part's rows start on a 16-byte boundary (gathered messages of an odd
+    // number of rows do not)
+    const bool vec = (d_v & 3) == 0 && (part_stride_o & 3) == 0 && (reinterpret_cast<uintptr_t>(O_part) & 15) == 0;
     if (rows <= 4096) {      // a block per row keeps more of the GPU busy than a warp per row would
         if (out_dtype == FDMLA_F32)
             merge_row_block_kernel<float><<<(unsigned)rows, 128, 0, stream>>>(O_part, m_part, l_part, static_cast<float *>(O), m, l,
-                                                                               rows, d_v, num_parts, part_stride_o, part_stride_ml);
+                                                                               rows, d_v, num_parts, part_stride_o, part_stride_ml, vec);
         else if (out_dtype == FDMLA_BF16)
             merge_row_block_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(
-                O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O), m, l, rows, d_v, num_parts, part_stride_o, part_stride_ml);
+                O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O), m, l, rows, d_v, num_parts, part_stride_o, part_stride_ml, vec);
         else
             return FDMLA_ERR_INVALID;
         return check_launch();
@@ -347,10 +350,10 @@ int launch_merge_strided(const float *O_part, const float *m_part, const float *
     const unsigned grid = (unsigned)(want < 8LL * kNumSMs ? want : 8LL * kNumSMs);
     if (out_dtype == FDMLA_F32)
         merge_kernel<float><<<grid, 256, 0, stream>>>(O_part, m_part, l_part, static_cast<float *>(O), m, l, rows,
-                                                      d_v, num_parts, part_stride_o, part_stride_ml);
+                                                      d_v, num_parts, part_stride_o, part_stride_ml, vec);
     else if (out_dtype == FDMLA_BF16)
         merge_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(O_part, m_part, l_part, static_cast<__nv_bfloat16 *>(O),
-                                                             m, l, rows, d_v, num_parts, part_stride_o, part_stride_ml);
+                                                             m, l, rows, d_v, num_parts, part_stride_o, part_stride_ml, vec);
     else
         return FDMLA_ERR_INVALID;
     return check_launch();
