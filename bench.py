@@ -631,7 +631,34 @@ def bench_long_context(dev, rank, world, steps=50, warmup=10):
     else:
         res[0] = dec.step(Q, lpool, ltab, llen)
     torch.cuda.synchronize()
-    total_ms = graph_ms if graph_ms is not None else prealloc_ms
+    # the same step with the exchange and the merge as one kernel over peer memory (no collective library on the path)
+    peer_eager_ms = peer_graph_ms = None
+    peer_equal = None
+    peer_ok = 1
+    pdec = None
+    try:
+        pdec = parallel.SequenceParallelDecoder(B8, H, D_QK, D_V, PAGE, int(llen.max().item()), dev, scale=SCALE, exchange="peer")
+    except Exception as exc:                          # CUDA IPC between the ranks' processes refused on this machine
+        peer_ok = 0
+        sys.stderr.write(f"rank {rank}: peer exchange not set up: {exc}\n")
+    flag = torch.tensor([peer_ok], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 1:
+        want = tuple(t.clone() for t in res[0])
+        got = pdec.step(Q, lpool, ltab, llen)
+        torch.cuda.synchronize()
+        peer_equal = bool(all(torch.equal(a, b) for a, b in zip(got, want)))
+        dist.barrier()
+        peer_eager_ms = time_steps(lambda: pdec.step(Q, lpool, ltab, llen), steps, 3, world) / steps
+        pdec.capture(Q, lpool, ltab, llen)
+        dist.barrier()
+        peer_graph_ms = time_steps(pdec.replay, steps, 3, world) / steps
+        torch.cuda.synchronize()
+        if peer_equal and flashdmla.device_error_flag() == 0 and (graph_ms is None or peer_graph_ms < graph_ms):
+            res[0] = pdec.replay()
+            torch.cuda.synchronize()
+    use_peer = peer_graph_ms is not None and peer_equal and (graph_ms is None or peer_graph_ms < graph_ms)
+    total_ms = peer_graph_ms if use_peer else (graph_ms if graph_ms is not None else prealloc_ms)
     O, m, l = res[0]
     err = float((O.float() - O1.float()).abs().max())
     msg_bytes = B8 * H * (D_V + 2) * 4
@@ -639,9 +666,13 @@ def bench_long_context(dev, rank, world, steps=50, warmup=10):
     return {"workload": f"long-context decode B={B8} H={H} Skv~U[16384,131072] page={PAGE}, KV split over {world} GPUs "
                         f"(sequence lengths {lens})",
             "tokens_per_s": B8 / (total_ms * 1e-3), "ms_per_step": total_ms,
-            "ms_per_step_how": ("whole step replayed from a CUDA graph (SequenceParallelDecoder)" if graph_ms is not None
+            "ms_per_step_how": ("whole step replayed from a CUDA graph, exchange + merge as one kernel over peer memory "
+                                "(SequenceParallelDecoder, exchange='peer')" if use_peer else
+                                "whole step replayed from a CUDA graph (SequenceParallelDecoder)" if graph_ms is not None
                                 else "eager steps on preallocated buffers (SequenceParallelDecoder)"),
             "ms_per_step_eager_python": eager_ms, "ms_per_step_preallocated": prealloc_ms, "ms_per_step_graph": graph_ms,
+            "ms_per_step_peer_exchange_eager": peer_eager_ms, "ms_per_step_peer_exchange_graph": peer_graph_ms,
+            "peer_exchange_bit_identical_to_nccl_path": peer_equal,
             "phase_times_note": "local / all-gather / merge are CUDA-event spans of the eager Python step: they include the "
                                 "host's enqueue gaps",
             "local_splits": dec.splits,

@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 #include <atomic>
+#include <cstring>
 
 namespace fdmla {
 
@@ -138,8 +139,58 @@ int fdmla_get_backend(void) { return g_backend.load(); }
 int fdmla_set_single_cta(int on) { tensor_prefer_single_cta(on != 0); return FDMLA_OK; }
 const char *fdmla_last_kernel(void) { return t_last_kernel; }
 int fdmla_device_error_flag(int reset) {
-    const int fwd = tensor_error_flag(reset), bwd = bwd_tensor_error_flag(reset), gemm = gemm_error_flag(reset);
-    return fwd ? fwd : (bwd ? bwd : gemm);
+    const int fwd = tensor_error_flag(reset), bwd = bwd_tensor_error_flag(reset), gemm = gemm_error_flag(reset),
+              xch = exchange_error_flag(reset);
+    return fwd ? fwd : (bwd ? bwd : (gemm ? gemm : xch));
+}
+
+size_t fdmla_exchange_bytes(int world, long long rows, int d_v) { return exchange_bytes(world, rows, d_v); }
+
+int fdmla_exchange_alloc(size_t bytes, void **buf, void *ipc_handle) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the header promises a 64-byte handle");
+    if (!buf || !ipc_handle || bytes == 0) return FDMLA_ERR_INVALID;
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return FDMLA_ERR_CUDA; }
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return FDMLA_ERR_CUDA;
+    }
+    memcpy(ipc_handle, &h, sizeof(h));
+    *buf = p;
+    return FDMLA_OK;
+}
+
+int fdmla_exchange_open(const void *ipc_handle, void **peer_buf) {
+    if (!ipc_handle || !peer_buf) return FDMLA_ERR_INVALID;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handle, sizeof(h));
+    void *p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return FDMLA_ERR_CUDA; }
+    *peer_buf = p;
+    return FDMLA_OK;
+}
+
+int fdmla_exchange_close(void *peer_buf) {
+    if (!peer_buf) return FDMLA_OK;
+    if (cudaIpcCloseMemHandle(peer_buf) != cudaSuccess) { cudaGetLastError(); return FDMLA_ERR_CUDA; }
+    return FDMLA_OK;
+}
+
+int fdmla_exchange_free(void *buf) {
+    if (!buf) return FDMLA_OK;
+    if (cudaFree(buf) != cudaSuccess) { cudaGetLastError(); return FDMLA_ERR_CUDA; }
+    return FDMLA_OK;
+}
+
+int fdmla_exchange_merge(const float *msg, void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
+                         float *m, float *l, int out_dtype, int timeout_ms, void *stream) {
+    const int rc = launch_exchange_merge(msg, bufs, world, rank, rows, d_v, O, m, l, out_dtype, timeout_ms,
+                                         static_cast<cudaStream_t>(stream));
+    if (rc == FDMLA_OK && rows > 0) t_last_kernel = "exchange_merge_kernel";
+    return rc;
 }
 
 int fdmla_fwd_cache_latent(const void *Q, const void *K_lat, void *O, float *m, float *l, int B,

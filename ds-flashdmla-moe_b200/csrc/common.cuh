@@ -138,6 +138,10 @@ int launch_bwd_cache_latent_tensor(const BwdProblem &p, void *workspace, size_t 
 int launch_rope_rows(const void *x, long long ldx, void *y, long long ldy, const int32_t *pos, long long rows,
                      int rows_per_pos, int d, float base, cudaStream_t stream);
 int gemm_error_flag(int reset);
+int exchange_error_flag(int reset);
+size_t exchange_bytes(int world, long long rows, int d_v);
+int launch_exchange_merge(const void *msg, void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
+                          float *m, float *l, int out_dtype, int timeout_ms, cudaStream_t stream);
 // tcgen05 projections / weight-gradient partials for widths (128 -> 64) and (64 -> 128 transposed); they return
 // FDMLA_ERR_UNSUPPORTED for other shapes
 int launch_project_tensor(const void *X, const void *W, void *Y, long long rows, int d_in, int d_out, int w_transposed,

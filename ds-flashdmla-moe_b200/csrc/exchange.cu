@@ -1,0 +1,215 @@
+// Exchange and merge of the ranks' partial attention results in ONE kernel, over NVLink peer memory.
+//
+// Long-context decode splits every sequence's KV cache over the GPUs of a node; each rank attends its slice and holds
+// a partial result per row - O (normalised, d_v floats), m (row maximum), l (row sum) - in one fp32 message
+// [ O (rows x d_v) | m (rows) | l (rows) ].  Every rank needs the merged result.  The reference's MPI wrapper gathers K
+// and V themselves with MPI_Allgatherv on the host (csrc/attention/fa2_fwd_mpi.cu:65-74) and runs the whole attention
+// on every rank; the merge rule is the running update of csrc/attention/fa2_fwd.cu:93-111 applied across partials:
+//     m = max_p m_p,   w_p = l_p exp(m_p - m),   l = sum_p w_p,   O = sum_p (w_p / l) O_p.
+//
+// Every rank owns an exchange buffer that its peers have mapped (CUDA IPC):
+//     [ slot 0: world messages | slot 1: world messages | flags: world x GRID words | step counters: GRID words ]
+// One launch of exchange_merge_kernel on every rank does the step.  The grid is GRID thread blocks on every rank (all
+// resident at once: 128 threads, no shared memory to speak of); block c owns the same run of rows everywhere.
+//   1. it copies its rows of this rank's message into message [rank] of the current slot of every peer's buffer
+//      (plain 16-byte stores to peer memory), fences at system scope, and writes the step number into
+//      flags[rank][c] of every peer (st.release.sys);
+//   2. it waits until flags[p][c] of its own buffer has reached the step number for every peer p (ld.acquire.sys;
+//      bounded by a time limit on the global timer - a peer that never arrives sets error code 31 and the block
+//      returns without writing a result);
+//   3. it merges its rows: this rank's part straight from the message, the peers' parts from its own buffer.
+// A block never waits for another block of its own GPU, so nothing depends on the order in which blocks are scheduled.
+// The step number is a counter kept per block in the rank's own buffer (a CUDA graph replays the launch unchanged);
+// the slot alternates with it: a peer can only be one step ahead (it needs this rank's flags of step s to finish
+// step s), so it writes slot (s + 1) & 1 while this rank may still read slot s & 1.  All ranks must launch the same
+// sequence of steps on one exchange, each rank from one stream, as with a collective.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace fdmla {
+namespace xch {
+
+constexpr int GRID = 128, THREADS = 128, MAX_WORLD = 16;
+enum { ERR_EXCHANGE_TIMEOUT = 31 };
+
+__device__ int g_xch_error = 0;
+
+struct Args {
+    const float *msg;              // this rank's message
+    float *bufs[MAX_WORLD];        // exchange buffer of every rank as mapped here; bufs[rank] is this rank's own
+    int world, rank;
+    long long rows;
+    int d_v;
+    size_t stride;                 // floats between messages of a slot (the message size rounded up to 16 bytes)
+    void *O;
+    float *m, *l;
+    unsigned long long timeout_ns;
+};
+
+__host__ __device__ inline size_t message_stride(long long rows, int d_v) {
+    return ((size_t)rows * (size_t)(d_v + 2) + 3) & ~(size_t)3;
+}
+__host__ __device__ inline size_t flags_offset_floats(int world, size_t stride) { return 2 * (size_t)world * stride; }
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+template <typename TO> __device__ __forceinline__ TO out_from_f32(float x);
+template <> __device__ __forceinline__ float out_from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 out_from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+template <typename TO>
+__global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
+    const int c = blockIdx.x, tid = threadIdx.x, W = a.world;
+    float *own = a.bufs[a.rank];
+    uint32_t *flags_own = reinterpret_cast<uint32_t *>(own + flags_offset_floats(W, a.stride));     // [world][GRID]
+    uint32_t *steps = flags_own + (size_t)W * GRID;                                                 // [GRID]
+    __shared__ uint32_t s_step;
+    __shared__ int s_bad;
+    if (tid == 0) {
+        s_step = steps[c] + 1;
+        steps[c] = s_step;
+        s_bad = 0;
+    }
+    __syncthreads();
+    const uint32_t step = s_step;
+    const size_t slot_off = (size_t)(step & 1) * W * a.stride;
+    const long long per = (a.rows + GRID - 1) / GRID;
+    const long long r0 = (long long)c * per;
+    const long long r1 = r0 + per < a.rows ? r0 + per : a.rows;
+    const long long nr = r1 > r0 ? r1 - r0 : 0;
+    const size_t o_m = (size_t)a.rows * a.d_v, o_l = o_m + (size_t)a.rows;       // offsets of m and l in a message
+
+    // ---- 1. this block's rows of this rank's message into every peer's buffer ----------------------------
+    {
+        const float4 *src = reinterpret_cast<const float4 *>(a.msg + (size_t)r0 * a.d_v);
+        const long long n4 = nr * a.d_v / 4;
+        for (long long i = tid; i < n4; i += THREADS) {
+            const float4 v = src[i];
+            for (int p = 0; p < W; ++p)
+                if (p != a.rank)
+                    reinterpret_cast<float4 *>(a.bufs[p] + slot_off + (size_t)a.rank * a.stride + (size_t)r0 * a.d_v)[i] = v;
+        }
+        for (long long i = tid; i < nr; i += THREADS) {
+            const float mv = a.msg[o_m + r0 + i], lv = a.msg[o_l + r0 + i];
+            for (int p = 0; p < W; ++p)
+                if (p != a.rank) {
+                    float *dst = a.bufs[p] + slot_off + (size_t)a.rank * a.stride;
+                    dst[o_m + r0 + i] = mv;
+                    dst[o_l + r0 + i] = lv;
+                }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < W && tid != a.rank) {
+        uint32_t *peer_flags = reinterpret_cast<uint32_t *>(a.bufs[tid] + flags_offset_floats(W, a.stride));
+        st_release_sys(peer_flags + (size_t)a.rank * GRID + c, step);
+    }
+
+    // ---- 2. until every peer's rows of this block have landed here -----------------------------------------
+    if (tid < W && tid != a.rank) {
+        const unsigned long long t0 = global_timer_ns();
+        const uint32_t *f = flags_own + (size_t)tid * GRID + c;
+        while ((int)(ld_acquire_sys(f) - step) < 0) {
+            if (global_timer_ns() - t0 > a.timeout_ns) {
+                atomicCAS(&g_xch_error, 0, ERR_EXCHANGE_TIMEOUT);
+                s_bad = 1;
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    if (s_bad) return;
+
+    // ---- 3. merge (the arithmetic of the merge kernel of the split-KV decode, part by part in rank order) ----
+    TO *O = static_cast<TO *>(a.O);
+    for (long long r = r0; r < r1; ++r) {
+        float mx = -CUDART_INF_F;
+        for (int q = 0; q < W; ++q) {
+            const float *part = q == a.rank ? a.msg : own + slot_off + (size_t)q * a.stride;
+            if (__ldcg(part + o_l + r) > 0.f) mx = fmaxf(mx, __ldcg(part + o_m + r));
+        }
+        float ls = 0.f;
+        for (int q = 0; q < W; ++q) {
+            const float *part = q == a.rank ? a.msg : own + slot_off + (size_t)q * a.stride;
+            const float lp = __ldcg(part + o_l + r);
+            if (lp > 0.f) ls += lp * __expf(__ldcg(part + o_m + r) - mx);
+        }
+        const float inv = ls > 0.f ? 1.f / ls : 0.f;
+        for (int col = tid * 4; col < a.d_v; col += 4 * THREADS) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < W; ++q) {
+                const float *part = q == a.rank ? a.msg : own + slot_off + (size_t)q * a.stride;
+                const float lp = __ldcg(part + o_l + r);
+                if (lp > 0.f) {
+                    const float w = lp * __expf(__ldcg(part + o_m + r) - mx) * inv;
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(part + (size_t)r * a.d_v + col));
+                    acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
+                    acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+                }
+            }
+            for (int e = 0; e < 4; ++e) O[(size_t)r * a.d_v + col + e] = out_from_f32<TO>(acc[e]);
+        }
+        if (tid == 0) { a.m[r] = mx; a.l[r] = ls; }
+    }
+}
+
+}  // namespace xch
+
+int exchange_error_flag(int reset) {
+    int v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, xch::g_xch_error, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(xch::g_xch_error, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
+    return v;
+}
+
+size_t exchange_bytes(int world, long long rows, int d_v) {
+    if (world < 1 || world > xch::MAX_WORLD || rows <= 0 || d_v <= 0 || (d_v & 3)) return 0;
+    const size_t stride = xch::message_stride(rows, d_v);
+    return (xch::flags_offset_floats(world, stride) + (size_t)world * xch::GRID + xch::GRID) * sizeof(float);
+}
+
+int launch_exchange_merge(const void *msg, void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
+                          float *m, float *l, int out_dtype, int timeout_ms, cudaStream_t stream) {
+    using namespace xch;
+    if (world < 1 || world > MAX_WORLD || rank < 0 || rank >= world || rows < 0 || d_v <= 0 || timeout_ms <= 0) return FDMLA_ERR_INVALID;
+    if (rows == 0) return FDMLA_OK;
+    if (!msg || !bufs || !O || !m || !l) return FDMLA_ERR_INVALID;
+    if (d_v & 3) return FDMLA_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(msg) | reinterpret_cast<uintptr_t>(O)) & 15) return FDMLA_ERR_UNSUPPORTED;
+    Args a{};
+    a.msg = static_cast<const float *>(msg);
+    for (int p = 0; p < world; ++p) {
+        if (!bufs[p] || (reinterpret_cast<uintptr_t>(bufs[p]) & 15)) return FDMLA_ERR_INVALID;
+        a.bufs[p] = static_cast<float *>(bufs[p]);
+    }
+    a.world = world; a.rank = rank; a.rows = rows; a.d_v = d_v;
+    a.stride = message_stride(rows, d_v);
+    a.O = O; a.m = m; a.l = l;
+    a.timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    if (out_dtype == FDMLA_F32) exchange_merge_kernel<float><<<GRID, THREADS, 0, stream>>>(a);
+    else if (out_dtype == FDMLA_BF16) exchange_merge_kernel<__nv_bfloat16><<<GRID, THREADS, 0, stream>>>(a);
+    else return FDMLA_ERR_INVALID;
+    return check_launch();
+}
+
+}  // namespace fdmla

@@ -38,6 +38,12 @@ SIGNATURES = {
     "fdmla_decode_paged_noalloc": (_i, [_vp] * 7 + [_i] * 8 + [_f, _i, _vp]),
     "fdmla_merge_lse": (_i, [_vp] * 6 + [_ll, _i, _i, _i, _vp]),
     "fdmla_merge_lse_strided": (_i, [_vp] * 6 + [_ll, _i, _i, _ll, _ll, _i, _vp]),
+    "fdmla_exchange_bytes": (_sz, [_i, _ll, _i]),
+    "fdmla_exchange_alloc": (_i, [_sz, _vp, _vp]),
+    "fdmla_exchange_open": (_i, [_vp, _vp]),
+    "fdmla_exchange_close": (_i, [_vp]),
+    "fdmla_exchange_free": (_i, [_vp]),
+    "fdmla_exchange_merge": (_i, [_vp, _vp, _i, _i, _ll, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "fdmla_gemm_batched": (_i, [_vp] * 4 + [_i] * 4 + [_ll, _ll, _i, _i, _ll, _ll, _i, _i, _i, _ll, _ll, _ll, _i, _vp]),
     "fdmla_gemm_grouped": (_i, [_vp] * 5 + [_i] * 4 + [_ll, _ll, _ll, _i, _i, _ll, _i, _vp]),
     "fdmla_rope_rows": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _f, _vp]),

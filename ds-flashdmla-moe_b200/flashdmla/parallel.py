@@ -156,17 +156,27 @@ class SequenceParallelDecoder:
     B, H, d_qk, d_v, page_size: the problem; max_local_tokens: the longest slice any sequence has on this rank
     (fixes the split count).  The tensors handed to `step` may change from call to call; a captured graph replays on
     the tensors it was captured with (update them in place).
+
+    exchange="nccl": all-gather of the messages with NCCL, then the merge kernel.  exchange="peer" (ranks of one
+    node): `flashdmla.exchange.PeerExchange` - one kernel per rank stores the message into every peer's buffer over
+    NVLink, waits for the peers' and merges; same result bit for bit, one launch instead of a collective and a merge.
     """
 
     def __init__(self, B: int, H: int, d_qk: int, d_v: int, page_size: int, max_local_tokens: int, device,
                  dtype=torch.bfloat16, scale: Optional[float] = None, group: Optional[dist.ProcessGroup] = None,
-                 num_splits: Optional[int] = None):
+                 num_splits: Optional[int] = None, exchange: str = "nccl"):
         from . import ops
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        self.xch = None
+        if exchange == "peer":
+            from .exchange import PeerExchange
+            self.xch = PeerExchange(B * H, d_v, device, group)
         self.B, self.H, self.d_v, self.scale, self.group = B, H, d_v, scale, group
         self.world = dist.get_world_size(group)
         n = B * H * (d_v + 2)
         self.msg = torch.empty(n, dtype=torch.float32, device=device)
-        self.flat = torch.empty(self.world * n, dtype=torch.float32, device=device)
+        self.flat = None if self.xch is not None else torch.empty(self.world * n, dtype=torch.float32, device=device)
         self.out = (torch.empty(B, H, d_v, dtype=dtype, device=device), torch.empty(B, H, dtype=torch.float32, device=device),
                     torch.empty(B, H, dtype=torch.float32, device=device))
         self.splits = int(num_splits) if num_splits else (ops.suggest_partial_slabs(B, H, max(int(max_local_tokens), 1), page_size)
@@ -183,6 +193,8 @@ class SequenceParallelDecoder:
         mO, mm, ml = message_views(self.msg, (self.B, self.H), self.d_v)
         ops.flash_dmla_paged_decode_partial(Q, local_pool, local_page_table, local_seqlens, self.d_v, self.scale,
                                             num_splits=self.splits, out=(mO, mm, ml), scratch=self.part)
+        if self.xch is not None:
+            return self.xch.merge(self.msg, self.out)
         dist.all_gather_into_tensor(self.flat, self.msg, group=self.group)
         O_p, m_p, l_p = message_views(self.flat.view(self.world, -1), (self.B, self.H), self.d_v)
         ops.merge_partials(O_p, m_p, l_p, self.out[0].dtype, out=self.out)

@@ -70,8 +70,8 @@ int fdmla_set_single_cta(int on);
 const char *fdmla_last_kernel(void);
 
 /* Device-side error flag of the tensor-core kernels on the current device:
- * 0 = none; 1..3, 11..17 and 21..23 = a bounded wait inside a kernel gave up (which
- * kernel, role and wait); 4 = a page id outside [0, num_pages) was read from a page
+ * 0 = none; 1..3, 11..17, 21..23 and 31 = a bounded wait inside a kernel gave up (which
+ * kernel, role and wait; 31: a peer of fdmla_exchange_merge did not arrive); 4 = a page id outside [0, num_pages) was read from a page
  * table, or a sequence length outside [0, max_pages * page_size] was clamped.
  * Synchronises the device; reset != 0 clears the flag.  Returns -1 if the flag
  * cannot be read.
@@ -243,6 +243,38 @@ int fdmla_merge_lse_strided(const float *O_part, const float *m_part,
                             long long rows, int d_v, int num_parts,
                             long long part_stride_o, long long part_stride_ml,
                             int out_dtype, void *stream);
+
+/*
+ * Exchange and merge of the ranks' partial results in one kernel over peer memory (NVLink), for the GPUs of one
+ * node, one process per GPU: the fused form of "all-gather the messages, then fdmla_merge_lse_strided".
+ * It replaces the same exchange step as the all-gather does (the host MPI_Allgatherv of
+ * csrc/attention/fa2_fwd_mpi.cu:65-74) with the merge rule of fa2_fwd.cu:93-111; the reference has no device-side
+ * exchange.
+ *
+ * Set-up, once per (world, rows, d_v): every rank allocates an exchange buffer of fdmla_exchange_bytes with
+ * fdmla_exchange_alloc (device memory, zeroed; ipc_handle receives 64 bytes that name it to other processes),
+ * hands the handle to its peers by any host channel, maps every peer's buffer with fdmla_exchange_open, and
+ * synchronises with its peers on the host once before the first step.  fdmla_exchange_close unmaps a peer's
+ * buffer, fdmla_exchange_free releases the rank's own.
+ *
+ * A step, on every rank: msg is the rank's message [ O (rows x d_v) | m (rows) | l (rows) ] fp32 (what
+ * fdmla_decode_paged_partial writes); bufs[p], p < world, is rank p's buffer as mapped in this process
+ * (bufs[rank] the rank's own; a host array).  The kernel stores the message into every peer's buffer, signals,
+ * waits for every peer's signal and writes the merged O [rows, d_v] (out_dtype), m, l [rows]; the result is
+ * bit-identical to the all-gather followed by fdmla_merge_lse_strided.  All ranks must issue the same sequence
+ * of steps on one set of buffers, each rank from one stream (a step may be captured into a CUDA graph: the step
+ * counter lives in the buffer).  A peer that does not arrive within timeout_ms leaves O, m, l of the affected
+ * rows unwritten and sets fdmla_device_error_flag code 31; the buffers must then be set up again.
+ * world <= 16, d_v a multiple of 4.
+ */
+size_t fdmla_exchange_bytes(int world, long long rows, int d_v);
+int fdmla_exchange_alloc(size_t bytes, void **buf, void *ipc_handle);
+int fdmla_exchange_open(const void *ipc_handle, void **peer_buf);
+int fdmla_exchange_close(void *peer_buf);
+int fdmla_exchange_free(void *buf);
+int fdmla_exchange_merge(const float *msg, void *const *bufs, int world, int rank,
+                         long long rows, int d_v, void *O, float *m, float *l,
+                         int out_dtype, int timeout_ms, void *stream);
 
 /*
  * Batched bf16 GEMM on the tensor cores, fp32 accumulation: C[b] (M x N) = A[b] (M x K) * B[b] for b < batch.

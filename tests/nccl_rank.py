@@ -51,6 +51,7 @@ def sequence_parallel_case(dev, world, rank):
     assert_stats(m, l, mf, lf)
     # the same step with every buffer allocated once, eagerly and replayed from a CUDA graph (three split counts:
     # the attention kernel writing the message itself, and split-KV partials merged into it)
+    import flashdmla
     from flashdmla.parallel import SequenceParallelDecoder
     Qd, pd, td, ld = Q.to(dev), pool.to(dev), ltable.to(dev), llens.to(dev)
     for splits in (1, 3, None):
@@ -64,6 +65,26 @@ def sequence_parallel_case(dev, world, rank):
         O3, m3, l3 = dec.replay()
         torch.cuda.synchronize()
         assert torch.equal(O3, O2) and torch.equal(m3, m2) and torch.equal(l3, l2)
+        # the exchange and the merge as ONE kernel over peer memory: bit-identical to all-gather + merge, on several
+        # steps in a row (both slots of the exchange buffers, the step counters) and replayed from a CUDA graph
+        peer = SequenceParallelDecoder(len(lens), H, 576, 512, ps, int(llens.max()), dev, scale=sc, num_splits=splits,
+                                       exchange="peer")
+        for _ in range(3):
+            for t in peer.out:
+                t.zero_()
+            O4, m4, l4 = peer.step(Qd, pd, td, ld)
+            torch.cuda.synchronize()
+            assert torch.equal(O4, O2) and torch.equal(m4, m2) and torch.equal(l4, l2)
+        assert flashdmla.last_kernel() == "exchange_merge_kernel"
+        peer.capture(Qd, pd, td, ld)
+        for _ in range(3):
+            for t in peer.out:
+                t.zero_()
+            O5, m5, l5 = peer.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(O5, O2) and torch.equal(m5, m2) and torch.equal(l5, l2)
+        assert flashdmla.device_error_flag() == 0
+        peer.xch.close()
 
 
 def expert_parallel_case(dev, world, rank):
