@@ -10,14 +10,15 @@
 // Every rank owns an exchange buffer that its peers have mapped (CUDA IPC):
 //     [ slot 0: world messages | slot 1: world messages | flags: world x GRID words | step counters: GRID words ]
 // One launch of exchange_merge_kernel on every rank does the step.  The grid is GRID thread blocks on every rank (all
-// resident at once: 128 threads, no shared memory to speak of); block c owns the same run of rows everywhere.
+// resident at once: 512 threads, no shared memory to speak of); block c owns the same run of rows everywhere.
 //   1. it copies its rows of this rank's message into message [rank] of the current slot of every peer's buffer
 //      (plain 16-byte stores to peer memory), fences at system scope, and writes the step number into
 //      flags[rank][c] of every peer (st.release.sys);
 //   2. it waits until flags[p][c] of its own buffer has reached the step number for every peer p (ld.acquire.sys;
 //      bounded by a time limit on the global timer - a peer that never arrives sets error code 31 and the block
 //      returns without writing a result);
-//   3. it merges its rows: this rank's part straight from the message, the peers' parts from its own buffer.
+//   3. it merges its rows, a warp per row: this rank's part straight from the message, the peers' parts from its own
+//      buffer.
 // A block never waits for another block of its own GPU, so nothing depends on the order in which blocks are scheduled.
 // The step number is a counter kept per block in the rank's own buffer (a CUDA graph replays the launch unchanged);
 // the slot alternates with it: a peer can only be one step ahead (it needs this rank's flags of step s to finish
@@ -32,7 +33,7 @@
 namespace fdmla {
 namespace xch {
 
-constexpr int GRID = 128, THREADS = 128, MAX_WORLD = 16;
+constexpr int GRID = 128, THREADS = 512, MAX_WORLD = 16;
 enum { ERR_EXCHANGE_TIMEOUT = 31 };
 
 __device__ int g_xch_error = 0;
@@ -67,9 +68,17 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-template <typename TO> __device__ __forceinline__ TO out_from_f32(float x);
-template <> __device__ __forceinline__ float out_from_f32<float>(float x) { return x; }
-template <> __device__ __forceinline__ __nv_bfloat16 out_from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+// four consecutive output elements, the first on a 16-byte (fp32) / 8-byte (bf16) boundary
+__device__ __forceinline__ void store4(float *dst, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16 *dst, const float (&v)[4]) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t *>(&lo);
+    w.y = *reinterpret_cast<const uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(dst) = w;
+}
 
 template <typename TO>
 __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
@@ -136,36 +145,58 @@ __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
     __syncthreads();
     if (s_bad) return;
 
-    // ---- 3. merge (the arithmetic of the merge kernel of the split-KV decode, part by part in rank order) ----
+    // ---- 3. merge: a warp per row; the arithmetic of the merge kernel of the split-KV decode, part by part in rank
+    // order (every lane runs the same sums, so the result does not depend on the number of lanes) --------------------
     TO *O = static_cast<TO *>(a.O);
-    for (long long r = r0; r < r1; ++r) {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (long long r = r0 + warp; r < r1; r += THREADS / 32) {
+        // lane q holds m and l of part q
+        float m_q = -CUDART_INF_F, l_q = 0.f;
+        if (lane < W) {
+            const float *part = lane == a.rank ? a.msg : own + slot_off + (size_t)lane * a.stride;
+            l_q = __ldcg(part + o_l + r);
+            m_q = __ldcg(part + o_m + r);
+        }
         float mx = -CUDART_INF_F;
         for (int q = 0; q < W; ++q) {
-            const float *part = q == a.rank ? a.msg : own + slot_off + (size_t)q * a.stride;
-            if (__ldcg(part + o_l + r) > 0.f) mx = fmaxf(mx, __ldcg(part + o_m + r));
+            const float lp = __shfl_sync(0xffffffffu, l_q, q), mp = __shfl_sync(0xffffffffu, m_q, q);
+            if (lp > 0.f) mx = fmaxf(mx, mp);
         }
         float ls = 0.f;
         for (int q = 0; q < W; ++q) {
-            const float *part = q == a.rank ? a.msg : own + slot_off + (size_t)q * a.stride;
-            const float lp = __ldcg(part + o_l + r);
-            if (lp > 0.f) ls += lp * __expf(__ldcg(part + o_m + r) - mx);
+            const float lp = __shfl_sync(0xffffffffu, l_q, q), mp = __shfl_sync(0xffffffffu, m_q, q);
+            if (lp > 0.f) ls += lp * __expf(mp - mx);
         }
         const float inv = ls > 0.f ? 1.f / ls : 0.f;
-        for (int col = tid * 4; col < a.d_v; col += 4 * THREADS) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c0 = 0; c0 < a.d_v; c0 += 512) {               // 4 x (32 lanes x 4 columns) per pass
+            float acc[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
             for (int q = 0; q < W; ++q) {
-                const float *part = q == a.rank ? a.msg : own + slot_off + (size_t)q * a.stride;
-                const float lp = __ldcg(part + o_l + r);
+                const float lp = __shfl_sync(0xffffffffu, l_q, q), mp = __shfl_sync(0xffffffffu, m_q, q);
                 if (lp > 0.f) {
-                    const float w = lp * __expf(__ldcg(part + o_m + r) - mx) * inv;
-                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(part + (size_t)r * a.d_v + col));
-                    acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
-                    acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+                    const float w = lp * __expf(mp - mx) * inv;
+                    const float *src = (q == a.rank ? a.msg : own + slot_off + (size_t)q * a.stride) + (size_t)r * a.d_v;
+                    float4 v[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int col = c0 + (i * 32 + lane) * 4;
+                        v[i] = col < a.d_v ? __ldcg(reinterpret_cast<const float4 *>(src + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc[i][0] = fmaf(w, v[i].x, acc[i][0]); acc[i][1] = fmaf(w, v[i].y, acc[i][1]);
+                        acc[i][2] = fmaf(w, v[i].z, acc[i][2]); acc[i][3] = fmaf(w, v[i].w, acc[i][3]);
+                    }
                 }
             }
-            for (int e = 0; e < 4; ++e) O[(size_t)r * a.d_v + col + e] = out_from_f32<TO>(acc[e]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int col = c0 + (i * 32 + lane) * 4;
+                if (col < a.d_v) store4(O + (size_t)r * a.d_v + col, acc[i]);
+            }
         }
-        if (tid == 0) { a.m[r] = mx; a.l[r] = ls; }
+        if (lane == 0) { a.m[r] = mx; a.l[r] = ls; }
     }
 }
 
