@@ -7,23 +7,29 @@
 // on every rank; the merge rule is the running update of csrc/attention/fa2_fwd.cu:93-111 applied across partials:
 //     m = max_p m_p,   w_p = l_p exp(m_p - m),   l = sum_p w_p,   O = sum_p (w_p / l) O_p.
 //
-// Every rank owns an exchange buffer that its peers have mapped (CUDA IPC):
-//     [ slot 0: world messages | slot 1: world messages | flags: world x GRID words | step counters: GRID words ]
+// Every rank owns an exchange buffer that its peers have mapped (CUDA IPC).  Per slot (two slots, used in turn):
+//     [ world messages: the peers' partial rows for the row blocks this rank merges | one result area ]
+// and behind the slots   [ data flags: world x GRID words | result flags: GRID words | step counters: GRID words ].
 // One launch of exchange_merge_kernel on every rank does the step.  The grid is GRID thread blocks on every rank (all
-// resident at once: 512 threads, no shared memory to speak of); block c owns the same run of rows everywhere.
-//   1. it copies its rows of this rank's message into message [rank] of the current slot of every peer's buffer
-//      (plain 16-byte stores to peer memory), fences at system scope, and writes the step number into
-//      flags[rank][c] of every peer (st.release.sys);
-//   2. it waits until flags[p][c] of its own buffer has reached the step number for every peer p (ld.acquire.sys;
-//      bounded by a time limit on the global timer - a peer that never arrives sets error code 31 and the block
-//      returns without writing a result);
-//   3. it merges its rows, a warp per row: this rank's part straight from the message, the peers' parts from its own
-//      buffer.
-// A block never waits for another block of its own GPU, so nothing depends on the order in which blocks are scheduled.
-// The step number is a counter kept per block in the rank's own buffer (a CUDA graph replays the launch unchanged);
-// the slot alternates with it: a peer can only be one step ahead (it needs this rank's flags of step s to finish
-// step s), so it writes slot (s + 1) & 1 while this rank may still read slot s & 1.  All ranks must launch the same
-// sequence of steps on one exchange, each rank from one stream, as with a collective.
+// resident at once: 512 threads, no shared memory to speak of); block c stands for the same run of rows everywhere, and
+// rank c mod world is the OWNER of that run: the partials travel to the owner only and the merged rows travel back, so
+// a rank sends (world - 1) / world of its message plus its share of the results instead of world - 1 whole messages.
+//   not the owner:  the block stores its rows of this rank's message into message [rank] of the owner's current slot
+//                   (plain 16-byte stores to peer memory), fences at system scope and writes the step number into
+//                   data flag [rank][c] of the owner (st.release.sys); then it waits for result flag [c] of its own
+//                   buffer (ld.acquire.sys) and copies the merged rows from its own result area to O, m, l;
+//   the owner:      the block waits until data flag [p][c] of its own buffer has reached the step number for every
+//                   peer p, merges its rows (a warp per row: this rank's part straight from the message, the peers'
+//                   parts from its own buffer, part by part in rank order), writes them to its own O, m, l and into
+//                   the result area of every peer, fences, and writes the step number into result flag [c] of every peer.
+// Every wait is bounded by a time limit on the global timer: a peer that never arrives sets error code 31 and the block
+// returns without writing a result.  A block never waits for another block of its own GPU, and the owner of a run
+// waits only for stores that its peers issue before they wait themselves, so nothing depends on the order in which
+// blocks are scheduled.  The step number is a counter kept per block in the rank's own buffer (a CUDA graph replays
+// the launch unchanged); the slot alternates with it: for a run of rows, a rank can be at most one step ahead of a peer
+// (each needs the other's flag of step s to finish step s), so it writes slot (s + 1) & 1 while the peer may still read
+// slot s & 1.  All ranks must launch the same sequence of steps on one exchange, each rank from one stream, as with a
+// collective.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
@@ -53,7 +59,8 @@ struct Args {
 __host__ __device__ inline size_t message_stride(long long rows, int d_v) {
     return ((size_t)rows * (size_t)(d_v + 2) + 3) & ~(size_t)3;
 }
-__host__ __device__ inline size_t flags_offset_floats(int world, size_t stride) { return 2 * (size_t)world * stride; }
+__host__ __device__ inline size_t slot_floats(int world, size_t stride) { return ((size_t)world + 1) * stride; }
+__host__ __device__ inline size_t flags_offset_floats(int world, size_t stride) { return 2 * slot_floats(world, stride); }
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -80,12 +87,24 @@ __device__ __forceinline__ void store4(__nv_bfloat16 *dst, const float (&v)[4]) 
     *reinterpret_cast<uint2 *>(dst) = w;
 }
 
+// bounded wait of one thread until *flag has reached `step`
+__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t step, unsigned long long timeout_ns) {
+    const unsigned long long t0 = global_timer_ns();
+    while ((int)(ld_acquire_sys(flag) - step) < 0) {
+        if (global_timer_ns() - t0 > timeout_ns) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
     const int c = blockIdx.x, tid = threadIdx.x, W = a.world;
     float *own = a.bufs[a.rank];
-    uint32_t *flags_own = reinterpret_cast<uint32_t *>(own + flags_offset_floats(W, a.stride));     // [world][GRID]
-    uint32_t *steps = flags_own + (size_t)W * GRID;                                                 // [GRID]
+    const size_t flags_off = flags_offset_floats(W, a.stride);
+    uint32_t *data_flags = reinterpret_cast<uint32_t *>(own + flags_off);       // [world][GRID]
+    uint32_t *res_flags = data_flags + (size_t)W * GRID;                        // [GRID]
+    uint32_t *steps = res_flags + GRID;                                         // [GRID]
     __shared__ uint32_t s_step;
     __shared__ int s_bad;
     if (tid == 0) {
@@ -95,59 +114,62 @@ __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
     }
     __syncthreads();
     const uint32_t step = s_step;
-    const size_t slot_off = (size_t)(step & 1) * W * a.stride;
+    const size_t slot_off = (size_t)(step & 1) * slot_floats(W, a.stride);
+    const size_t res_off = slot_off + (size_t)W * a.stride;                      // the slot's result area
     const long long per = (a.rows + GRID - 1) / GRID;
     const long long r0 = (long long)c * per;
     const long long r1 = r0 + per < a.rows ? r0 + per : a.rows;
     const long long nr = r1 > r0 ? r1 - r0 : 0;
-    const size_t o_m = (size_t)a.rows * a.d_v, o_l = o_m + (size_t)a.rows;       // offsets of m and l in a message
+    const size_t o_m = (size_t)a.rows * a.d_v, o_l = o_m + (size_t)a.rows;       // offsets of m and l in a message / result area
+    const int owner = c % W;
+    TO *O = static_cast<TO *>(a.O);
 
-    // ---- 1. this block's rows of this rank's message into every peer's buffer ----------------------------
-    {
+    if (owner != a.rank) {
+        // ---- this block's rows of this rank's message to their owner -----------------------------------------
+        float *dst = a.bufs[owner] + slot_off + (size_t)a.rank * a.stride;
         const float4 *src = reinterpret_cast<const float4 *>(a.msg + (size_t)r0 * a.d_v);
+        float4 *dst4 = reinterpret_cast<float4 *>(dst + (size_t)r0 * a.d_v);
         const long long n4 = nr * a.d_v / 4;
-        for (long long i = tid; i < n4; i += THREADS) {
-            const float4 v = src[i];
-            for (int p = 0; p < W; ++p)
-                if (p != a.rank)
-                    reinterpret_cast<float4 *>(a.bufs[p] + slot_off + (size_t)a.rank * a.stride + (size_t)r0 * a.d_v)[i] = v;
-        }
+        for (long long i = tid; i < n4; i += THREADS) dst4[i] = src[i];
         for (long long i = tid; i < nr; i += THREADS) {
-            const float mv = a.msg[o_m + r0 + i], lv = a.msg[o_l + r0 + i];
-            for (int p = 0; p < W; ++p)
-                if (p != a.rank) {
-                    float *dst = a.bufs[p] + slot_off + (size_t)a.rank * a.stride;
-                    dst[o_m + r0 + i] = mv;
-                    dst[o_l + r0 + i] = lv;
-                }
+            dst[o_m + r0 + i] = a.msg[o_m + r0 + i];
+            dst[o_l + r0 + i] = a.msg[o_l + r0 + i];
         }
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < W && tid != a.rank) {
-        uint32_t *peer_flags = reinterpret_cast<uint32_t *>(a.bufs[tid] + flags_offset_floats(W, a.stride));
-        st_release_sys(peer_flags + (size_t)a.rank * GRID + c, step);
-    }
-
-    // ---- 2. until every peer's rows of this block have landed here -----------------------------------------
-    if (tid < W && tid != a.rank) {
-        const unsigned long long t0 = global_timer_ns();
-        const uint32_t *f = flags_own + (size_t)tid * GRID + c;
-        while ((int)(ld_acquire_sys(f) - step) < 0) {
-            if (global_timer_ns() - t0 > a.timeout_ns) {
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t *owner_flags = reinterpret_cast<uint32_t *>(a.bufs[owner] + flags_off);
+            st_release_sys(owner_flags + (size_t)a.rank * GRID + c, step);
+            // ---- until the owner has stored the merged rows here ----------------------------------------------
+            if (!wait_flag(res_flags + c, step, a.timeout_ns)) {
                 atomicCAS(&g_xch_error, 0, ERR_EXCHANGE_TIMEOUT);
                 s_bad = 1;
-                break;
             }
-            __nanosleep(64);
         }
+        __syncthreads();
+        if (s_bad) return;
+        const float *res = own + res_off;
+        const uint2 *rs = reinterpret_cast<const uint2 *>(reinterpret_cast<const TO *>(res) + (size_t)r0 * a.d_v);
+        uint2 *od = reinterpret_cast<uint2 *>(O + (size_t)r0 * a.d_v);
+        const long long n8 = nr * a.d_v * (long long)sizeof(TO) / 8;
+        for (long long i = tid; i < n8; i += THREADS) od[i] = __ldcg(rs + i);
+        for (long long i = tid; i < nr; i += THREADS) {
+            a.m[r0 + i] = __ldcg(res + o_m + r0 + i);
+            a.l[r0 + i] = __ldcg(res + o_l + r0 + i);
+        }
+        return;
+    }
+
+    // ---- the owner: until every peer's rows of this block have landed here ----------------------------------------
+    if (tid < W && tid != a.rank && !wait_flag(data_flags + (size_t)tid * GRID + c, step, a.timeout_ns)) {
+        atomicCAS(&g_xch_error, 0, ERR_EXCHANGE_TIMEOUT);
+        s_bad = 1;
     }
     __syncthreads();
     if (s_bad) return;
 
-    // ---- 3. merge: a warp per row; the arithmetic of the merge kernel of the split-KV decode, part by part in rank
-    // order (every lane runs the same sums, so the result does not depend on the number of lanes) --------------------
-    TO *O = static_cast<TO *>(a.O);
+    // ---- merge: a warp per row; the arithmetic of the merge kernel of the split-KV decode, part by part in rank order
+    // (every lane runs the same sums, so the result does not depend on the number of lanes) ---------------------------
     const int warp = tid >> 5, lane = tid & 31;
     for (long long r = r0 + warp; r < r1; r += THREADS / 32) {
         // lane q holds m and l of part q
@@ -193,10 +215,28 @@ __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int col = c0 + (i * 32 + lane) * 4;
-                if (col < a.d_v) store4(O + (size_t)r * a.d_v + col, acc[i]);
+                if (col < a.d_v) {
+                    store4(O + (size_t)r * a.d_v + col, acc[i]);
+                    for (int p = 0; p < W; ++p)
+                        if (p != a.rank) store4(reinterpret_cast<TO *>(a.bufs[p] + res_off) + (size_t)r * a.d_v + col, acc[i]);
+                }
             }
         }
-        if (lane == 0) { a.m[r] = mx; a.l[r] = ls; }
+        if (lane == 0) {
+            a.m[r] = mx;
+            a.l[r] = ls;
+            for (int p = 0; p < W; ++p)
+                if (p != a.rank) {
+                    a.bufs[p][res_off + o_m + r] = mx;
+                    a.bufs[p][res_off + o_l + r] = ls;
+                }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < W && tid != a.rank) {
+        uint32_t *peer_res_flags = reinterpret_cast<uint32_t *>(a.bufs[tid] + flags_off) + (size_t)W * GRID;
+        st_release_sys(peer_res_flags + c, step);
     }
 }
 
@@ -216,7 +256,7 @@ int exchange_error_flag(int reset) {
 size_t exchange_bytes(int world, long long rows, int d_v) {
     if (world < 1 || world > xch::MAX_WORLD || rows <= 0 || d_v <= 0 || (d_v & 3)) return 0;
     const size_t stride = xch::message_stride(rows, d_v);
-    return (xch::flags_offset_floats(world, stride) + (size_t)world * xch::GRID + xch::GRID) * sizeof(float);
+    return (xch::flags_offset_floats(world, stride) + (size_t)world * xch::GRID + 2 * xch::GRID) * sizeof(float);
 }
 
 int launch_exchange_merge(const void *msg, void *const *bufs, int world, int rank, long long rows, int d_v, void *O,

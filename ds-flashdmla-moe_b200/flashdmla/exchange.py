@@ -1,9 +1,10 @@
 """Exchange and merge of the ranks' partial decode results in one kernel over NVLink peer memory.
 
 `PeerExchange` is the host side of `fdmla_exchange_merge` (include/flashdmla.h): every rank of a node owns an
-exchange buffer in device memory that its peers have mapped through CUDA IPC; one kernel launch per rank stores the
-rank's message [O | m | l] into every peer's buffer, signals, waits for the peers' signals and merges - the fused
-form of `all_gather_into_tensor` + `merge_partials`, with bit-identical results.  It stands where the reference's
+exchange buffer in device memory that its peers have mapped through CUDA IPC; one kernel launch per rank sends the
+rows of the rank's message [O | m | l] to the ranks that own them, merges the rows it owns once its peers' have landed
+and stores the merged rows into every peer's buffer - the fused form of `all_gather_into_tensor` + `merge_partials`,
+with bit-identical results and a fraction of the NVLink traffic.  It stands where the reference's
 MPI wrapper gathers on the host (csrc/attention/fa2_fwd_mpi.cu:65-74).  CUDA only; one process per GPU, all on one
 node.
 """

@@ -158,8 +158,9 @@ class SequenceParallelDecoder:
     the tensors it was captured with (update them in place).
 
     exchange="nccl": all-gather of the messages with NCCL, then the merge kernel.  exchange="peer" (ranks of one
-    node): `flashdmla.exchange.PeerExchange` - one kernel per rank stores the message into every peer's buffer over
-    NVLink, waits for the peers' and merges; same result bit for bit, one launch instead of a collective and a merge.
+    node): `flashdmla.exchange.PeerExchange` - one kernel per rank sends its partial rows over NVLink to the ranks that
+    own them, merges the rows it owns and hands the merged rows to every peer; same result bit for bit, one launch
+    instead of a collective and a merge.
     """
 
     def __init__(self, B: int, H: int, d_qk: int, d_v: int, page_size: int, max_local_tokens: int, device,
