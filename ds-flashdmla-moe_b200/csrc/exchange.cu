@@ -34,6 +34,8 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace fdmla {
@@ -97,7 +99,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t step, u
     return true;
 }
 
-template <typename TO>
+template <typename TO, bool GATHER>
 __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
     const int c = blockIdx.x, tid = threadIdx.x, W = a.world;
     float *own = a.bufs[a.rank];
@@ -121,10 +123,32 @@ __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
     const long long r1 = r0 + per < a.rows ? r0 + per : a.rows;
     const long long nr = r1 > r0 ? r1 - r0 : 0;
     const size_t o_m = (size_t)a.rows * a.d_v, o_l = o_m + (size_t)a.rows;       // offsets of m and l in a message / result area
-    const int owner = c % W;
+    const int owner = GATHER ? a.rank : c % W;        // all-gather form: every rank merges every run itself
     TO *O = static_cast<TO *>(a.O);
 
-    if (owner != a.rank) {
+    if (GATHER) {
+        // ---- this block's rows of this rank's message into every peer's buffer -------------------------------
+        const float4 *src = reinterpret_cast<const float4 *>(a.msg + (size_t)r0 * a.d_v);
+        const size_t dst_off = slot_off + (size_t)a.rank * a.stride;
+        const long long n4 = nr * a.d_v / 4;
+        for (long long i = tid; i < n4; i += THREADS) {
+            const float4 v = src[i];
+            for (int p = 0; p < W; ++p)
+                if (p != a.rank) reinterpret_cast<float4 *>(a.bufs[p] + dst_off + (size_t)r0 * a.d_v)[i] = v;
+        }
+        for (long long i = tid; i < nr; i += THREADS) {
+            const float mv = a.msg[o_m + r0 + i], lv = a.msg[o_l + r0 + i];
+            for (int p = 0; p < W; ++p)
+                if (p != a.rank) {
+                    a.bufs[p][dst_off + o_m + r0 + i] = mv;
+                    a.bufs[p][dst_off + o_l + r0 + i] = lv;
+                }
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid < W && tid != a.rank)
+            st_release_sys(reinterpret_cast<uint32_t *>(a.bufs[tid] + flags_off) + (size_t)a.rank * GRID + c, step);
+    } else if (owner != a.rank) {
         // ---- this block's rows of this rank's message to their owner -----------------------------------------
         float *dst = a.bufs[owner] + slot_off + (size_t)a.rank * a.stride;
         const float4 *src = reinterpret_cast<const float4 *>(a.msg + (size_t)r0 * a.d_v);
@@ -217,21 +241,23 @@ __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
                 const int col = c0 + (i * 32 + lane) * 4;
                 if (col < a.d_v) {
                     store4(O + (size_t)r * a.d_v + col, acc[i]);
-                    for (int p = 0; p < W; ++p)
-                        if (p != a.rank) store4(reinterpret_cast<TO *>(a.bufs[p] + res_off) + (size_t)r * a.d_v + col, acc[i]);
+                    if (!GATHER)
+                        for (int p = 0; p < W; ++p)
+                            if (p != a.rank) store4(reinterpret_cast<TO *>(a.bufs[p] + res_off) + (size_t)r * a.d_v + col, acc[i]);
                 }
             }
         }
         if (lane == 0) {
             a.m[r] = mx;
             a.l[r] = ls;
-            for (int p = 0; p < W; ++p)
+            for (int p = 0; !GATHER && p < W; ++p)
                 if (p != a.rank) {
                     a.bufs[p][res_off + o_m + r] = mx;
                     a.bufs[p][res_off + o_l + r] = ls;
                 }
         }
     }
+    if (GATHER) return;
     __threadfence_system();
     __syncthreads();
     if (tid < W && tid != a.rank) {
@@ -277,9 +303,19 @@ int launch_exchange_merge(const void *msg, void *const *bufs, int world, int ran
     a.stride = message_stride(rows, d_v);
     a.O = O; a.m = m; a.l = l;
     a.timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
-    if (out_dtype == FDMLA_F32) exchange_merge_kernel<float><<<GRID, THREADS, 0, stream>>>(a);
-    else if (out_dtype == FDMLA_BF16) exchange_merge_kernel<__nv_bfloat16><<<GRID, THREADS, 0, stream>>>(a);
-    else return FDMLA_ERR_INVALID;
+    // two ranks: every rank sends its whole message to the other and merges everything itself (one hop); more: the
+    // rows go to their owners and the merged rows come back (two hops, 1 / world of the traffic)
+    static const int forced = [] { const char *e = getenv("FDMLA_EXCHANGE_GATHER"); return e && *e ? atoi(e) : -1; }();
+    const bool gather = forced >= 0 ? forced != 0 : world <= 2;
+    if (out_dtype == FDMLA_F32) {
+        if (gather) exchange_merge_kernel<float, true><<<GRID, THREADS, 0, stream>>>(a);
+        else exchange_merge_kernel<float, false><<<GRID, THREADS, 0, stream>>>(a);
+    } else if (out_dtype == FDMLA_BF16) {
+        if (gather) exchange_merge_kernel<__nv_bfloat16, true><<<GRID, THREADS, 0, stream>>>(a);
+        else exchange_merge_kernel<__nv_bfloat16, false><<<GRID, THREADS, 0, stream>>>(a);
+    } else {
+        return FDMLA_ERR_INVALID;
+    }
     return check_launch();
 }
 

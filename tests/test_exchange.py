@@ -2,8 +2,8 @@
 
 The peers of a real exchange are other GPUs (tests/test_multi_gpu.py runs that on two).  Here rank 0 of a world of two
 runs alone: its "peer's" buffer is a second local buffer, and what the peer would have stored into rank 0's buffer -
-its partial rows and data flags for the row blocks rank 0 owns (the even ones), the merged rows and result flags for
-the blocks the peer owns - is written by the host before the launch, so the kernel never waits for another kernel.
+its partial rows and data flags, and in the owner form the merged rows and result flags of the row blocks the peer
+owns - is written by the host before the launch, so the kernel never waits for another kernel.
 The time-limit case leaves the flags unset: the wait runs out, the kernel returns, the error flag reads 31.
 """
 import ctypes
@@ -43,7 +43,7 @@ def test_exchange_argument_validation_needs_no_gpu():
     assert L.fdmla_exchange_bytes(0, 8, 512) == 0 and L.fdmla_exchange_bytes(17, 8, 512) == 0
     assert L.fdmla_exchange_bytes(2, 8, 510) == 0
     n = 8 * 514
-    assert L.fdmla_exchange_bytes(2, 8, 512) == (2 * 3 * n + 2 * GRID + 2 * GRID) * 4      # 2 slots x (2 messages + results), flags
+    assert L.fdmla_exchange_bytes(2, 8, 512) == (2 * 3 * n + 2 * GRID + 2 * GRID) * 4      # 2 slots x (2 messages + results), flags, counters
     assert L.fdmla_exchange_merge(None, None, 2, 0, 0, 512, None, None, None, 0, 100, None) == 0      # no rows: no-op
     assert L.fdmla_exchange_merge(None, None, 2, 0, 8, 512, None, None, None, 0, 100, None) == -1
     assert L.fdmla_exchange_merge(None, None, 2, 2, 8, 512, None, None, None, 0, 100, None) == -1     # rank outside the world
@@ -53,80 +53,93 @@ def test_exchange_argument_validation_needs_no_gpu():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("rows,d_v,out_dtype", [(1024, 512, torch.bfloat16), (130, 512, torch.float32), (7, 64, torch.float32)])
-def test_exchange_merge_against_merge_kernel(rows, d_v, out_dtype, cuda):
+def test_exchange_merge_against_merge_kernel(rows, d_v, out_dtype, world, cuda):
+    """world 2 runs the all-gather form (whole messages to every peer, every rank merges everything), world 3 the owner
+    form (rows to the rank that owns their block, merged rows back)."""
     import flashdmla
     from flashdmla import _lib
     from flashdmla.parallel import message_views
     L = _lib.lib()
+    W = world
+    gather = W <= 2
     n = rows * (d_v + 2)
     stride = (n + 3) // 4 * 4
-    nbytes = L.fdmla_exchange_bytes(2, rows, d_v)
+    nbytes = L.fdmla_exchange_bytes(W, rows, d_v)
     with torch.cuda.device(cuda):
-        own, own_t = _alloc(L, nbytes, cuda)
-        peer, peer_t = _alloc(L, nbytes, cuda)
-        assert float(own_t.abs().sum()) == 0.0                       # allocated zeroed
-        bufs = (ctypes.c_void_p * 2)(own.value, peer.value)
-        slot_floats, flags_off = 3 * stride, 2 * 3 * stride          # a slot: two messages and the result area
+        raw, t = zip(*[_alloc(L, nbytes, cuda) for _ in range(W)])       # t[0]: rank 0's own buffer; t[p]: "peer" p's
+        assert float(t[0].abs().sum()) == 0.0                            # allocated zeroed
+        bufs = (ctypes.c_void_p * W)(*[r.value for r in raw])
+        slot_floats, flags_off = (W + 1) * stride, 2 * (W + 1) * stride  # a slot: W messages and the result area
         code = _lib.F32 if out_dtype == torch.float32 else _lib.BF16
         per = (rows + GRID - 1) // GRID
-        block_of_row = torch.arange(rows) // per
-        mine = (block_of_row % 2 == 0).to(cuda)                      # rows whose block rank 0 owns
-        for step in (1, 2, 3):                                       # slots 1, 0, 1
-            msg0 = _message(rows, d_v, 10 * step, empty_rows=(0,)).to(cuda)
-            msg1 = _message(rows, d_v, 10 * step + 1, empty_rows=(0, rows - 1)).to(cuda)
-            O_p, m_p, l_p = message_views(torch.stack([msg0, msg1]), (rows,), d_v)
+        owner_of_row = ((torch.arange(rows) // per) % W).to(cuda)
+        owner_of_block = torch.arange(GRID, device=cuda) % W
+        mine = torch.ones(rows, dtype=torch.bool, device=cuda) if gather else owner_of_row == 0
+        for step in (1, 2, 3):                                           # slots 1, 0, 1
+            msgs = [_message(rows, d_v, 10 * step + q, empty_rows=(0,) if q == 0 else (0, rows - 1)).to(cuda) for q in range(W)]
+            O_p, m_p, l_p = message_views(torch.stack(msgs), (rows,), d_v)
             Ow, mw, lw = flashdmla.merge_partials(O_p, m_p, l_p, out_dtype)
             slot = (step & 1) * slot_floats
             stepw = torch.full((GRID,), step, dtype=torch.int32).view(torch.float32).to(cuda)
-            # what rank 1 would have stored here.  For the blocks rank 0 owns: its partial rows in message [1] of the
-            # slot and the step number in data flags [1][*] ...
-            own_t[slot + stride: slot + stride + n] = msg1
-            own_t[flags_off + GRID: flags_off + 2 * GRID] = stepw
-            # ... for the blocks rank 1 owns: the merged rows in the slot's result area and the step number in the
-            # result flags (only those rows: the others hold a marker that must not reach the output)
-            res = own_t[slot + 2 * stride: slot + 3 * stride]
+            # what the peers would have stored here.  Their partial rows in messages [1..] of the slot and the step
+            # number in data flags [p][*] (the owner form reads only the rows of the blocks rank 0 owns) ...
+            for q in range(1, W):
+                t[0][slot + q * stride: slot + q * stride + n] = msgs[q]
+                t[0][flags_off + q * GRID: flags_off + (q + 1) * GRID] = stepw
+            # ... and, owner form, for the blocks they own: the merged rows in the slot's result area and the step number
+            # in the result flags (only those rows: the others hold a marker that must not reach the output)
+            res = t[0][slot + W * stride: slot + (W + 1) * stride]
             res[:] = 12345.0
-            res_O = res.view(out_dtype)[: rows * d_v].view(rows, d_v)
-            res_O[~mine] = Ow[~mine]
-            res[rows * d_v: rows * d_v + rows][~mine] = mw[~mine]
-            res[rows * d_v + rows: rows * d_v + 2 * rows][~mine] = lw[~mine]
-            own_t[flags_off + 2 * GRID: flags_off + 3 * GRID] = stepw
-            peer_t[slot: slot + 3 * stride] = -777.0
+            if not gather:
+                res.view(out_dtype)[: rows * d_v].view(rows, d_v)[~mine] = Ow[~mine]
+                res[rows * d_v: rows * d_v + rows][~mine] = mw[~mine]
+                res[rows * d_v + rows: rows * d_v + 2 * rows][~mine] = lw[~mine]
+                t[0][flags_off + W * GRID: flags_off + (W + 1) * GRID] = stepw
+            for q in range(1, W):
+                t[q][slot: slot + (W + 1) * stride] = -777.0
             O = torch.full((rows, d_v), float("nan"), dtype=out_dtype, device=cuda)
             m = torch.full((rows,), float("nan"), device=cuda)
             l = torch.full((rows,), float("nan"), device=cuda)
             torch.cuda.synchronize()
-            rc = L.fdmla_exchange_merge(msg0.data_ptr(), bufs, 2, 0, rows, d_v, O.data_ptr(), m.data_ptr(), l.data_ptr(),
+            rc = L.fdmla_exchange_merge(msgs[0].data_ptr(), bufs, W, 0, rows, d_v, O.data_ptr(), m.data_ptr(), l.data_ptr(),
                                         code, 2000, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
             assert rc == 0
             torch.cuda.synchronize()
             assert flashdmla.last_kernel() == "exchange_merge_kernel"
             assert torch.equal(O, Ow) and torch.equal(m, mw) and torch.equal(l, lw)        # bit for bit
-            # and both against the merge rule written out in fp32 (an odd number of rows puts the second gathered
-            # message off the 16-byte grid: the merge kernel must not read it with vector loads)
+            # and both against the merge rule written out in fp32 (an odd number of rows puts the later gathered
+            # messages off the 16-byte grid: the merge kernel must not read them with vector loads)
             w = l_p * torch.exp(m_p - m_p.max(dim=0).values.clamp_min(-1e30))
             ref = (w[..., None] * O_p).sum(0) / w.sum(0).clamp_min(1e-30)[..., None]
             assert float((O.float()[1:] - ref[1:]).abs().max()) <= (2e-2 if out_dtype == torch.bfloat16 else 1e-4)
             assert float(l[0]) == 0.0 and float(m[0]) == float("-inf") and float(O[0].float().abs().sum()) == 0.0
-            # what it stored for its peer.  Blocks the peer owns: rank 0's partial rows in message [0] of the peer's slot
-            # and the step number in the peer's data flags [0][odd blocks] ...
-            sent_O, sent_m, sent_l = message_views(peer_t[slot: slot + n], (rows,), d_v)
-            mO0, mm0, ml0 = message_views(msg0, (rows,), d_v)
-            assert torch.equal(sent_O[~mine], mO0[~mine]) and torch.equal(sent_m[~mine], mm0[~mine]) and torch.equal(sent_l[~mine], ml0[~mine])
-            assert bool((sent_O[mine] == -777.0).all())                  # nothing else travels
-            flags = peer_t[flags_off: flags_off + 3 * GRID].view(torch.int32)
-            odd = torch.arange(GRID, device=cuda) % 2 == 1
-            assert bool((flags[:GRID][odd] == step).all()) and bool((flags[:GRID][~odd] == 0).all())
-            # ... blocks rank 0 owns: the merged rows in the peer's result area and the step number in its result flags
-            pres = peer_t[slot + 2 * stride: slot + 3 * stride]
-            assert torch.equal(pres.view(out_dtype)[: rows * d_v].view(rows, d_v)[mine], Ow[mine])
-            assert torch.equal(pres[rows * d_v: rows * d_v + rows][mine], mw[mine])
-            assert torch.equal(pres[rows * d_v + rows: rows * d_v + 2 * rows][mine], lw[mine])
-            assert bool((flags[2 * GRID:][~odd] == step).all()) and bool((flags[2 * GRID:][odd] == 0).all())
+            mO0, mm0, ml0 = message_views(msgs[0], (rows,), d_v)
+            for q in range(1, W):
+                # what it stored for peer q: rank 0's partial rows in message [0] of the peer's slot (all-gather form: all
+                # rows; owner form: the rows of the blocks the peer owns, nothing else) and the step number in the
+                # peer's data flags [0][those blocks]
+                sent_O, sent_m, sent_l = message_views(t[q][slot: slot + n], (rows,), d_v)
+                theirs = torch.ones(rows, dtype=torch.bool, device=cuda) if gather else owner_of_row == q
+                their_blocks = torch.ones(GRID, dtype=torch.bool, device=cuda) if gather else owner_of_block == q
+                assert torch.equal(sent_O[theirs], mO0[theirs]) and torch.equal(sent_m[theirs], mm0[theirs]) and torch.equal(sent_l[theirs], ml0[theirs])
+                assert bool((sent_O[~theirs] == -777.0).all())
+                flags = t[q][flags_off: flags_off + (W + 1) * GRID].view(torch.int32)
+                assert bool((flags[:GRID][their_blocks] == step).all()) and bool((flags[:GRID][~their_blocks] == 0).all())
+                if gather:
+                    continue
+                # owner form, blocks rank 0 owns: the merged rows in the peer's result area, the step number in its result flags
+                pres = t[q][slot + W * stride: slot + (W + 1) * stride]
+                assert torch.equal(pres.view(out_dtype)[: rows * d_v].view(rows, d_v)[mine], Ow[mine])
+                assert torch.equal(pres[rows * d_v: rows * d_v + rows][mine], mw[mine])
+                assert torch.equal(pres[rows * d_v + rows: rows * d_v + 2 * rows][mine], lw[mine])
+                my_blocks = owner_of_block == 0
+                assert bool((flags[W * GRID:][my_blocks] == step).all()) and bool((flags[W * GRID:][~my_blocks] == 0).all())
         assert flashdmla.device_error_flag() == 0
-        del own_t, peer_t
-        assert L.fdmla_exchange_free(own) == 0 and L.fdmla_exchange_free(peer) == 0
+        del t
+        for r in raw:
+            assert L.fdmla_exchange_free(r) == 0
 
 
 @pytest.mark.gpu
