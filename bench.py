@@ -261,6 +261,8 @@ def main():
                     help="B,H,S of the prefill measurement (default 4,128,8192); a reduced shape is used for ncu captures")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill measurement (profiling aid)")
     ap.add_argument("--only-moe", action="store_true", help="run only the MoE plumbing measurement (profiling aid)")
+    ap.add_argument("--only-long-context", action="store_true",
+                    help="run only the long-context decode over N GPUs (KV split, exchange, merge; profiling aid)")
     ap.add_argument("--only-otf", action="store_true", help="run only the on-the-fly forward/backward measurement (profiling aid)")
     ap.add_argument("--otf-shape", default="", help="B,H,S of the on-the-fly measurement (a reduced shape for ncu captures)")
     ap.add_argument("--only-gemm", action="store_true", help="run only the batched-GEMM measurement (profiling aid)")
@@ -317,6 +319,14 @@ def main():
                               "device_error_flag": flashdmla.device_error_flag()}), flush=True)
         if world > 1:
             dist.destroy_process_group()
+        return
+    if args.only_long_context:
+        if world < 2:
+            raise SystemExit("--only-long-context needs --gpus N > 1 under torch.distributed.run")
+        lc = bench_long_context(dev, rank, world)
+        if rank == 0:
+            print(json.dumps({"long_context": lc, "device_error_flag": flashdmla.device_error_flag()}), flush=True)
+        dist.destroy_process_group()
         return
     if args.only_moe:
         mp_ = bench_moe_plumbing(dev, hbm_peak)
@@ -551,7 +561,9 @@ def bench_long_context(dev, rank, world, steps=50, warmup=10):
     into `world` contiguous page-aligned slices (remainder to the first ranks, the rule of the reference's
     csrc/attention/fa2_fwd_mpi.cu:47-53), every rank attends its slice, the partial (O, m, l) travel in one
     NCCL all-gather and every rank merges them.  Timed per phase with CUDA events (median over the steps, max over
-    ranks) and as a whole like the headline (K steps between barriers, max over ranks)."""
+    ranks) and as a whole like the headline (K steps between barriers, max over ranks).  Then the same step with the
+    exchange and the merge as one kernel over peer memory (flashdmla.exchange), which must return the same bits; the
+    faster of the two graph replays is the reported step."""
     import flashdmla
     from flashdmla import parallel
     B8 = 8
@@ -681,7 +693,9 @@ def bench_long_context(dev, rank, world, steps=50, warmup=10):
             "allgather_busbw_gbs": (world - 1) * msg_bytes / (ag_ms * 1e-3) / 1e9,
             "vs_1gpu_ms": one_ms, "speedup_over_1gpu": one_ms / total_ms,
             "local_hbm_gbs_rank0": local_tokens * D_QK * 2 / (local_ms * 1e-3) / 1e9,
-            "max_abs_vs_unsplit": err, "collective": "torch.distributed.all_gather_into_tensor (NCCL), one message per rank",
+            "max_abs_vs_unsplit": err, "collective": ("exchange_merge_kernel: peer stores over NVLink into buffers mapped with CUDA IPC, the merge in the same kernel "
+                           "(the NCCL all-gather + merge path is timed beside it: ms_per_step_graph)" if use_peer else
+                           "torch.distributed.all_gather_into_tensor (NCCL), one message per rank"),
             "limiter": max((("local attention", local_ms), ("all-gather", ag_ms), ("merge", merge_ms)), key=lambda kv: kv[1])[0]}
 
 

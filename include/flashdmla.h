@@ -259,14 +259,17 @@ int fdmla_merge_lse_strided(const float *O_part, const float *m_part,
  *
  * A step, on every rank: msg is the rank's message [ O (rows x d_v) | m (rows) | l (rows) ] fp32 (what
  * fdmla_decode_paged_partial writes); bufs[p], p < world, is rank p's buffer as mapped in this process
- * (bufs[rank] the rank's own; a host array).  The rows are dealt to the ranks in 128 runs; the kernel stores its
- * partial rows of a run into the buffer of the rank that owns the run, and for the runs it owns itself waits for
- * its peers' rows, merges, and stores the merged rows into every peer's buffer, from where each copies them out:
- * every rank ends with the merged O [rows, d_v] (out_dtype), m, l [rows], having sent (world - 1) / world of a
- * message and its share of the results.  The arithmetic is that of fdmla_merge_lse_strided on the all-gathered
+ * (bufs[rank] the rank's own; a host array).  Up to four ranks, the kernel stores the whole message into every
+ * peer's buffer, waits for the peers' and merges everything itself (one NVLink hop).  Beyond four, the rows are
+ * dealt to the ranks in 128 runs; the kernel stores its partial rows of a run into the buffer of the rank that
+ * owns the run, and for the runs it owns itself waits for its peers' rows, merges, and stores the merged rows
+ * into every peer's buffer, from where each copies them out (two hops; a rank sends (world - 1) / world of a
+ * message and its share of the results).  Either way every rank ends with the merged O [rows, d_v] (out_dtype),
+ * m, l [rows].  The arithmetic is that of fdmla_merge_lse_strided on the all-gathered
  * messages, part by part in rank order (bit-identical to it up to 4096 rows, where that merge sums in the same
- * order).  All ranks must issue the same sequence of steps on one set of buffers, each rank from one stream (a
- * step may be captured into a CUDA graph: the step counter lives in the buffer).  A peer that does not arrive
+ * order).  FDMLA_EXCHANGE_GATHER=1 / 0 in the environment (of every rank alike) forces the first / second form.
+ * All ranks must issue the same sequence of steps on one set of buffers, each rank from one stream (a step may
+ * be captured into a CUDA graph: the step counter lives in the buffer).  A peer that does not arrive
  * within timeout_ms leaves O, m, l of the affected rows unwritten and sets fdmla_device_error_flag code 31; the
  * buffers must then be set up again.
  * world <= 16, d_v a multiple of 4.
