@@ -1,6 +1,7 @@
 // extern "C" entry points of libflashdmla.so: argument checks, problem
 // set-up and dispatch to the tcgen05 or the portable kernels.  Nothing here
-// allocates or synchronises; every scratch buffer comes from the caller.
+// allocates or synchronises; every scratch buffer comes from the caller (the
+// one exception: fdmla_exchange_alloc / _free, the set-up of an exchange buffer).
 #include <cmath>
 #include "common.cuh"
 
@@ -187,8 +188,18 @@ int fdmla_exchange_free(void *buf) {
 
 int fdmla_exchange_merge(const float *msg, void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
                          float *m, float *l, int out_dtype, int timeout_ms, void *stream) {
-    const int rc = launch_exchange_merge(msg, bufs, world, rank, rows, d_v, O, m, l, out_dtype, timeout_ms,
-                                         static_cast<cudaStream_t>(stream));
+    const int rc = launch_exchange_merge(nullptr, nullptr, nullptr, 0, const_cast<float *>(msg), bufs, world, rank, rows, d_v,
+                                         O, m, l, out_dtype, timeout_ms, static_cast<cudaStream_t>(stream));
+    if (rc == FDMLA_OK && rows > 0) t_last_kernel = "exchange_merge_kernel";
+    return rc;
+}
+
+int fdmla_exchange_merge_parts(const float *O_part, const float *m_part, const float *l_part, int num_parts, float *msg,
+                               void *const *bufs, int world, int rank, long long rows, int d_v, void *O, float *m,
+                               float *l, int out_dtype, int timeout_ms, void *stream) {
+    if (num_parts < 1) return FDMLA_ERR_INVALID;
+    const int rc = launch_exchange_merge(O_part, m_part, l_part, num_parts, msg, bufs, world, rank, rows, d_v, O, m, l,
+                                         out_dtype, timeout_ms, static_cast<cudaStream_t>(stream));
     if (rc == FDMLA_OK && rows > 0) t_last_kernel = "exchange_merge_kernel";
     return rc;
 }
@@ -361,7 +372,9 @@ int fdmla_decode_paged_partial(const void *Q, const void *kv_pool, const int32_t
         num_splits < 1)
         return FDMLA_ERR_INVALID;
     if (B == 0 || H == 0) return FDMLA_OK;
-    if (!Q || !kv_pool || !page_table || !seqlens || !O_out || !m_out || !l_out) return FDMLA_ERR_INVALID;
+    if (!Q || !kv_pool || !page_table || !seqlens) return FDMLA_ERR_INVALID;
+    const bool pieces_only = !O_out && !m_out && !l_out && num_splits > 1;      // the caller merges the pieces itself
+    if (!pieces_only && (!O_out || !m_out || !l_out)) return FDMLA_ERR_INVALID;
     if (num_splits > 1 && (!O_part || !m_part || !l_part)) return FDMLA_ERR_WORKSPACE;
     if (B > 65535 || (long long)max_pages * page_size > 2147483647LL) return FDMLA_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -385,7 +398,7 @@ int fdmla_decode_paged_partial(const void *Q, const void *kv_pool, const int32_t
         if (p.quota_min < 1) p.quota_min = 1;
     }
     const int rc = run_forward(p, dtype, st);
-    if (rc) return rc;
+    if (rc || pieces_only) return rc;
     return launch_merge(O_part, m_part, l_part, O_out, m_out, l_out, (long long)B * H, d_v, num_splits, FDMLA_F32, st);
 }
 

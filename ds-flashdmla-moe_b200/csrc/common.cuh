@@ -140,7 +140,8 @@ int launch_rope_rows(const void *x, long long ldx, void *y, long long ldy, const
 int gemm_error_flag(int reset);
 int exchange_error_flag(int reset);
 size_t exchange_bytes(int world, long long rows, int d_v);
-int launch_exchange_merge(const void *msg, void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
+int launch_exchange_merge(const float *O_part, const float *m_part, const float *l_part, int num_parts, void *msg,
+                          void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
                           float *m, float *l, int out_dtype, int timeout_ms, cudaStream_t stream);
 // tcgen05 projections / weight-gradient partials for widths (128 -> 64) and (64 -> 128 transposed); they return
 // FDMLA_ERR_UNSUPPORTED for other shapes

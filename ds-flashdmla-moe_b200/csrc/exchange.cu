@@ -50,7 +50,12 @@ enum { ERR_EXCHANGE_TIMEOUT = 31 };
 __device__ int g_xch_error = 0;
 
 struct Args {
-    const float *msg;              // this rank's message
+    // The pieces of this rank's partial result that are still to be merged into its message (num_parts > 0: dense
+    // [num_parts, rows, d_v], [num_parts, rows], [num_parts, rows]; parts with l <= 0 hold nothing), or nothing
+    // (num_parts == 0: msg already holds the rank's partial result).
+    const float *O_part, *m_part, *l_part;
+    int num_parts;
+    float *msg;                    // this rank's message
     float *bufs[MAX_WORLD];        // exchange buffer of every rank as mapped here; bufs[rank] is this rank's own
     int world, rank;
     long long rows;
@@ -129,18 +134,77 @@ __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
     const int owner = GATHER ? a.rank : c % W;        // all-gather form: every rank merges every run itself
     TO *O = static_cast<TO *>(a.O);
 
+    if (a.num_parts > 0) {
+        // ---- 0. this block's rows of the rank's own pieces into its message: a warp per row, the arithmetic of the
+        // merge kernel, piece by piece in order (lane q holds m and l of pieces q and q + 32) ---------------------------
+        const int warp = tid >> 5, lane = tid & 31, P = a.num_parts;
+        const size_t so = (size_t)a.rows * a.d_v, sml = (size_t)a.rows;
+        for (long long r = r0 + warp; r < r1; r += THREADS / 32) {
+            float m_q[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_q[2] = {0.f, 0.f};
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (lane + 32 * h < P) {
+                    l_q[h] = a.l_part[(size_t)(lane + 32 * h) * sml + r];
+                    m_q[h] = a.m_part[(size_t)(lane + 32 * h) * sml + r];
+                }
+            auto l_of = [&](int q) { return __shfl_sync(0xffffffffu, q < 32 ? l_q[0] : l_q[1], q & 31); };
+            auto m_of = [&](int q) { return __shfl_sync(0xffffffffu, q < 32 ? m_q[0] : m_q[1], q & 31); };
+            float mx = -CUDART_INF_F;
+            for (int q = 0; q < P; ++q) {
+                const float lp = l_of(q), mp = m_of(q);
+                if (lp > 0.f) mx = fmaxf(mx, mp);
+            }
+            float ls = 0.f;
+            for (int q = 0; q < P; ++q) {
+                const float lp = l_of(q), mp = m_of(q);
+                if (lp > 0.f) ls += lp * __expf(mp - mx);
+            }
+            const float inv = ls > 0.f ? 1.f / ls : 0.f;
+            for (int c0 = 0; c0 < a.d_v; c0 += 512) {
+                float acc[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+                for (int q = 0; q < P; ++q) {
+                    const float lp = l_of(q), mp = m_of(q);
+                    if (lp > 0.f) {
+                        const float w = lp * __expf(mp - mx) * inv;
+                        const float *src = a.O_part + (size_t)q * so + (size_t)r * a.d_v;
+                        float4 v[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int col = c0 + (i * 32 + lane) * 4;
+                            v[i] = col < a.d_v ? *reinterpret_cast<const float4 *>(src + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            acc[i][0] = fmaf(w, v[i].x, acc[i][0]); acc[i][1] = fmaf(w, v[i].y, acc[i][1]);
+                            acc[i][2] = fmaf(w, v[i].z, acc[i][2]); acc[i][3] = fmaf(w, v[i].w, acc[i][3]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int col = c0 + (i * 32 + lane) * 4;
+                    if (col < a.d_v) store4(a.msg + (size_t)r * a.d_v + col, acc[i]);
+                }
+            }
+            if (lane == 0) { a.msg[o_m + r] = mx; a.msg[o_l + r] = ls; }
+        }
+        __syncthreads();          // the rows are read back below by other threads of this block
+    }
+
     if (GATHER) {
         // ---- this block's rows of this rank's message into every peer's buffer -------------------------------
         const float4 *src = reinterpret_cast<const float4 *>(a.msg + (size_t)r0 * a.d_v);
         const size_t dst_off = slot_off + (size_t)a.rank * a.stride;
         const long long n4 = nr * a.d_v / 4;
         for (long long i = tid; i < n4; i += THREADS) {
-            const float4 v = src[i];
+            const float4 v = __ldcg(src + i);
             for (int p = 0; p < W; ++p)
                 if (p != a.rank) reinterpret_cast<float4 *>(a.bufs[p] + dst_off + (size_t)r0 * a.d_v)[i] = v;
         }
         for (long long i = tid; i < nr; i += THREADS) {
-            const float mv = a.msg[o_m + r0 + i], lv = a.msg[o_l + r0 + i];
+            const float mv = __ldcg(a.msg + o_m + r0 + i), lv = __ldcg(a.msg + o_l + r0 + i);
             for (int p = 0; p < W; ++p)
                 if (p != a.rank) {
                     a.bufs[p][dst_off + o_m + r0 + i] = mv;
@@ -157,10 +221,10 @@ __global__ void __launch_bounds__(THREADS) exchange_merge_kernel(const Args a) {
         const float4 *src = reinterpret_cast<const float4 *>(a.msg + (size_t)r0 * a.d_v);
         float4 *dst4 = reinterpret_cast<float4 *>(dst + (size_t)r0 * a.d_v);
         const long long n4 = nr * a.d_v / 4;
-        for (long long i = tid; i < n4; i += THREADS) dst4[i] = src[i];
+        for (long long i = tid; i < n4; i += THREADS) dst4[i] = __ldcg(src + i);
         for (long long i = tid; i < nr; i += THREADS) {
-            dst[o_m + r0 + i] = a.msg[o_m + r0 + i];
-            dst[o_l + r0 + i] = a.msg[o_l + r0 + i];
+            dst[o_m + r0 + i] = __ldcg(a.msg + o_m + r0 + i);
+            dst[o_l + r0 + i] = __ldcg(a.msg + o_l + r0 + i);
         }
         __threadfence_system();
         __syncthreads();
@@ -288,16 +352,20 @@ size_t exchange_bytes(int world, long long rows, int d_v) {
     return (xch::flags_offset_floats(world, stride) + (size_t)world * xch::GRID + 2 * xch::GRID) * sizeof(float);
 }
 
-int launch_exchange_merge(const void *msg, void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
+int launch_exchange_merge(const float *O_part, const float *m_part, const float *l_part, int num_parts, void *msg,
+                          void *const *bufs, int world, int rank, long long rows, int d_v, void *O,
                           float *m, float *l, int out_dtype, int timeout_ms, cudaStream_t stream) {
     using namespace xch;
     if (world < 1 || world > MAX_WORLD || rank < 0 || rank >= world || rows < 0 || d_v <= 0 || timeout_ms <= 0) return FDMLA_ERR_INVALID;
     if (rows == 0) return FDMLA_OK;
-    if (!msg || !bufs || !O || !m || !l) return FDMLA_ERR_INVALID;
+    if (!msg || !bufs || !O || !m || !l || num_parts < 0 || num_parts > 64) return FDMLA_ERR_INVALID;
+    if (num_parts > 0 && (!O_part || !m_part || !l_part)) return FDMLA_ERR_INVALID;
     if (d_v & 3) return FDMLA_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(O_part) & 15) return FDMLA_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(msg) | reinterpret_cast<uintptr_t>(O)) & 15) return FDMLA_ERR_UNSUPPORTED;
     Args a{};
-    a.msg = static_cast<const float *>(msg);
+    a.O_part = O_part; a.m_part = m_part; a.l_part = l_part; a.num_parts = num_parts;
+    a.msg = static_cast<float *>(msg);
     for (int p = 0; p < world; ++p) {
         if (!bufs[p] || (reinterpret_cast<uintptr_t>(bufs[p]) & 15)) return FDMLA_ERR_INVALID;
         a.bufs[p] = static_cast<float *>(bufs[p]);

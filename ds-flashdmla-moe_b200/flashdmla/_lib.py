@@ -44,6 +44,7 @@ SIGNATURES = {
     "fdmla_exchange_close": (_i, [_vp]),
     "fdmla_exchange_free": (_i, [_vp]),
     "fdmla_exchange_merge": (_i, [_vp, _vp, _i, _i, _ll, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "fdmla_exchange_merge_parts": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _ll, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "fdmla_gemm_batched": (_i, [_vp] * 4 + [_i] * 4 + [_ll, _ll, _i, _i, _ll, _ll, _i, _i, _i, _ll, _ll, _ll, _i, _vp]),
     "fdmla_gemm_grouped": (_i, [_vp] * 5 + [_i] * 4 + [_ll, _ll, _ll, _i, _i, _ll, _i, _vp]),
     "fdmla_rope_rows": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _f, _vp]),

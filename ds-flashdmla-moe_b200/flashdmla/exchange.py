@@ -76,6 +76,33 @@ class PeerExchange:
                   "fdmla_exchange_merge")
         return out
 
+    def merge_parts(self, parts, msg: torch.Tensor, out):
+        """The same step when the rank's own partial result is still in pieces: parts = (O_part [S, rows.., d_v], m_part,
+        l_part [S, rows..]) fp32, dense (what `flash_dmla_paged_decode_partial(..., pieces_only=True)` leaves in its
+        scratch).  The kernel first merges the pieces into `msg` (which it overwrites), then exchanges and merges as
+        `merge` does: one launch for the local merge, the exchange and the final merge."""
+        Op, mp, lp = parts
+        S = Op.shape[0]
+        n = self.rows * (self.d_v + 2)
+        for t, k in ((Op, S * self.rows * self.d_v), (mp, S * self.rows), (lp, S * self.rows)):
+            if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.numel() == k):
+                raise FlashDMLAError("parts must be dense CUDA float32 tensors [S, rows, d_v], [S, rows], [S, rows]")
+        if not (msg.is_cuda and msg.dtype == torch.float32 and msg.is_contiguous() and msg.numel() == n):
+            raise FlashDMLAError("message must be a contiguous CUDA float32 tensor of rows * (d_v + 2) elements")
+        O, m, l = out
+        if (O.numel() != self.rows * self.d_v or m.numel() != self.rows or l.numel() != self.rows
+                or not (O.is_contiguous() and m.is_contiguous() and l.is_contiguous())
+                or O.dtype not in (torch.float32, torch.bfloat16) or m.dtype != torch.float32 or l.dtype != torch.float32):
+            raise FlashDMLAError("out tensors do not match the merged result")
+        code = _lib.F32 if O.dtype == torch.float32 else _lib.BF16
+        with torch.cuda.device(self.device):
+            stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            check(_lib.lib().fdmla_exchange_merge_parts(Op.data_ptr(), mp.data_ptr(), lp.data_ptr(), int(S), msg.data_ptr(),
+                                                        self._bufs, self.world, self.rank, self.rows, self.d_v,
+                                                        O.data_ptr(), m.data_ptr(), l.data_ptr(), code, self.timeout_ms, stream),
+                  "fdmla_exchange_merge_parts")
+        return out
+
     def close(self):
         """Unmap the peers' buffers and free this rank's own (collective in effect: peers must have stopped using it)."""
         L = _lib.lib()

@@ -301,17 +301,21 @@ def suggest_partial_slabs(B: int, H: int, max_tokens: int, page_size: int = 64) 
 
 
 def flash_dmla_paged_decode_partial(Q, kv_pool, page_table, seqlens, d_v, scale=None, num_splits=None, out=None,
-                                    scratch=None):
+                                    scratch=None, pieces_only=False):
     """Attention of Q [B,H,d_qk] over the whole of this paged cache as an fp32 partial result: O [B,H,d_v] normalised
     by its own l, m, l [B,H] - what a rank that holds one slice of every sequence sends to its peers.  out: three
     contiguous fp32 tensors to write into (views of a message buffer); scratch: (O_part [S,B,H,d_v], m_part, l_part
-    [S,B,H]) fp32 for num_splits = S > 1, allocated when missing."""
+    [S,B,H]) fp32 for num_splits = S > 1, allocated when missing.  pieces_only (S > 1): leave the pieces unmerged in
+    `scratch` and return it - for a caller that merges them itself (`PeerExchange.merge_parts`); pieces with l <= 0
+    hold nothing."""
     _need_cuda(Q, kv_pool, page_table, seqlens)
     _same_dtype(Q, kv_pool)
     if page_table.dtype != torch.int32 or seqlens.dtype != torch.int32:
         raise FlashDMLAError("page_table and seqlens must be int32")
     Q, kv_pool, page_table, seqlens = Q.contiguous(), kv_pool.contiguous(), page_table.contiguous(), seqlens.contiguous()
     B, H, d_qk = Q.shape
+    if pieces_only and (num_splits is None or int(num_splits) < 2 or scratch is None):
+        raise FlashDMLAError("pieces_only needs num_splits >= 2 and the scratch tensors that receive the pieces")
     num_pages, page_size, _ = kv_pool.shape
     max_pages = page_table.shape[1]
     if scale is None:
@@ -320,13 +324,16 @@ def flash_dmla_paged_decode_partial(Q, kv_pool, page_table, seqlens, d_v, scale=
     if num_splits is None:
         num_splits = suggest_partial_slabs(B, H, max_pages * page_size, page_size) if (d_qk, d_v) == (576, 512) else 1
     S = max(1, int(num_splits))
-    if out is None:
-        out = (torch.empty(B, H, d_v, dtype=torch.float32, device=dev), torch.empty(B, H, dtype=torch.float32, device=dev),
-               torch.empty(B, H, dtype=torch.float32, device=dev))
-    O, m, l = out
-    for t, n in ((O, B * H * d_v), (m, B * H), (l, B * H)):
-        if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n or t.device != dev:
-            raise FlashDMLAError("out must be contiguous float32 tensors of B*H*d_v, B*H and B*H elements")
+    if pieces_only:
+        O = m = l = None
+    else:
+        if out is None:
+            out = (torch.empty(B, H, d_v, dtype=torch.float32, device=dev), torch.empty(B, H, dtype=torch.float32, device=dev),
+                   torch.empty(B, H, dtype=torch.float32, device=dev))
+        O, m, l = out
+        for t, n in ((O, B * H * d_v), (m, B * H), (l, B * H)):
+            if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n or t.device != dev:
+                raise FlashDMLAError("out must be contiguous float32 tensors of B*H*d_v, B*H and B*H elements")
     Op = mp = lp = None
     if S > 1:
         if scratch is None:
@@ -340,7 +347,7 @@ def flash_dmla_paged_decode_partial(Q, kv_pool, page_table, seqlens, d_v, scale=
             _ptr(Q), _ptr(kv_pool), _ptr(page_table), _ptr(seqlens), _ptr(O), _ptr(m), _ptr(l), _ptr(Op), _ptr(mp), _ptr(lp),
             B, H, d_qk, int(d_v), page_size, max_pages, num_pages, S, float(scale), _dtype_code(Q), _stream(Q)),
             "fdmla_decode_paged_partial")
-    return O, m, l
+    return scratch if pieces_only else (O, m, l)
 
 
 def _part_stride(t: torch.Tensor, inner: int) -> Optional[int]:

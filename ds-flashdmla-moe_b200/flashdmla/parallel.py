@@ -191,6 +191,11 @@ class SequenceParallelDecoder:
     def step(self, Q, local_pool, local_page_table, local_seqlens):
         """One decode step; returns (O [B,H,d_v], m, l) - the same tensors every call."""
         from . import ops
+        if self.xch is not None and self.part is not None:
+            # the pieces of the local slice stay in the scratch slabs; one kernel merges them, exchanges and merges again
+            ops.flash_dmla_paged_decode_partial(Q, local_pool, local_page_table, local_seqlens, self.d_v, self.scale,
+                                                num_splits=self.splits, scratch=self.part, pieces_only=True)
+            return self.xch.merge_parts(self.part, self.msg, self.out)
         mO, mm, ml = message_views(self.msg, (self.B, self.H), self.d_v)
         ops.flash_dmla_paged_decode_partial(Q, local_pool, local_page_table, local_seqlens, self.d_v, self.scale,
                                             num_splits=self.splits, out=(mO, mm, ml), scratch=self.part)

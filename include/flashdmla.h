@@ -161,6 +161,8 @@ int fdmla_decode_paged(const void *Q, const void *kv_pool,
  * fdmla_merge_lse_strided.  O_part / m_part / l_part [num_splits, ...] are private scratch (NULL for num_splits
  * == 1): the library cuts the work as it likes (on the tcgen05 path: the 256-key tiles of all sequences in equal
  * contiguous runs, which suits few long ragged sequences) and merges the pieces into the output itself.
+ * With num_splits >= 2 and O_out = m_out = l_out = NULL the pieces are left unmerged in the scratch (a piece with
+ * l <= 0 holds nothing) for a caller that merges them itself (fdmla_exchange_merge_parts).
  * Replaces the per-rank part of fa2_forward_mpi (csrc/attention/fa2_fwd_mpi.cu:76-90: each rank's fa2_forward over
  * its rows), for the split along the keys that long-context decode needs.
  */
@@ -282,6 +284,15 @@ int fdmla_exchange_free(void *buf);
 int fdmla_exchange_merge(const float *msg, void *const *bufs, int world, int rank,
                          long long rows, int d_v, void *O, float *m, float *l,
                          int out_dtype, int timeout_ms, void *stream);
+/* The same step when the rank's own partial result is still in num_parts (1..64) pieces - O_part [num_parts, rows,
+ * d_v], m_part, l_part [num_parts, rows] fp32, dense, pieces with l <= 0 hold nothing: what
+ * fdmla_decode_paged_partial leaves in its scratch when it is called without outputs.  The kernel first merges the
+ * pieces into msg (written, then sent), so the local merge, the exchange and the final merge are one launch. */
+int fdmla_exchange_merge_parts(const float *O_part, const float *m_part,
+                               const float *l_part, int num_parts, float *msg,
+                               void *const *bufs, int world, int rank, long long rows,
+                               int d_v, void *O, float *m, float *l, int out_dtype,
+                               int timeout_ms, void *stream);
 
 /*
  * Batched bf16 GEMM on the tensor cores, fp32 accumulation: C[b] (M x N) = A[b] (M x K) * B[b] for b < batch.

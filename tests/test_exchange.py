@@ -53,11 +53,13 @@ def test_exchange_argument_validation_needs_no_gpu():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("pieces", [0, 5])
 @pytest.mark.parametrize("world", [2, 5])
 @pytest.mark.parametrize("rows,d_v,out_dtype", [(1024, 512, torch.bfloat16), (130, 512, torch.float32), (7, 64, torch.float32)])
-def test_exchange_merge_against_merge_kernel(rows, d_v, out_dtype, world, cuda):
+def test_exchange_merge_against_merge_kernel(rows, d_v, out_dtype, world, pieces, cuda):
     """world 2 runs the all-gather form (whole messages to every peer, every rank merges everything), world 5 the owner
-    form (rows to the rank that owns their block, merged rows back)."""
+    form (rows to the rank that owns their block, merged rows back).  pieces > 0: rank 0's own partial result arrives in
+    that many unmerged pieces (fdmla_exchange_merge_parts: the kernel merges them into the message first)."""
     import flashdmla
     from flashdmla import _lib
     from flashdmla.parallel import message_views
@@ -79,6 +81,11 @@ def test_exchange_merge_against_merge_kernel(rows, d_v, out_dtype, world, cuda):
         mine = torch.ones(rows, dtype=torch.bool, device=cuda) if gather else owner_of_row == 0
         for step in (1, 2, 3):                                           # slots 1, 0, 1
             msgs = [_message(rows, d_v, 10 * step + q, empty_rows=(0,) if q == 0 else (0, rows - 1)).to(cuda) for q in range(W)]
+            if pieces:
+                # rank 0's message = the merge kernel's result over its pieces (piece 1 empty everywhere, row 0 empty in all)
+                pm = [_message(rows, d_v, 100 * step + q, empty_rows=range(rows) if q == 1 else (0,)).to(cuda) for q in range(pieces)]
+                pO, pmm, pl = (t.contiguous() for t in message_views(torch.stack(pm), (rows,), d_v))
+                msgs[0] = torch.cat([t.reshape(-1) for t in flashdmla.merge_partials(pO, pmm, pl, torch.float32)])
             O_p, m_p, l_p = message_views(torch.stack(msgs), (rows,), d_v)
             Ow, mw, lw = flashdmla.merge_partials(O_p, m_p, l_p, out_dtype)
             slot = (step & 1) * slot_floats
@@ -103,10 +110,18 @@ def test_exchange_merge_against_merge_kernel(rows, d_v, out_dtype, world, cuda):
             m = torch.full((rows,), float("nan"), device=cuda)
             l = torch.full((rows,), float("nan"), device=cuda)
             torch.cuda.synchronize()
-            rc = L.fdmla_exchange_merge(msgs[0].data_ptr(), bufs, W, 0, rows, d_v, O.data_ptr(), m.data_ptr(), l.data_ptr(),
-                                        code, 2000, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            if pieces:
+                built = torch.full((n,), float("nan"), device=cuda)
+                rc = L.fdmla_exchange_merge_parts(pO.data_ptr(), pmm.data_ptr(), pl.data_ptr(), pieces, built.data_ptr(), bufs, W, 0,
+                                                  rows, d_v, O.data_ptr(), m.data_ptr(), l.data_ptr(), code, 2000, stream)
+            else:
+                rc = L.fdmla_exchange_merge(msgs[0].data_ptr(), bufs, W, 0, rows, d_v, O.data_ptr(), m.data_ptr(), l.data_ptr(),
+                                            code, 2000, stream)
             assert rc == 0
             torch.cuda.synchronize()
+            if pieces:
+                assert torch.equal(built, msgs[0])                    # the message it built from the pieces, bit for bit
             assert flashdmla.last_kernel() == "exchange_merge_kernel"
             assert torch.equal(O, Ow) and torch.equal(m, mw) and torch.equal(l, lw)        # bit for bit
             # and both against the merge rule written out in fp32 (an odd number of rows puts the later gathered
