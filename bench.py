@@ -871,8 +871,19 @@ def bench_gemm(dev, tf_burst, hbm_peak, E=64):
         torch.cuda.synchronize()
         return median_launch_ms(gr.replay, launches=10, warmup=2) / reps
     ta, tp = graph_ms(ga), graph_ms(gp)
+    del q, WUK, WUV, o_lat, Qo, oo
+    # the CTA-pair form of the kernel (256 x 256 tiles over two SMs) on a problem whose rows fill such tiles
+    Mp = 8192
+    Ap, Bp, Cp = mk(Mp, Mp), mk(Mp, Mp, std=0.02), torch.empty(Mp, Mp, dtype=torch.bfloat16, device=dev)
+    t_pair = median_launch_ms(lambda: gemm.gemm_batched(Ap, Bp, Cp, 1, Mp, Mp, Mp), launches=10, warmup=3)
+    t_vend = median_launch_ms(lambda: torch.matmul(Ap, Bp, out=Cp), launches=10, warmup=3)
+    del Ap, Bp, Cp
     ba, bp = (n * Hh * 128 + Hh * 512 * 128 + n * Hh * 512) * 2, (n * Hh * 512 + Hh * 512 * 128 + n * Hh * 128) * 2
-    return {"kernel": "tcg::gemm_kernel (tcgen05, TMA ring of 4 x 48 KB, 128 x 256 tiles, two accumulators in tensor memory)",
+    return {"kernel": "tcg::gemm_kernel (tcgen05, TMA ring of 4 x 48 KB, 128 x 256 tiles, two accumulators in tensor memory; "
+                      "CTA pairs with 256 x 256 tiles and 6 x 32 KB stages where the rows fill them)",
+            "pair_form_8192_cubed_ms": t_pair, "pair_form_8192_cubed_tflops": 2.0 * Mp ** 3 / (t_pair * 1e-3) / 1e12,
+            "pair_form_8192_cubed_frac_of_measured_bf16_peak": 2.0 * Mp ** 3 / (t_pair * 1e-3) / 1e12 / tf_burst,
+            "vendor_library_8192_cubed_tflops": 2.0 * Mp ** 3 / (t_vend * 1e-3) / 1e12,
             "expert_mlp_workload": f"E={E} x {rows} rows, d={d}, d_ff={f}, bf16 (padded packing of T=4096, top-8, capacity 1.25)",
             "gate_up_gemm_ms": t1, "gate_up_gemm_tflops": fl1 / (t1 * 1e-3) / 1e12, "down_gemm_ms": t2,
             "down_gemm_tflops": fl2 / (t2 * 1e-3) / 1e12,
