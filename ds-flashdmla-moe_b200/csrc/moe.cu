@@ -149,15 +149,47 @@ __global__ void __launch_bounds__(PACK_BLOCK) pack_assign_kernel(const int *__re
     pos[a] = p;
 }
 
+// The gather walks its 16-byte vectors flat over a grid that fills the GPU once, keeps (row, vector) as a pair that
+// advances by the grid's stride - no division in the loop - and issues several loads before the first store.
+struct RowVec {
+    int r, v;                    // row and vector inside the row
+    int dr, dv, vpr;             // the grid's stride as (rows, vectors), vectors per row
+    __device__ __forceinline__ RowVec(int vec_per_row) : vpr(vec_per_row) {
+        const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x, st = (long long)gridDim.x * blockDim.x;
+        r = (int)(i / vpr); v = (int)(i - (long long)r * vpr);
+        dr = (int)(st / vpr); dv = (int)(st - (long long)dr * vpr);
+    }
+    __device__ __forceinline__ void step() {
+        r += dr; v += dv;
+        if (v >= vpr) { v -= vpr; ++r; }
+    }
+};
+
 // ---- gather: packed[r] = x[perm[r]] (16-byte vectors) -----------------------------------------------
-__global__ void gather_rows_kernel(const uint4 *__restrict__ x, const int *__restrict__ perm, const int *__restrict__ offsets,
-                                   uint4 *__restrict__ packed, int E, int vec_per_row) {
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4 *__restrict__ x, const int *__restrict__ perm,
+                                                          const int *__restrict__ offsets, uint4 *__restrict__ packed, int E,
+                                                          int vec_per_row) {
     const int n_rows = offsets[E];
-    const long long total = (long long)n_rows * vec_per_row;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int r = (int)(i / vec_per_row), v = (int)(i - (long long)r * vec_per_row);
-        const int t = perm[r];          // -1: a row of padded packing that holds no assignment
-        packed[i] = t >= 0 ? x[(size_t)t * vec_per_row + v] : make_uint4(0, 0, 0, 0);
+    constexpr int U = 4;
+    RowVec it(vec_per_row);
+    while (it.r < n_rows) {
+        uint4 val[U];
+        size_t dst[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            live[u] = it.r < n_rows;
+            val[u] = make_uint4(0, 0, 0, 0);
+            if (live[u]) {
+                dst[u] = (size_t)it.r * vec_per_row + it.v;
+                const int t = perm[it.r];          // -1: a row of padded packing that holds no assignment
+                if (t >= 0) val[u] = x[(size_t)t * vec_per_row + it.v];
+            }
+            it.step();
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (live[u]) packed[dst[u]] = val[u];
     }
 }
 
@@ -171,11 +203,22 @@ __global__ void scatter_rows_kernel(const uint4 *__restrict__ x, const int *__re
         __syncthreads();
         if (threadIdx.x < k) s_pos[threadIdx.x] = pos[(size_t)t * k + threadIdx.x];
         __syncthreads();
-        for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-            const uint4 val = x[(size_t)t * vec_per_row + v];
+        constexpr int U = 4;            // vectors of the row a thread reads before it starts storing
+        for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += blockDim.x * U) {
+            uint4 val[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int v = v0 + u * blockDim.x;
+                if (v < vec_per_row) val[u] = x[(size_t)t * vec_per_row + v];
+            }
             for (int j = 0; j < k; ++j) {
                 const int p = s_pos[j];
-                if (p >= 0) packed[(size_t)p * vec_per_row + v] = val;
+                if (p < 0) continue;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int v = v0 + u * blockDim.x;
+                    if (v < vec_per_row) packed[(size_t)p * vec_per_row + v] = val[u];
+                }
             }
         }
     }
@@ -220,17 +263,25 @@ __global__ void combine_bf16x8_kernel(const __nv_bfloat16 *__restrict__ y, const
     const float inv = kept_sum > 0.f ? 1.f / kept_sum : 0.f;
     for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < k; ++j) {
-            const int p = s_pos[j];
-            if (p < 0) continue;
-            const uint4 v = *reinterpret_cast<const uint4 *>(y + (size_t)p * d + c);
-            const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
-            const float wj = s_w[j] * inv;
+        constexpr int U = 8;            // source rows read side by side: all of their loads are issued before the sums
+        for (int j0 = 0; j0 < k; j0 += U) {
+            uint4 v[U];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(h[e]);
-                acc[2 * e] += wj * f.x;
-                acc[2 * e + 1] += wj * f.y;
+            for (int u = 0; u < U; ++u) {
+                const int p = j0 + u < k ? s_pos[j0 + u] : -1;
+                if (p >= 0) v[u] = *reinterpret_cast<const uint4 *>(y + (size_t)p * d + c);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (j0 + u >= k || s_pos[j0 + u] < 0) continue;
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v[u]);
+                const float wj = s_w[j0 + u] * inv;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(h[e]);
+                    acc[2 * e] += wj * f.x;
+                    acc[2 * e + 1] += wj * f.y;
+                }
             }
         }
         if (shared) {
@@ -300,8 +351,23 @@ extern "C" int fdmla_moe_gather(const void *x, const int *perm, const int *offse
     if ((d * esz) % 16 || ((uintptr_t)x | (uintptr_t)packed) % 16) return FDMLA_ERR_UNSUPPORTED;
     if (max_rows == 0) return FDMLA_OK;
     const int vec = d * esz / 16;
-    long long blocks = ((long long)max_rows * vec + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    // four vectors per thread and round; at most the blocks that are resident at once (one wave, no tail)
+    static int resident = 0;
+    if (resident == 0) {
+        int per_sm = 0, dev = 0, sms = 148;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gather_rows_kernel, 256, 0) != cudaSuccess || per_sm < 1) {
+            cudaGetLastError();
+            per_sm = 4;
+        }
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            cudaGetLastError();
+            sms = 148;
+        }
+        resident = per_sm * sms;
+    }
+    long long blocks = ((long long)max_rows * vec + 1023) / 1024;
+    if (blocks > resident) blocks = resident;
+    if (blocks < 1) blocks = 1;
     gather_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4 *>(x), perm, offsets,
                                                                       static_cast<uint4 *>(packed), E, vec);
     return launch_ok();
