@@ -23,15 +23,16 @@
 namespace fdmla {
 namespace clb {
 
-constexpr long long kChunkBytes = 1ll << 29;      // bound on the score workspace of one chunk (14 bytes per score)
+constexpr long long kChunkBytes = 1ll << 31;      // bound on the score workspace of one chunk (14 bytes per score)
+constexpr long long kChunkRowsMax = 131072;       // and on its rows (the elementwise kernel's grid: rows / 32 <= 65535)
 
 __host__ __device__ inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
 
-// rows of one chunk: a multiple of 128, at most what 512 MB of score workspace hold, at most the group's rows
+// rows of one chunk: a multiple of 128, at most what 2 GB of score workspace hold, at most the group's rows
 static int chunk_rows(long long R, int Skv) {
     long long rc = kChunkBytes / ((long long)Skv * 14) / 128 * 128;
     if (rc < 128) rc = 128;
-    if (rc > 16384) rc = 16384;
+    if (rc > kChunkRowsMax) rc = kChunkRowsMax;
     const long long r_up = round_up(R, 128);
     return (int)(rc < r_up ? rc : r_up);
 }

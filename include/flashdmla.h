@@ -367,8 +367,8 @@ int fdmla_bwd_on_the_fly(const void *Q, const void *K, const void *V,
  * value gradient is folded into the first d_v columns of dK_lat because
  * V = K_lat[..., :d_v].  Same formulas as above (fa2_bwd.cu:198-309).
  *   workspace: fdmla_bwd_cache_latent_workspace_bytes() bytes.  bf16 problems whose d_qk, d_v and Skv are multiples
- *   of 64 run as tensor-core GEMMs with the score matrices of up to 16 384 query rows at a time in the workspace
- *   (at most about 0.55 GB beside B*H*Sq floats and one fp32 copy of a batch entry's dK_lat); everything else runs
+ *   of 64 run as tensor-core GEMMs with the score matrices of up to 131 072 query rows at a time in the workspace
+ *   (at most about 2 GB beside B*H*Sq floats and up to 16 fp32 copies of a batch entry's dK_lat); everything else runs
  *   on the CUDA-core kernels and needs B*H*Sq floats.
  */
 size_t fdmla_bwd_cache_latent_workspace_bytes(int B, int H, int Sq, int Skv,
