@@ -65,42 +65,75 @@ static Layout layout(int G, long long R, int Skv, int d_qk) {
     return L;
 }
 
-// One 32 x 32 tile of scores per block (32 x 8 threads).  Rows r0 .. of the chunk are rows row_base + r of the group.
+// One 64 x 64 tile of scores per block of 256 threads.  Rows r0 .. of the chunk are rows row_base + r of the group.
+// Pass 1: a thread takes four keys (one 16-byte vector of S and of dP) of four rows - all eight loads issued before the
+// first use; vectors a causal row cannot see are not loaded at all - forms P and dS, stores dS as 8 bytes and drops both
+// into shared memory transposed.  Pass 2: eight rows (16 bytes) of one key per thread to P^T and dS^T.
+constexpr int SG_T = 64, SG_LD = SG_T + 8;       // tile edge; row pitch of the transposed tiles in bf16 (16-byte multiples)
 __global__ void __launch_bounds__(256)
 softmax_grad_kernel(const float *__restrict__ S, const float *__restrict__ dP, const float *__restrict__ m,
                     const float *__restrict__ l, const float *__restrict__ D, __nv_bfloat16 *__restrict__ dS,
                     __nv_bfloat16 *__restrict__ dST, __nv_bfloat16 *__restrict__ PT, int rc, int rows_valid, int Skv,
                     long long row_base, int Sq, int causal, float scale) {
-    __shared__ float tp[32][33], tds[32][33];
-    const int k0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-    const int tx = threadIdx.x, ty = threadIdx.y;
+    __shared__ __align__(16) __nv_bfloat16 tp[SG_T][SG_LD], tds[SG_T][SG_LD];      // [key][row]
+    const int k0 = blockIdx.x * SG_T, r0 = blockIdx.y * SG_T;
+    const int tid = threadIdx.x;
+    const int kq = (tid & 15) * 4;                 // this thread's four keys inside the tile
     const float sl2 = scale * 1.4426950408889634f;
     const int off = Skv - Sq;                      // key j is visible to query position i iff j <= i + off
+    float4 sv[4], dv[4];
+    float mv[4], lv[4], Dv[4];
+    int lim[4];                                    // last visible key of the row (-1: the row holds nothing)
 #pragma unroll
-    for (int rr = ty; rr < 32; rr += 8) {
-        const int r = r0 + rr, k = k0 + tx;
-        float p = 0.f, ds = 0.f;
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + (tid >> 4) + 16 * i;
+        lim[i] = -1;
+        mv[i] = 0.f; lv[i] = 0.f; Dv[i] = 0.f;
+        sv[i] = dv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < rows_valid) {
             const long long gr = row_base + r;
-            const bool vis = !causal || k <= (int)(gr % Sq) + off;
-            const float lv = l[gr];
-            if (vis && lv > 0.f) {
-                const size_t idx = (size_t)r * Skv + k;
-                p = exp2f(fmaf(S[idx], sl2, -m[gr] * 1.4426950408889634f)) / lv;
-                ds = p * (dP[idx] - D[gr]);
+            lv[i] = l[gr];
+            if (lv[i] > 0.f) lim[i] = causal ? (int)(gr % Sq) + off : Skv - 1;
+            if (k0 + kq <= lim[i]) {
+                mv[i] = m[gr]; Dv[i] = D[gr];
+                const size_t idx = (size_t)r * Skv + k0 + kq;
+                sv[i] = *reinterpret_cast<const float4 *>(S + idx);
+                dv[i] = *reinterpret_cast<const float4 *>(dP + idx);
             }
         }
-        if (r < rc) dS[(size_t)r * Skv + k] = __float2bfloat16(ds);
-        tp[rr][tx] = p;
-        tds[rr][tx] = ds;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int rr = (tid >> 4) + 16 * i, r = r0 + rr;
+        const float s4[4] = {sv[i].x, sv[i].y, sv[i].z, sv[i].w}, d4[4] = {dv[i].x, dv[i].y, dv[i].z, dv[i].w};
+        __nv_bfloat16 pb[4], db[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float pe = 0.f, de = 0.f;
+            if (k0 + kq + e <= lim[i]) {
+                pe = exp2f(fmaf(s4[e], sl2, -mv[i] * 1.4426950408889634f)) / lv[i];
+                de = pe * (d4[e] - Dv[i]);
+            }
+            pb[e] = __float2bfloat16(pe);
+            db[e] = __float2bfloat16(de);
+            tp[kq + e][rr] = pb[e];
+            tds[kq + e][rr] = db[e];
+        }
+        if (r < rc) {
+            uint2 w;
+            w.x = (uint32_t)__bfloat16_as_ushort(db[0]) | ((uint32_t)__bfloat16_as_ushort(db[1]) << 16);
+            w.y = (uint32_t)__bfloat16_as_ushort(db[2]) | ((uint32_t)__bfloat16_as_ushort(db[3]) << 16);
+            *reinterpret_cast<uint2 *>(dS + (size_t)r * Skv + k0 + kq) = w;
+        }
     }
     __syncthreads();
 #pragma unroll
-    for (int kk = ty; kk < 32; kk += 8) {
-        const int k = k0 + kk, r = r0 + tx;
-        if (r < rc) {
-            PT[(size_t)k * rc + r] = __float2bfloat16(tp[tx][kk]);
-            dST[(size_t)k * rc + r] = __float2bfloat16(tds[tx][kk]);
+    for (int i = 0; i < 2; ++i) {
+        const int kk = (tid >> 3) + 32 * i, r8 = (tid & 7) * 8;
+        if (r0 + r8 < rc) {                        // rc is a multiple of 128: a vector of eight rows is inside or outside
+            const size_t o = (size_t)(k0 + kk) * rc + r0 + r8;
+            *reinterpret_cast<uint4 *>(PT + o) = *reinterpret_cast<const uint4 *>(&tp[kk][r8]);
+            *reinterpret_cast<uint4 *>(dST + o) = *reinterpret_cast<const uint4 *>(&tds[kk][r8]);
         }
     }
 }
@@ -171,7 +204,7 @@ int launch_bwd_cache_latent_tensor(const BwdProblem &p_in, void *workspace, size
             // S = Q K^T, dP = dO V^T (rows past the chunk's end read as zero: the tensor maps end there)
             if ((rc = gemm(Qc, rows, dq, Kg, Skv, dq, 1, S, Skv, rows, Skv, dq, 1.f, 1, 0))) return rc;
             if ((rc = gemm(dOc, rows, dv, Kg, Skv, dq, 1, dP, Skv, rows, Skv, dv, 1.f, 1, 0))) return rc;
-            softmax_grad_kernel<<<dim3(Skv / 32, RC / 32), dim3(32, 8), 0, stream>>>(
+            softmax_grad_kernel<<<dim3(Skv / clb::SG_T, RC / clb::SG_T), 256, 0, stream>>>(
                 S, dP, p.m, p.l, p.D, dS, dST, PT, RC, rows, Skv, grow, p.Sq, p.causal, p.scale);
             if ((rc = check_launch())) return rc;
             // dQ = scale dS K
