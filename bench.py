@@ -824,8 +824,8 @@ def bench_cache_latent_bwd(dev, tf_peak, iters=5):
     return {"workload": f"cache-latent backward B={Bc} H={Hc} Sq=Skv={Sc} d=576/512 causal (autograd operator)", "ms": ms,
             "tflops_visible_half": flop / (ms * 1e-3) / 1e12, "frac_of_measured_bf16_peak": flop / (ms * 1e-3) / 1e12 / tf_peak,
             "kernel_family": flashdmla.last_kernel(),
-            "how": "five tcgen05 GEMM launches and one elementwise kernel per chunk of query rows (the masked half of the "
-                   "scores is computed too)"}
+            "how": "five tcgen05 GEMM launches and one elementwise kernel per chunk of query rows (causal: score tiles nobody sees are left out "
+                   "of the S, dP and dQ GEMMs; the dK GEMMs run over the masked half too)"}
 
 
 def bench_gemm(dev, tf_burst, hbm_peak, E=64):

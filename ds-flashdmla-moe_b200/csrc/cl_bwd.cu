@@ -190,9 +190,10 @@ int launch_bwd_cache_latent_tensor(const BwdProblem &p_in, void *workspace, size
                         *dO = static_cast<const __nv_bfloat16 *>(p.dO);
     __nv_bfloat16 *dQ = static_cast<__nv_bfloat16 *>(p.dQ), *dK = static_cast<__nv_bfloat16 *>(p.dK);
     auto gemm = [&](const void *A, long long a_rows, long long lda, const void *B, long long b_rows, long long ldb, int k_major,
-                    void *C, long long ldc, int M, int N, int Kd, float alpha, int c_f32, int acc) {
+                    void *C, long long ldc, int M, int N, int Kd, float alpha, int c_f32, int acc,
+                    const GemmCausalHint *hint = nullptr) {
         return launch_gemm_batched(A, B, nullptr, C, 1, M, N, Kd, a_rows, lda, 0, 0, b_rows, ldb, 0, 0, k_major, ldc, 0, 0, 0,
-                                   nullptr, stream, alpha, c_f32, acc);
+                                   nullptr, stream, alpha, c_f32, acc, hint);
     };
     for (int g = 0; g < p.G; ++g) {
         const __nv_bfloat16 *Kg = K + (size_t)g * Skv * dq;
@@ -202,13 +203,16 @@ int launch_bwd_cache_latent_tensor(const BwdProblem &p_in, void *workspace, size
             const __nv_bfloat16 *Qc = Q + grow * dq, *dOc = dO + grow * dv;
             int rc;
             // S = Q K^T, dP = dO V^T (rows past the chunk's end read as zero: the tensor maps end there)
-            if ((rc = gemm(Qc, rows, dq, Kg, Skv, dq, 1, S, Skv, rows, Skv, dq, 1.f, 1, 0))) return rc;
-            if ((rc = gemm(dOc, rows, dv, Kg, Skv, dq, 1, dP, Skv, rows, Skv, dv, 1.f, 1, 0))) return rc;
+            // causal: score tiles that no row of the tile sees are neither computed nor written (the elementwise kernel
+            // does not read them), and the reduction of dQ stops behind the last key a tile's rows see
+            const GemmCausalHint skip{p.causal ? 1 : 0, p.Sq, Skv - p.Sq, grow}, limit{p.causal ? 2 : 0, p.Sq, Skv - p.Sq, grow};
+            if ((rc = gemm(Qc, rows, dq, Kg, Skv, dq, 1, S, Skv, rows, Skv, dq, 1.f, 1, 0, &skip))) return rc;
+            if ((rc = gemm(dOc, rows, dv, Kg, Skv, dq, 1, dP, Skv, rows, Skv, dv, 1.f, 1, 0, &skip))) return rc;
             softmax_grad_kernel<<<dim3(Skv / clb::SG_T, RC / clb::SG_T), 256, 0, stream>>>(
                 S, dP, p.m, p.l, p.D, dS, dST, PT, RC, rows, Skv, grow, p.Sq, p.causal, p.scale);
             if ((rc = check_launch())) return rc;
             // dQ = scale dS K
-            if ((rc = gemm(dS, rows, Skv, Kg, Skv, dq, 0, dQ + grow * dq, dq, rows, dq, Skv, p.scale, 0, 0))) return rc;
+            if ((rc = gemm(dS, rows, Skv, Kg, Skv, dq, 0, dQ + grow * dq, dq, rows, dq, Skv, p.scale, 0, 0, &limit))) return rc;
             // dK (+)= scale dS^T Q;  dK[:, :d_v] += P^T dO   (reduction over the chunk's rows, zero-padded to RC, in KS
             // slices that run as a batch: slice s reads columns s RC/KS .. of dS^T / P^T and the same rows of Q / dO and
             // accumulates into slab s)

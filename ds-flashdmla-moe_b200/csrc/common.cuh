@@ -126,11 +126,16 @@ bool bwd_tensor_supported(const BwdProblem &p, int dtype, int grads_f32);
 int launch_bwd_tensor(const BwdProblem &p, cudaStream_t stream);
 int bwd_tensor_error_flag(int reset);
 // batched bf16 GEMM on tcgen05 (csrc/tc_gemm.cu) and the RoPE tail of the absorbed query
+// Causal hint for a GEMM of the attention backward: row m of an entry is query position (row0 + m) mod period and sees
+// columns (mode 1: S, dP - tiles nobody sees are neither computed nor written) or reduction indices (mode 2: dQ = dS K)
+// up to position + off.
+struct GemmCausalHint { int mode, period, off; long long row0; };
 int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
                         long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
                         int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
                         int gated, const int32_t *row_offsets, cudaStream_t stream, float alpha = 1.f, int c_f32 = 0,
-                        int accumulate = 0);
+                        int accumulate = 0,
+                        const GemmCausalHint *causal = nullptr);
 // cache-latent backward as GEMMs on the tensor cores with the score matrices in a workspace (csrc/cl_bwd.cu)
 bool bwd_cache_latent_tensor_supported(const BwdProblem &p, int dtype);
 size_t bwd_cache_latent_tensor_workspace(int G, long long R, int Skv, int d_qk);

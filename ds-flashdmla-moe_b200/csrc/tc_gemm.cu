@@ -72,7 +72,29 @@ struct Problem {
     // Grouped (ragged) mode: batch entry b owns rows [row_offsets[b], row_offsets[b + 1]) of A's and C's tensors (read on the
     // device: the packed rows of a MoE layer, whose per-expert counts the host never sees); M is then only an upper bound.
     const int32_t *row_offsets;
+    // Causal hint (attention backward; 0 = none).  Row m of an entry is query position (causal_row0 + m) mod
+    // causal_period and sees columns / reduction indices <= position + causal_off.
+    //   1: output tiles whose columns no row of the tile sees are not computed and not written (S, dP: the consumer
+    //      does not read them);  2: the reduction of a tile stops behind the last index one of its rows sees (dQ = dS K:
+    //      dS is zero beyond it).
+    int causal_mode, causal_period, causal_off, causal_row0;
 };
+
+// last column / reduction index that a row of the tile [m0, m0 + tile_m) sees (a tile that runs over the end of a period
+// sees everything the period's last position sees)
+__device__ __forceinline__ int causal_limit(const Problem &p, int m0, int tile_m) {
+    const int q0 = (p.causal_row0 + m0) % p.causal_period;
+    const int q1 = q0 + tile_m - 1;
+    return (q1 >= p.causal_period ? p.causal_period - 1 : q1) + p.causal_off;
+}
+__device__ __forceinline__ bool tile_skipped(const Problem &p, int m0, int n0, int tile_m) {
+    return p.causal_mode == 1 && n0 > causal_limit(p, m0, tile_m);
+}
+__device__ __forceinline__ int tile_k_steps(const Problem &p, int m0, int tile_m, int k_steps) {
+    if (p.causal_mode != 2) return k_steps;
+    const int need = (causal_limit(p, m0, tile_m) + BK) / BK;        // indices 0 .. limit
+    return need < 1 ? 1 : (need < k_steps ? need : k_steps);
+}
 
 // Walks the tiles of a launch in increasing order: tile -> (batch entry, first row, first column, rows of the entry).
 struct TileWalker {
@@ -170,8 +192,10 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         TileWalker w;
         for (long long tile = first_tile; !poisoned && ok && w.locate(p, tile, out_cols, TILE_M); tile += tile_step) {
             const int b = w.b, m0 = w.m0, n0 = w.n0;
+            if (tile_skipped(p, m0, n0, TILE_M)) continue;
             const int a_row = (p.row_offsets ? w.row0 : b * p.a_brow) + m0 + rank * BM;
-            for (int kb = 0; kb < k_steps && ok; ++kb) {
+            const int ks = tile_k_steps(p, m0, TILE_M, k_steps);
+            for (int kb = 0; kb < ks && ok; ++kb) {
                 if (use > 0) ok = mbar_wait(EMPTY(s), (use - 1) & 1);
                 if (ok && elected) {
                     const uint32_t dstA = smem_u32(smem + s * STAGE), dstB = dstA + A_BYTES;
@@ -213,14 +237,16 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         uint32_t ph = 0;
         int n_done = 0;                              // tiles this CTA has issued
         TileWalker w;
-        for (long long tile = first_tile; !poisoned && rank == 0 && w.locate(p, tile, out_cols, TILE_M); tile += tile_step, ++n_done) {
+        for (long long tile = first_tile; !poisoned && rank == 0 && w.locate(p, tile, out_cols, TILE_M); tile += tile_step) {
             if (!__all_sync(0xffffffffu, ok)) break;
+            if (tile_skipped(p, w.m0, w.n0, TILE_M)) continue;
+            const int ks = tile_k_steps(p, w.m0, TILE_M, k_steps);
             const int acc = n_done & 1;
             if (n_done >= 2) {
                 ok = ok && mbar_wait(ACC_EMPTY(acc), ((n_done >> 1) - 1) & 1);     // the epilogue has read this accumulator
                 tc_fence_after_sync();
             }
-            for (int kb = 0; kb < k_steps; ++kb) {
+            for (int kb = 0; kb < ks; ++kb) {
                 ok = ok && mbar_wait(FULL(s), ph);
                 tc_fence_after_sync();
                 if (elected) {
@@ -235,14 +261,15 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
                     }
                     if constexpr (PAIR) {
                         mma_commit_2cta(EMPTY(s), 3);
-                        if (kb == k_steps - 1) mma_commit_2cta(ACC_FULL(acc), 3);
+                        if (kb == ks - 1) mma_commit_2cta(ACC_FULL(acc), 3);
                     } else {
                         mma_commit(EMPTY(s));
-                        if (kb == k_steps - 1) mma_commit(ACC_FULL(acc));
+                        if (kb == ks - 1) mma_commit(ACC_FULL(acc));
                     }
                 }
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
+            ++n_done;
         }
         if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, ERR_MMA);
         __syncwarp();
@@ -254,8 +281,9 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
         bool ok = true;
         int n_done = 0;
         TileWalker w;
-        for (long long tile = first_tile; !poisoned && w.locate(p, tile, out_cols, TILE_M); tile += tile_step, ++n_done) {
+        for (long long tile = first_tile; !poisoned && w.locate(p, tile, out_cols, TILE_M); tile += tile_step) {
             const int b = w.b, m0 = w.m0, n0 = w.n0;
+            if (tile_skipped(p, m0, n0, TILE_M)) continue;
             const int acc = n_done & 1;
             if (ok) ok = mbar_wait(ACC_FULL(acc), (n_done >> 1) & 1);
             tc_fence_after_sync();
@@ -313,6 +341,7 @@ gemm_kernel(const Problem p, const __grid_constant__ CUtensorMap tmA, const __gr
             } else {
                 mbar_arrive(ACC_EMPTY(acc));                           // 128 arrivals free the accumulator
             }
+            ++n_done;
         }
         if (!ok) atomicCAS(&g_gemm_error, 0, ERR_EPILOGUE);
     }
@@ -367,7 +396,8 @@ int gemm_error_flag(int reset) {
 int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, int batch, int M, int N, int K,
                         long long a_rows, long long lda, int a_brow, int a_bcol, long long b_rows, long long ldb,
                         int b_brow, int b_bcol, int b_k_major, long long ldc, long long c_brow, long long c_bcol,
-                        int gated, const int32_t *row_offsets, cudaStream_t stream, float alpha, int c_f32, int accumulate) {
+                        int gated, const int32_t *row_offsets, cudaStream_t stream, float alpha, int c_f32, int accumulate,
+                        const GemmCausalHint *causal) {
     using namespace tcg;
     if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return FDMLA_OK;
     if (K % BK != 0 || N % 64 != 0 || lda % 8 != 0 || ldb % 64 != 0 || ldc % (c_f32 ? 8 : 16) != 0) return FDMLA_ERR_UNSUPPORTED;
@@ -384,6 +414,12 @@ int launch_gemm_batched(const void *A, const void *B, const void *B2, void *C, i
     p.alpha = alpha; p.c_f32 = c_f32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
     p.b_k_major = b_k_major ? 1 : 0; p.gated = gated ? 1 : 0;
     p.row_offsets = row_offsets;
+    if (causal && causal->mode != 0) {
+        if (row_offsets || causal->period <= 0 || causal->mode < 0 || causal->mode > 2 || (accumulate && causal->mode == 1))
+            return FDMLA_ERR_INVALID;
+        p.causal_mode = causal->mode; p.causal_period = causal->period; p.causal_off = causal->off;
+        p.causal_row0 = (int)(causal->row0 % causal->period);
+    }
     int dev = 0, sms = kNumSMs;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // CTA pairs with 256-row tiles when that pads an entry's rows no further than 128-row tiles would (ragged entries:

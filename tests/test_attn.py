@@ -310,10 +310,12 @@ def test_cache_latent_backward(dtype, backend, cuda):
 
 
 @pytest.mark.parametrize("shape", [(2, 3, 100, 128, 192, 128, True), (1, 4, 64, 192, 576, 512, True), (1, 2, 300, 256, 576, 512, False),
-                                   (1, 2, 130, 64, 64, 64, True)])
+                                   (1, 2, 130, 64, 64, 64, True), (1, 3, 512, 512, 576, 512, True), (1, 2, 384, 640, 192, 128, True)])
 def test_cache_latent_backward_on_tensor_cores(shape, cuda):
     """bf16 with d_qk, d_v and Skv multiples of 64: the backward runs as GEMMs on the tensor cores over a score
-    workspace (row counts that are not multiples of the 128-row tile, Sq != Skv, causal and not)."""
+    workspace (row counts that are not multiples of the 128-row tile, Sq != Skv, causal and not; the two largest
+    shapes have score tiles that no query row sees, which the score GEMMs leave out, and row tiles that run over the
+    end of a head)."""
     import flashdmla
     B, H, Sq, Skv, dq, dv, causal = shape
     Q = _rand((B, H, Sq, dq), 0.3, 61, torch.bfloat16)
