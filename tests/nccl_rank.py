@@ -87,6 +87,40 @@ def sequence_parallel_case(dev, world, rank):
         peer.xch.close()
 
 
+def absent_peer_case(dev, world, rank):
+    """A rank that does not take part in a step of the peer exchange: the others' kernels give up their wait after the
+    time limit, return, and report error code 31 through the device flag; the context stays usable and a new exchange
+    works again.  The absent rank is simply not launching (it sits in a host barrier), nothing is killed."""
+    import flashdmla
+    from flashdmla.exchange import PeerExchange
+    rows, d_v = 64, 512
+    g = torch.Generator().manual_seed(900 + rank)
+    msg = torch.cat([torch.randn(rows * d_v, generator=g), torch.randn(rows, generator=g), torch.rand(rows, generator=g) + 0.5]).to(dev)
+    out = (torch.full((rows, d_v), 7.0, device=dev), torch.full((rows,), 7.0, device=dev), torch.full((rows,), 7.0, device=dev))
+    xch = PeerExchange(rows, d_v, dev, timeout_ms=300)
+    xch.merge(msg, out)                                   # a step everybody takes part in
+    torch.cuda.synchronize()
+    assert flashdmla.device_error_flag() == 0 and float(out[2].min()) > 0.0 and float((out[2] - 7.0).abs().min()) > 0.0
+    dist.barrier()
+    for t in out:
+        t.fill_(7.0)
+    if rank != world - 1:                                 # the last rank stays away from this step
+        xch.merge(msg, out)
+        torch.cuda.synchronize()
+        assert flashdmla.device_error_flag() == 31
+        assert flashdmla.device_error_flag(reset=True) == 31 and flashdmla.device_error_flag() == 0
+        if world == 2:                                    # every row needed the absent rank: nothing was written
+            assert all(float((t - 7.0).abs().max()) == 0.0 for t in out)
+    dist.barrier()
+    xch.close()
+    again = PeerExchange(rows, d_v, dev, timeout_ms=2000)   # fresh buffers and counters: the ranks are in step again
+    again.merge(msg, out)
+    torch.cuda.synchronize()
+    assert flashdmla.device_error_flag() == 0 and float((out[2] - 7.0).abs().min()) > 0.0
+    dist.barrier()
+    again.close()
+
+
 def expert_parallel_case(dev, world, rank):
     from flashdmla.moe import MoEFFN
     layer = MoEFFN(d_model=128, d_ff=256, n_experts=12, top_k=3, capacity_factor=1.0, device=dev, seed=4)    # same weights on every rank
@@ -112,6 +146,7 @@ def main():
         context_parallel_case(dev, world, rank)
         sequence_parallel_case(dev, world, rank)
         expert_parallel_case(dev, world, rank)
+        absent_peer_case(dev, world, rank)
         torch.cuda.synchronize()
         dist.barrier()
         print(f"rank {rank} of {world}: exchange checks passed", flush=True)

@@ -23,6 +23,9 @@ def test_exchange_steps_over_nccl(cuda):
     here = os.path.dirname(os.path.abspath(__file__))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(here, "nccl_rank.py")]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    # one of the cases keeps a rank away from a step of the peer exchange (nobody exits, nothing is killed); in-switch
+    # reduction is switched off for the run all the same, so that no rank's memory is bound to a multicast object
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert out.stdout.count("exchange checks passed") == world
