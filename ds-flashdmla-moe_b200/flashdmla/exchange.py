@@ -42,20 +42,41 @@ class PeerExchange:
         self._own = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
         self._peers = {}
+        self._bufs = (ctypes.c_void_p * self.world)()
+        # Every rank goes through the same collectives whether its own set-up works or not; a failure anywhere is
+        # agreed on with an all-reduce and raised on all ranks together, so that no rank is left in a barrier alone.
+        failure = None
         with torch.cuda.device(device):
-            check(L.fdmla_exchange_alloc(nbytes, ctypes.byref(self._own), handle), "fdmla_exchange_alloc")
+            rc = L.fdmla_exchange_alloc(nbytes, ctypes.byref(self._own), handle)
+            if rc != 0:
+                failure = f"fdmla_exchange_alloc failed with status {rc}"
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle.raw), group=group)
-            self._bufs = (ctypes.c_void_p * self.world)()
-            for p in range(self.world):
-                if p == self.rank:
-                    self._bufs[p] = self._own.value
-                else:
+            dist.all_gather_object(handles, bytes(handle.raw) if failure is None else None, group=group)
+            if failure is None and any(h is None for h in handles):
+                failure = "a peer could not allocate its exchange buffer"
+            if failure is None:
+                for p in range(self.world):
+                    if p == self.rank:
+                        self._bufs[p] = self._own.value
+                        continue
                     ptr = ctypes.c_void_p()
-                    check(L.fdmla_exchange_open(ctypes.create_string_buffer(handles[p], 64), ctypes.byref(ptr)),
-                          f"fdmla_exchange_open (rank {p})")
+                    rc = L.fdmla_exchange_open(ctypes.create_string_buffer(handles[p], 64), ctypes.byref(ptr))
+                    if rc != 0:
+                        failure = f"fdmla_exchange_open of rank {p}'s buffer failed with status {rc} (CUDA IPC between the ranks' processes)"
+                        break
                     self._peers[p] = ptr
                     self._bufs[p] = ptr.value
+            ok = torch.tensor([0 if failure else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                for ptr in self._peers.values():
+                    L.fdmla_exchange_close(ptr)
+                self._peers = {}
+                dist.barrier(group=group)           # nobody frees a buffer that a peer may still be unmapping
+                if self._own:
+                    L.fdmla_exchange_free(self._own)
+                    self._own = ctypes.c_void_p()
+                raise FlashDMLAError("peer exchange not set up: " + (failure or "the set-up failed on another rank"))
         dist.barrier(group=group)       # every buffer is zeroed and mapped before anyone stores into it
 
     def merge(self, msg: torch.Tensor, out):

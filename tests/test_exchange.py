@@ -50,6 +50,11 @@ def test_exchange_argument_validation_needs_no_gpu():
     assert L.fdmla_exchange_merge(None, None, 2, 0, 8, 512, None, None, None, 0, 0, None) == -1       # no time limit
     assert L.fdmla_exchange_alloc(0, None, None) == -1 and L.fdmla_exchange_open(None, None) == -1
     assert L.fdmla_exchange_close(None) == 0 and L.fdmla_exchange_free(None) == 0
+    assert L.fdmla_exchange_merge_parts(None, None, None, 0, None, None, 2, 0, 8, 512, None, None, None, 0, 100, None) == -1   # no pieces
+    # the host side refuses anything but CUDA devices before it touches the process group: there is no CPU path
+    from flashdmla.exchange import PeerExchange
+    with pytest.raises(_lib.FlashDMLAError):
+        PeerExchange(8, 512, "cpu")
 
 
 @pytest.mark.gpu
